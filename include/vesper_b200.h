@@ -1,0 +1,210 @@
+/*
+ * vesper_b200 -- C ABI of the B200 (sm_100a) attention backend.
+ *
+ * These entry points are what Vesper's CUDA backend seam binds for its
+ * attention hot path.  Every function
+ *   - borrows all pointers (device memory unless stated), allocates nothing
+ *     on the device and frees nothing;
+ *   - launches asynchronously on the caller's stream and never synchronises
+ *     the device;
+ *   - returns VB200_OK or a negative vb200_status (never throws, never aborts).
+ * "file:line" citations name the reference interface each entry point stands
+ * behind, relative to the reference project root.
+ */
+#ifndef VESPER_B200_H
+#define VESPER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VB200_ABI_VERSION 1
+
+typedef enum vb200_status {
+    VB200_OK = 0,
+    VB200_ERR_INVALID_ARG = -1,   /* null pointer, bad shape, Hq % Hkv != 0, ...      */
+    VB200_ERR_UNSUPPORTED = -2,   /* dtype / head_dim combination without a kernel    */
+    VB200_ERR_ALIGNMENT = -3,     /* pointer or stride not 16-byte aligned            */
+    VB200_ERR_WORKSPACE = -4,     /* workspace missing or too small                   */
+    VB200_ERR_CUDA = -5,          /* a CUDA runtime/driver call failed                */
+    VB200_ERR_NO_DEVICE = -6,     /* no usable sm_100 device                          */
+    VB200_ERR_KERNEL_TIMEOUT = -7 /* a bounded in-kernel wait expired (status word)   */
+} vb200_status;
+
+typedef enum vb200_dtype {
+    VB200_F32 = 0,   /* fp32 in/out, fp32 math on CUDA cores                          */
+    VB200_BF16 = 1,  /* bf16 in/out, fp32 accumulate                                  */
+    VB200_F16 = 2    /* fp16 in/out, fp32 accumulate                                  */
+} vb200_dtype;
+
+/* A [B, H, S, D] tensor view: element strides for B, H, S; D is contiguous.
+ * Mirrors vesper::Tensor's shape/strides/offset view (include/vesper/core/tensor.h:26-80)
+ * with the offset already folded into `ptr`. */
+typedef struct vb200_tensor4 {
+    void* ptr;
+    int64_t stride_b, stride_h, stride_s;
+} vb200_tensor4;
+
+/* Rotary embedding in the convention the attention modules use
+ * (functional::compute_rope_frequencies + apply_rotary_emb,
+ * src/nn/functional.cpp:424-494): adjacent pairs (x[2i], x[2i+1]) rotated by
+ * angle float(pos) * inv_freq[i].  inv_freq is a HOST array of D/2 floats, as
+ * vb200_rope_inv_freq() fills it (the reference's own fp32 expression). */
+typedef struct vb200_rope {
+    int32_t enabled;
+    const float* inv_freq_host;
+} vb200_rope;
+
+/* ---- prefill / flash attention ------------------------------------------
+ * One call = for T new tokens at positions start_pos .. start_pos+T-1:
+ *   rotate Q and K (if rope.enabled), append rotated K and raw V to the cache
+ *   rows [start_pos, start_pos+T) (if k_cache is non-null), then attention of
+ *   the T queries over keys [0, start_pos+T), causal = bottom-right aligned
+ *   (key j visible to query i iff j <= start_pos + i), GQA by head-group
+ *   indexing (kv_head = q_head / (Hq/Hkv)), output O and natural-log LSE.
+ * With k_cache == NULL and rope disabled it is exactly the flash op:
+ *   replaces flash_attention_cuda_dispatch (src/ops/flash_attention.cpp:28-32,
+ *   src/ops/cuda/flash_attention.cu:518-544).
+ * With a cache it replaces the chain in GroupedQueryAttention::forward(x,cache,pos)
+ *   src/nn/gqa_attention.cpp:124-149 (apply_rotary_emb, KVCache::update,
+ *   repeat_kv, scaled_dot_product_attention) and the same chain in
+ *   MultiHeadAttention::forward, src/nn/transformer.cpp:184-204.
+ */
+typedef struct vb200_prefill_args {
+    uint32_t struct_size;        /* sizeof(vb200_prefill_args)                       */
+    int32_t device;              /* CUDA ordinal, or -1 for the current device       */
+    void* stream;                /* cudaStream_t                                     */
+    int32_t dtype;               /* vb200_dtype of q,k,v,o and the cache             */
+    int32_t B, Hq, Hkv, T, D;    /* T = number of new tokens (query rows)            */
+    int32_t start_pos;           /* position of the first new token                  */
+    int32_t causal;              /* 0 / 1                                            */
+    float scale;                 /* multiplies q.k before max/exp                    */
+    vb200_tensor4 q;             /* [B,Hq,T,D]                                       */
+    vb200_tensor4 k, v;          /* [B,Hkv,T,D] new keys / values                    */
+    vb200_tensor4 o;             /* [B,Hq,T,D] output                                */
+    float* lse;                  /* [B,Hq,T] contiguous fp32, nullable               */
+    vb200_rope rope;
+    vb200_tensor4 k_cache, v_cache; /* [B,Hkv,cap,D]; ptr NULL = no cache            */
+    int32_t cache_cap;
+    void* workspace;             /* vb200_prefill_workspace_bytes() bytes, 256-aligned */
+    size_t workspace_bytes;
+} vb200_prefill_args;
+
+size_t vb200_prefill_workspace_bytes(const vb200_prefill_args* a);
+int vb200_prefill_fwd(const vb200_prefill_args* a);
+
+/* ---- decode ---------------------------------------------------------------
+ * One call = one new token per sequence (T = 1): rotate q and the new k at
+ * position seq_lens[b] (if rope.enabled), append k/v at cache row seq_lens[b]
+ * (if k_new is non-null), then attention of the one query row over keys
+ * [kv_begin, seq_lens[b] + appended) with the Hq/Hkv query heads of a group
+ * sharing each K/V fetch, split over `num_splits` CTAs per (b, kv_head) and
+ * merged by a log-sum-exp combine.
+ * Replaces, for T == 1, the same reference chain as prefill plus the five
+ * generic ops of the standard attention path (matmul, div, softmax, matmul,
+ * src/nn/functional.cpp:399-421; kernels src/ops/cuda/gemm.cu:257-388,
+ * src/ops/cuda/normalization.cu:68-267) and the strided copy behind
+ * KVCache::update (src/ops/cuda/copy.cu:17-93).
+ *
+ * seq_lens is a DEVICE int32[B] holding each sequence's length BEFORE this
+ * token; when k_new is given and advance_lens != 0 the kernel stores
+ * seq_lens[b] + 1 back after the step (so consecutive calls need no host
+ * work).  seq_lens == NULL means every sequence has length `uniform_len`.
+ *
+ * partial_out != NULL selects the sequence-sharded form (each GPU holds a
+ * contiguous shard of the KV sequence): instead of o/lse the kernel writes,
+ * per (b, q_head), D+2 floats: O normalised by the shard's own l, then m (max
+ * of the scaled scores, natural units), then l (sum of exp(s - m)).  After an
+ * all-gather of these records, vb200_lse_combine merges them.  pos_offset is
+ * the absolute position of cache row 0 of this shard; q_positions (device
+ * int32[B], nullable) gives the query's absolute position for RoPE when it is
+ * not pos_offset + seq_lens[b] (i.e. on every shard but the last);
+ * append_enabled = 0 makes a shard attend without appending.
+ */
+typedef struct vb200_decode_args {
+    uint32_t struct_size;
+    int32_t device;
+    void* stream;
+    int32_t dtype;
+    int32_t B, Hq, Hkv, D;
+    float scale;
+    vb200_tensor4 q;             /* [B,Hq,1,D]                                       */
+    vb200_tensor4 k_new, v_new;  /* [B,Hkv,1,D]; ptr NULL = nothing to append        */
+    vb200_tensor4 o;             /* [B,Hq,1,D]                                       */
+    float* lse;                  /* [B,Hq] fp32, nullable                            */
+    vb200_rope rope;
+    vb200_tensor4 k_cache, v_cache; /* [B,Hkv,cap,D]                                 */
+    int32_t cache_cap;
+    int32_t* seq_lens;           /* device int32[B] or NULL                          */
+    int32_t uniform_len;         /* used when seq_lens == NULL                       */
+    int32_t advance_lens;        /* store len+1 back into seq_lens after appending   */
+    int32_t max_len;             /* upper bound of any sequence length after the
+                                    step (sizes the split grid); 0 = cache_cap       */
+    int32_t num_splits;          /* 0 = choose                                       */
+    int64_t pos_offset;          /* absolute position of cache row 0 (sharding)      */
+    int32_t append_enabled;      /* 0: ignore k_new/v_new (a shard that does not own
+                                    the new token); 1: append and attend to it       */
+    const int32_t* q_positions;  /* device int32[B] or NULL                          */
+    float* partial_out;          /* NULL, or [B,Hq,D+2] fp32: O/l, then m, then l    */
+    void* workspace;
+    size_t workspace_bytes;
+} vb200_decode_args;
+
+size_t vb200_decode_workspace_bytes(const vb200_decode_args* a);
+int vb200_decode_fwd(const vb200_decode_args* a);
+
+/* Merge R partial results [R, rows, D+2] (layout of partial_out) into
+ * out [rows, D] of `dtype` and lse [rows] (nullable):
+ *   m* = max m_r,  l* = sum l_r e^{m_r - m*},  O* = sum O_r l_r e^{m_r - m*} / l*
+ * -- the online-softmax algebra of src/ops/flash_attention.cpp:309-345 applied
+ * across shards. */
+int vb200_lse_combine(int device, void* stream, const float* partials, int32_t R,
+                      int64_t rows, int32_t D, int32_t dtype, void* out, float* lse);
+
+/* ---- cache append without attention ---------------------------------------
+ * Rotates K (if rope.enabled) and writes K, V rows [start_pos, start_pos+T)
+ * of the cache.  Replaces the copy_strided_cuda_dispatch calls behind
+ * KVCache::update (src/nn/transformer.cpp:56-93, src/ops/cuda/copy.cu:75-93). */
+int vb200_kv_append(int device, void* stream, int32_t dtype,
+                    int32_t B, int32_t Hkv, int32_t T, int32_t D, int32_t start_pos,
+                    const vb200_tensor4* k, const vb200_tensor4* v,
+                    const vb200_tensor4* k_cache, const vb200_tensor4* v_cache,
+                    int32_t cache_cap, const vb200_rope* rope);
+
+/* In-place rotary embedding of x [B,H,S,D] with a caller-built cos/sin table
+ * [S, D/2] each.  Replaces apply_rope_cuda (src/nn/rope.cpp:25-28,
+ * src/ops/cuda/rope.cu:186-208). */
+int vb200_apply_rope(int device, void* stream, float* x, const float* cos_table,
+                     const float* sin_table, int32_t batch, int32_t heads,
+                     int32_t seq_len, int32_t head_dim);
+
+/* out[b, qh, s, :] = in[b, qh / n_rep, s, :] honouring the input view's strides.
+ * Replaces repeat_kv_cuda_dispatch (src/ops/attention_ops.cpp:24-27,
+ * src/ops/cuda/attention_ops.cu:69-96).  The attention entry points above do
+ * not need it; it exists so the op surface links. */
+int vb200_repeat_kv(int device, void* stream, int32_t dtype, const vb200_tensor4* in,
+                    void* out, int32_t B, int32_t Hkv, int32_t S, int32_t D, int32_t n_rep);
+
+/* Host helper: inv_freq[i] = powf(theta, -2.0f * i / D), i < D/2 -- the fp32
+ * expression of src/nn/functional.cpp:433. */
+void vb200_rope_inv_freq(float theta, int32_t D, float* inv_freq_host);
+
+const char* vb200_strerror(int status);
+/* Text of the last CUDA error seen by the calling thread (empty if none). */
+const char* vb200_last_error_detail(void);
+int vb200_abi_version(void);
+/* Number of kernels launched by this library from the calling thread since
+ * the last reset (used by the benchmark's launch count). */
+uint64_t vb200_launch_count(void);
+void vb200_reset_launch_count(void);
+/* Reads and clears the device-side status word that bounded waits set
+ * (synchronises the given stream).  Returns VB200_OK or VB200_ERR_KERNEL_TIMEOUT. */
+int vb200_check_kernel_status(int device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VESPER_B200_H */

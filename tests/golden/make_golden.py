@@ -1,0 +1,125 @@
+"""Generate the golden vectors under tests/golden from the UNMODIFIED reference.
+
+Run where the reference tree is mounted:
+
+    make -C oracle ref            # builds oracle/_ref/libvesper_ref.so from the reference sources
+    python tests/golden/make_golden.py
+
+Every .npz holds the inputs and the outputs the reference's own CPU code
+produced for them (through oracle/ref_shim.cpp).  The reference entry point
+behind each file is named in CASES below.  The files are what pins the plain-C
+oracle (tests/test_oracle_golden.py) on machines without the reference tree.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "..", ".."))
+from oracle.binding import Ref  # noqa: E402
+
+
+def save(name, **arrays):
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, **arrays)
+    print(f"{name}: {os.path.getsize(path) / 1024:.0f} KiB")
+
+
+def main():
+    r = Ref()
+
+    # -- config 1: ops::manual_seed(0); randn q,k,v; flash_attention_cpu_dispatch
+    #    (src/ops/flash_attention.cpp:218-364), B=1 H=8 S=256 D=64 causal, scale 1/8.
+    q, k, v = r.randn_seq(0, [(1, 8, 256, 64)] * 3)
+    o, lse = r.flash_attention(q, k, v, 0.125, True)
+    o_sdpa = r.sdpa(q, k, v, True)   # standard path (S<512), src/nn/functional.cpp:399-421
+    save("c1_flash_fp32", q=q, k=k, v=v, o=o, lse=lse, o_sdpa=o_sdpa, scale=np.float32(0.125))
+
+    # -- the shapes tests/test_flash_attention.cpp uses (:110-179, :195-284), plus ragged N
+    rng = np.random.default_rng(1234)
+    for name, (B, H, N, D), causal in [
+        ("flash_b2h4n64d64_noncausal", (2, 4, 64, 64), False),
+        ("flash_b2h8n128d64_causal", (2, 8, 128, 64), True),
+        ("flash_b4h2n32d128_causal", (4, 2, 32, 128), True),
+        ("flash_b1h2n50d64_causal", (1, 2, 50, 64), True),
+        ("flash_b1h2n33d128_noncausal", (1, 2, 33, 128), False),
+        ("flash_b1h1n1d64_causal", (1, 1, 1, 64), True),
+        ("flash_b1h2n130d128_causal", (1, 2, 130, 128), True),
+    ]:
+        q, k, v = (rng.standard_normal((B, H, N, D), dtype=np.float32) for _ in range(3))
+        scale = np.float32(1.0 / np.sqrt(D))
+        o, lse = r.flash_attention(q, k, v, float(scale), causal)
+        save(name, q=q, k=k, v=v, o=o, lse=lse, scale=scale, causal=np.int32(causal))
+
+    # -- the router at S>=512: functional::scaled_dot_product_attention -> flash
+    #    (src/nn/functional.cpp:385-395), one head S=512 D=64.
+    q, k, v = (rng.standard_normal((1, 1, 512, 64), dtype=np.float32) for _ in range(3))
+    save("sdpa_router_s512", q=q, k=k, v=v, o=r.sdpa(q, k, v, True))
+
+    # -- standard path with q_len != kv_len (decode shape), non-causal
+    q = rng.standard_normal((2, 4, 1, 64), dtype=np.float32)
+    k, v = (rng.standard_normal((2, 4, 37, 64), dtype=np.float32) for _ in range(2))
+    save("sdpa_decode_t1_l37", q=q, k=k, v=v, o=r.sdpa(q, k, v, False))
+
+    # -- RoPE: compute_rope_frequencies + apply_rotary_emb (src/nn/functional.cpp:424-494)
+    for name, (B, H, S, D), sp, theta in [
+        ("rope_s8d64_pos0", (1, 2, 8, 64), 0, 10000.0),
+        ("rope_s5d128_pos1000", (2, 2, 5, 128), 1000, 10000.0),
+        ("rope_s3d128_pos131000", (1, 1, 3, 128), 131000, 10000.0),
+        ("rope_s4d32_theta500k", (1, 1, 4, 32), 7, 500000.0),
+    ]:
+        x = rng.standard_normal((B, H, S, D), dtype=np.float32)
+        save(name, x=x, freqs=r.rope_frequencies(S, D, sp, theta), y=r.apply_rope(x, sp, theta),
+             start_pos=np.int32(sp), theta=np.float32(theta))
+
+    # -- ops::repeat_kv (src/ops/attention_ops.cpp:92-130) on contiguous input
+    x = rng.standard_normal((2, 2, 5, 16), dtype=np.float32)
+    save("repeat_kv_n3", x=x, y=r.repeat_kv(x, 3), n_rep=np.int32(3))
+
+    # -- nn::KVCache::update (src/nn/transformer.cpp:56-93): prefill 3 rows, then 2 appends
+    c = r.kvcache(2, 2, 8, 4)
+    steps = {}
+    pos = 0
+    for i, T in enumerate([3, 1, 1]):
+        nk, nv = (rng.standard_normal((2, 2, T, 4), dtype=np.float32) for _ in range(2))
+        ko, vo = c.update(nk, nv, pos)
+        steps.update({f"new_k{i}": nk, f"new_v{i}": nv, f"k_view{i}": ko, f"v_view{i}": vo,
+                      f"start{i}": np.int32(pos)})
+        pos += T
+    save("kvcache_update", **steps)
+
+    # -- GQA attention core with cache (src/nn/gqa_attention.cpp:111-159 composed from
+    #    reference ops with contiguous cache views): prefill T=8 at pos 0, then 4 decode steps.
+    for name, (B, Hq, Hkv, D, cap, T0, nsteps) in [
+        ("gqa_cached_b2hq4hkv2d32", (2, 4, 2, 32, 64, 8, 4)),
+        ("gqa_cached_b1hq8hkv2d128", (1, 8, 2, 128, 160, 70, 3)),
+        ("mha_cached_b2h2d64", (2, 2, 2, 64, 32, 5, 3)),
+    ]:
+        c = r.kvcache(B, Hkv, cap, D)
+        out = {"dims": np.array([B, Hq, Hkv, D, cap, T0, nsteps], np.int32)}
+        pos = 0
+        for i in range(nsteps + 1):
+            T = T0 if i == 0 else 1
+            qq = rng.standard_normal((B, Hq, T, D), dtype=np.float32)
+            kk = rng.standard_normal((B, Hkv, T, D), dtype=np.float32)
+            vv = rng.standard_normal((B, Hkv, T, D), dtype=np.float32)
+            out.update({f"q{i}": qq, f"k{i}": kk, f"v{i}": vv,
+                        f"o{i}": r.gqa_attention_cached(c, qq, kk, vv, pos, 10000.0, True)})
+            pos += T
+        save(name, **out)
+
+    # -- module level: GroupedQueryAttention::forward(x, causal) (uncached; right for any
+    #    n_rep) with caller-set weights.  C=64, Hq=4, Hkv=2, D=16, T=12.
+    Cdim, Hq, Hkv, T = 64, 4, 2, 12
+    D = Cdim // Hq
+    wqkv = (0.1 * rng.standard_normal(((Hq + 2 * Hkv) * D, Cdim))).astype(np.float32)
+    wo = (0.1 * rng.standard_normal((Cdim, Hq * D))).astype(np.float32)
+    x = rng.standard_normal((2, T, Cdim), dtype=np.float32)
+    g = r.gqa(Cdim, Hq, Hkv, 64, 10000.0, wqkv, wo)
+    save("gqa_module_forward", wqkv=wqkv, wo=wo, x=x, y=g.forward(x, True),
+         dims=np.array([Cdim, Hq, Hkv, T], np.int32))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,227 @@
+"""ctypes binding of libvesper_b200.so (include/vesper_b200.h) for the Python
+test / benchmark harness.  Device buffers are torch CUDA tensors (plumbing
+only: memory, streams); every computation goes through the C ABI.
+
+The library must be present: there is no fallback path.  ``load()`` raises
+when the shared object is missing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "lib", "libvesper_b200.so")
+
+F32, BF16, F16 = 0, 1, 2
+OK = 0
+
+
+class Tensor4(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_s", C.c_int64)]
+
+
+class Rope(C.Structure):
+    _fields_ = [("enabled", C.c_int32), ("inv_freq_host", C.POINTER(C.c_float))]
+
+
+class PrefillArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("device", C.c_int32), ("stream", C.c_void_p), ("dtype", C.c_int32),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("T", C.c_int32), ("D", C.c_int32),
+        ("start_pos", C.c_int32), ("causal", C.c_int32), ("scale", C.c_float),
+        ("q", Tensor4), ("k", Tensor4), ("v", Tensor4), ("o", Tensor4), ("lse", C.c_void_p),
+        ("rope", Rope), ("k_cache", Tensor4), ("v_cache", Tensor4), ("cache_cap", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class DecodeArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("device", C.c_int32), ("stream", C.c_void_p), ("dtype", C.c_int32),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32), ("scale", C.c_float),
+        ("q", Tensor4), ("k_new", Tensor4), ("v_new", Tensor4), ("o", Tensor4), ("lse", C.c_void_p),
+        ("rope", Rope), ("k_cache", Tensor4), ("v_cache", Tensor4), ("cache_cap", C.c_int32),
+        ("seq_lens", C.c_void_p), ("uniform_len", C.c_int32), ("advance_lens", C.c_int32),
+        ("max_len", C.c_int32), ("num_splits", C.c_int32), ("pos_offset", C.c_int64),
+        ("append_enabled", C.c_int32), ("q_positions", C.c_void_p), ("partial_out", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+EXPORTS = [
+    "vb200_prefill_workspace_bytes", "vb200_prefill_fwd", "vb200_decode_workspace_bytes", "vb200_decode_fwd",
+    "vb200_lse_combine", "vb200_kv_append", "vb200_apply_rope", "vb200_repeat_kv", "vb200_rope_inv_freq",
+    "vb200_strerror", "vb200_last_error_detail", "vb200_abi_version", "vb200_launch_count",
+    "vb200_reset_launch_count", "vb200_check_kernel_status",
+]
+
+_lib = None
+
+
+class Vb200Error(RuntimeError):
+    def __init__(self, status, text):
+        super().__init__(text)
+        self.status = status
+
+
+def load():
+    """dlopen the C-ABI library (raises if it has not been built)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(f"{LIB_PATH} is missing: run `python -m vesper_b200.build` (needs nvcc)")
+    L = C.CDLL(LIB_PATH)
+    L.vb200_prefill_workspace_bytes.argtypes = [C.POINTER(PrefillArgs)]
+    L.vb200_prefill_workspace_bytes.restype = C.c_size_t
+    L.vb200_prefill_fwd.argtypes = [C.POINTER(PrefillArgs)]
+    L.vb200_decode_workspace_bytes.argtypes = [C.POINTER(DecodeArgs)]
+    L.vb200_decode_workspace_bytes.restype = C.c_size_t
+    L.vb200_decode_fwd.argtypes = [C.POINTER(DecodeArgs)]
+    L.vb200_lse_combine.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+    L.vb200_kv_append.argtypes = [C.c_int, C.c_void_p, C.c_int32] + [C.c_int32] * 5 + [C.POINTER(Tensor4)] * 4 + [C.c_int32, C.POINTER(Rope)]
+    L.vb200_apply_rope.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int32] * 4
+    L.vb200_repeat_kv.argtypes = [C.c_int, C.c_void_p, C.c_int32, C.POINTER(Tensor4), C.c_void_p] + [C.c_int32] * 5
+    L.vb200_rope_inv_freq.argtypes = [C.c_float, C.c_int32, C.POINTER(C.c_float)]
+    L.vb200_rope_inv_freq.restype = None
+    L.vb200_strerror.argtypes = [C.c_int]
+    L.vb200_strerror.restype = C.c_char_p
+    L.vb200_last_error_detail.restype = C.c_char_p
+    L.vb200_launch_count.restype = C.c_uint64
+    L.vb200_reset_launch_count.restype = None
+    L.vb200_check_kernel_status.argtypes = [C.c_int, C.c_void_p]
+    _lib = L
+    return L
+
+
+def check(rc):
+    if rc != OK:
+        L = load()
+        raise Vb200Error(rc, f"vb200 status {rc} ({L.vb200_strerror(rc).decode()}): {L.vb200_last_error_detail().decode()}")
+
+
+def dtype_code(t):
+    import torch
+    return {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}[t.dtype]
+
+
+def view4(t):
+    """[B,H,S,D] torch tensor (any strides, D contiguous) -> Tensor4."""
+    if t is None:
+        return Tensor4(None, 0, 0, 0)
+    assert t.dim() == 4 and t.stride(3) == 1
+    return Tensor4(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+
+def inv_freq(theta, D):
+    arr = (C.c_float * (D // 2))()
+    load().vb200_rope_inv_freq(theta, D, arr)
+    return arr
+
+
+def _stream_ptr(stream):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def prefill_args(q, k, v, o, lse=None, *, scale, causal=True, start_pos=0, theta=None,
+                 k_cache=None, v_cache=None, workspace=None, stream=None):
+    B, Hq, T, D = q.shape
+    a = PrefillArgs()
+    a.struct_size = C.sizeof(PrefillArgs)
+    a.device = q.device.index if q.device.index is not None else -1
+    a.stream = _stream_ptr(stream)
+    a.dtype = dtype_code(q)
+    a.B, a.Hq, a.Hkv, a.T, a.D = B, Hq, k.shape[1], T, D
+    a.start_pos, a.causal, a.scale = start_pos, int(causal), scale
+    a.q, a.k, a.v, a.o = view4(q), view4(k), view4(v), view4(o)
+    a.lse = _ptr(lse)
+    keep = None
+    if theta is not None:
+        keep = inv_freq(theta, D)
+        a.rope = Rope(1, keep)
+    else:
+        a.rope = Rope(0, None)
+    a.k_cache, a.v_cache = view4(k_cache), view4(v_cache)
+    a.cache_cap = k_cache.shape[2] if k_cache is not None else 0
+    a.workspace = _ptr(workspace)
+    a.workspace_bytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    a._keep = keep
+    return a
+
+
+def prefill(q, k, v, o, lse=None, *, scale, causal=True, start_pos=0, theta=None,
+            k_cache=None, v_cache=None, workspace=None, stream=None):
+    """vb200_prefill_fwd on torch CUDA tensors.  Allocates a workspace with torch when none is given."""
+    import torch
+    L = load()
+    a = prefill_args(q, k, v, o, lse, scale=scale, causal=causal, start_pos=start_pos, theta=theta,
+                     k_cache=k_cache, v_cache=v_cache, workspace=workspace, stream=stream)
+    need = L.vb200_prefill_workspace_bytes(C.byref(a))
+    if need > a.workspace_bytes:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+        a.workspace, a.workspace_bytes = _ptr(workspace), need
+    check(L.vb200_prefill_fwd(C.byref(a)))
+    return workspace
+
+
+def decode_args(q, o, k_cache, v_cache, *, scale, k_new=None, v_new=None, lse=None, theta=None,
+                seq_lens=None, uniform_len=0, advance_lens=False, max_len=0, num_splits=0,
+                pos_offset=0, append_enabled=True, q_positions=None, partial_out=None,
+                workspace=None, stream=None):
+    B, Hq, _, D = q.shape
+    a = DecodeArgs()
+    a.struct_size = C.sizeof(DecodeArgs)
+    a.device = q.device.index if q.device.index is not None else -1
+    a.stream = _stream_ptr(stream)
+    a.dtype = dtype_code(q)
+    a.B, a.Hq, a.Hkv, a.D, a.scale = B, Hq, k_cache.shape[1], D, scale
+    a.q, a.k_new, a.v_new, a.o = view4(q), view4(k_new), view4(v_new), view4(o)
+    a.lse = _ptr(lse)
+    keep = None
+    if theta is not None:
+        keep = inv_freq(theta, D)
+        a.rope = Rope(1, keep)
+    else:
+        a.rope = Rope(0, None)
+    a.k_cache, a.v_cache = view4(k_cache), view4(v_cache)
+    a.cache_cap = k_cache.shape[2]
+    a.seq_lens = _ptr(seq_lens)
+    a.uniform_len, a.advance_lens, a.max_len, a.num_splits = uniform_len, int(advance_lens), max_len, num_splits
+    a.pos_offset, a.append_enabled = pos_offset, int(append_enabled)
+    a.q_positions, a.partial_out = _ptr(q_positions), _ptr(partial_out)
+    a.workspace = _ptr(workspace)
+    a.workspace_bytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    a._keep = keep
+    return a
+
+
+def decode(q, o, k_cache, v_cache, **kw):
+    """vb200_decode_fwd on torch CUDA tensors.  Allocates a workspace with torch when none is given."""
+    import torch
+    L = load()
+    a = decode_args(q, o, k_cache, v_cache, **kw)
+    need = L.vb200_decode_workspace_bytes(C.byref(a))
+    ws = kw.get("workspace")
+    if need > a.workspace_bytes:
+        ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+        a.workspace, a.workspace_bytes = _ptr(ws), need
+    check(L.vb200_decode_fwd(C.byref(a)))
+    return ws
+
+
+def lse_combine(partials, out, lse=None, stream=None):
+    """partials [R, rows, D+2] fp32 -> out [rows, D] (bf16/fp16), lse [rows]."""
+    R, rows, Dp2 = partials.shape
+    check(load().vb200_lse_combine(partials.device.index, _stream_ptr(stream), _ptr(partials), R, rows, Dp2 - 2,
+                                   dtype_code(out), _ptr(out), _ptr(lse)))
+
+
+def check_kernel_status(device=0, stream=None):
+    check(load().vb200_check_kernel_status(device, _stream_ptr(stream)))

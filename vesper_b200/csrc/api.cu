@@ -1,0 +1,363 @@
+// extern "C" entry points of libvesper_b200: argument validation, workspace
+// carving and kernel orchestration.  No device allocation, no synchronisation
+// (except vb200_check_kernel_status, which is documented to synchronise).
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "kernels.h"
+
+namespace vb200 {
+
+__device__ int g_kernel_status = 0;
+
+int* kernel_status_word() {
+    // one symbol instance per device; cache the address per ordinal
+    static thread_local int* cache[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cache[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_kernel_status) != cudaSuccess) return nullptr;
+        cache[dev] = static_cast<int*>(p);
+    }
+    return cache[dev];
+}
+
+namespace {
+thread_local std::string t_detail;
+thread_local uint64_t t_launches = 0;
+}  // namespace
+
+void note_launch(int n) { t_launches += static_cast<uint64_t>(n); }
+
+int cuda_fail(cudaError_t e, const char* what) {
+    t_detail = std::string(what) + ": " + cudaGetErrorString(e);
+    return VB200_ERR_CUDA;
+}
+
+int set_detail(int status, const char* msg) {
+    t_detail = msg;
+    return status;
+}
+
+namespace {
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline int elem_size(int dtype) { return dtype == VB200_F32 ? 4 : 2; }
+inline bool dtype_ok(int dtype) { return dtype == VB200_F32 || dtype == VB200_BF16 || dtype == VB200_F16; }
+
+// 16-byte alignment of the base and of every stride, which both the vector
+// loads and the TMA descriptors need.
+bool view_aligned(const vb200_tensor4& t, int esz) {
+    auto ok = [&](long long s) { return (s * esz) % 16 == 0; };
+    return (reinterpret_cast<uintptr_t>(t.ptr) % 16 == 0) && ok(t.stride_b) && ok(t.stride_h) && ok(t.stride_s);
+}
+
+struct PrefillPlan {
+    bool need_table, need_krot;   // krot: rotated K without a cache goes to the workspace
+    size_t table_bytes, krot_bytes, total;
+};
+
+PrefillPlan plan_prefill(const vb200_prefill_args* a) {
+    PrefillPlan pl{};
+    pl.need_table = a->rope.enabled != 0;
+    pl.need_krot = a->rope.enabled && a->k_cache.ptr == nullptr;
+    pl.table_bytes = pl.need_table ? align_up(static_cast<size_t>(a->T) * (a->D / 2) * sizeof(float2), 256) : 0;
+    pl.krot_bytes = pl.need_krot ? align_up(static_cast<size_t>(a->B) * a->Hkv * a->T * a->D * elem_size(a->dtype), 256) : 0;
+    pl.total = pl.table_bytes + pl.krot_bytes;
+    return pl;
+}
+
+int validate_prefill(const vb200_prefill_args* a) {
+    if (!a || a->struct_size != sizeof(vb200_prefill_args)) return set_detail(VB200_ERR_INVALID_ARG, "vb200_prefill_args: null or struct_size mismatch");
+    if (!dtype_ok(a->dtype)) return set_detail(VB200_ERR_UNSUPPORTED, "unknown dtype");
+    if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->T <= 0 || a->D <= 0) return set_detail(VB200_ERR_INVALID_ARG, "B, Hq, Hkv, T, D must be positive");
+    if (a->Hq % a->Hkv != 0) return set_detail(VB200_ERR_INVALID_ARG, "Hq must be divisible by Hkv");
+    if (a->start_pos < 0) return set_detail(VB200_ERR_INVALID_ARG, "start_pos must be >= 0");
+    if (!a->q.ptr || !a->k.ptr || !a->v.ptr || !a->o.ptr) return set_detail(VB200_ERR_INVALID_ARG, "q, k, v, o must be non-null");
+    if (a->D % 8 != 0 || a->D > 128) return set_detail(VB200_ERR_UNSUPPORTED, "head_dim must be a multiple of 8 and <= 128");
+    if ((a->k_cache.ptr == nullptr) != (a->v_cache.ptr == nullptr)) return set_detail(VB200_ERR_INVALID_ARG, "k_cache and v_cache must both be given or both be null");
+    if (a->k_cache.ptr) {
+        if (a->start_pos + a->T > a->cache_cap) return set_detail(VB200_ERR_INVALID_ARG, "start_pos + T exceeds the cache capacity");
+    } else if (a->start_pos != 0) {
+        return set_detail(VB200_ERR_INVALID_ARG, "start_pos > 0 needs a cache holding the earlier keys");
+    }
+    if (a->rope.enabled && !a->rope.inv_freq_host) return set_detail(VB200_ERR_INVALID_ARG, "rope enabled without inv_freq_host");
+    int esz = elem_size(a->dtype);
+    if (!view_aligned(a->q, esz) || !view_aligned(a->k, esz) || !view_aligned(a->v, esz) || !view_aligned(a->o, esz))
+        return set_detail(VB200_ERR_ALIGNMENT, "q/k/v/o base and strides must be 16-byte aligned");
+    if (a->k_cache.ptr && (!view_aligned(a->k_cache, esz) || !view_aligned(a->v_cache, esz)))
+        return set_detail(VB200_ERR_ALIGNMENT, "cache base and strides must be 16-byte aligned");
+    return VB200_OK;
+}
+
+void fill_inv_freq(InvFreq& f, const vb200_rope& r, int D) {
+    std::memset(&f, 0, sizeof(f));
+    if (r.enabled) std::memcpy(f.v, r.inv_freq_host, sizeof(float) * (D / 2));
+}
+
+struct DecodePlan {
+    int num_splits, chunk, ws_header;
+    size_t total;
+};
+
+DecodePlan plan_decode(const vb200_decode_args* a) {
+    DecodePlan pl{};
+    const int tile = decode_tile_keys();
+    int max_total = (a->max_len > 0 ? a->max_len : a->cache_cap);
+    if (max_total < 1) max_total = 1;
+    int chunk;
+    if (a->num_splits > 0) {
+        chunk = (max_total + a->num_splits - 1) / a->num_splits;
+    } else {
+        // enough CTAs for about two waves of 2 CTAs/SM on 148 SMs, but never
+        // more than 512 keys per CTA so ragged batches balance
+        long long units = static_cast<long long>(a->B) * a->Hkv;
+        int want = static_cast<int>((592 + units - 1) / units);
+        chunk = (max_total + want - 1) / want;
+        if (chunk > 512) chunk = 512;
+    }
+    chunk = (chunk + tile - 1) / tile * tile;
+    if (chunk < tile) chunk = tile;
+    pl.chunk = chunk;
+    pl.num_splits = (max_total + chunk - 1) / chunk;
+    pl.ws_header = (a->B + 63) / 64 * 64;
+    int nrep = a->Hq / a->Hkv;
+    pl.total = sizeof(float) * (static_cast<size_t>(pl.ws_header) +
+                                static_cast<size_t>(a->B) * a->Hkv * pl.num_splits * nrep * (a->D + 2));
+    pl.total = align_up(pl.total, 256);
+    return pl;
+}
+
+int validate_decode(const vb200_decode_args* a) {
+    if (!a || a->struct_size != sizeof(vb200_decode_args)) return set_detail(VB200_ERR_INVALID_ARG, "vb200_decode_args: null or struct_size mismatch");
+    if (!dtype_ok(a->dtype)) return set_detail(VB200_ERR_UNSUPPORTED, "unknown dtype");
+    if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->D <= 0) return set_detail(VB200_ERR_INVALID_ARG, "B, Hq, Hkv, D must be positive");
+    if (a->Hq % a->Hkv != 0) return set_detail(VB200_ERR_INVALID_ARG, "Hq must be divisible by Hkv");
+    if (!a->q.ptr || !a->k_cache.ptr || !a->v_cache.ptr) return set_detail(VB200_ERR_INVALID_ARG, "q, k_cache, v_cache must be non-null");
+    if (!a->o.ptr && !a->partial_out) return set_detail(VB200_ERR_INVALID_ARG, "o or partial_out must be given");
+    if ((a->k_new.ptr == nullptr) != (a->v_new.ptr == nullptr)) return set_detail(VB200_ERR_INVALID_ARG, "k_new and v_new must both be given or both be null");
+    if (a->cache_cap <= 0) return set_detail(VB200_ERR_INVALID_ARG, "cache_cap must be positive");
+    if (!a->seq_lens && (a->uniform_len < 0 || a->uniform_len + (a->k_new.ptr ? 1 : 0) > a->cache_cap))
+        return set_detail(VB200_ERR_INVALID_ARG, "uniform_len out of range for the cache");
+    if (a->rope.enabled && !a->rope.inv_freq_host) return set_detail(VB200_ERR_INVALID_ARG, "rope enabled without inv_freq_host");
+    int esz = elem_size(a->dtype);
+    if (!view_aligned(a->q, esz) || !view_aligned(a->k_cache, esz) || !view_aligned(a->v_cache, esz))
+        return set_detail(VB200_ERR_ALIGNMENT, "q / cache base and strides must be 16-byte aligned");
+    if (a->k_new.ptr && (!view_aligned(a->k_new, esz) || !view_aligned(a->v_new, esz)))
+        return set_detail(VB200_ERR_ALIGNMENT, "k_new / v_new base and strides must be 16-byte aligned");
+    if (a->o.ptr && !view_aligned(a->o, esz)) return set_detail(VB200_ERR_ALIGNMENT, "o base and strides must be 16-byte aligned");
+    return VB200_OK;
+}
+
+}  // namespace
+}  // namespace vb200
+
+using namespace vb200;
+
+extern "C" {
+
+int vb200_abi_version(void) { return VB200_ABI_VERSION; }
+
+const char* vb200_strerror(int status) {
+    switch (status) {
+        case VB200_OK: return "ok";
+        case VB200_ERR_INVALID_ARG: return "invalid argument";
+        case VB200_ERR_UNSUPPORTED: return "unsupported dtype / head_dim / layout";
+        case VB200_ERR_ALIGNMENT: return "pointer or stride not 16-byte aligned";
+        case VB200_ERR_WORKSPACE: return "workspace missing or too small";
+        case VB200_ERR_CUDA: return "CUDA error";
+        case VB200_ERR_NO_DEVICE: return "no usable CUDA device";
+        case VB200_ERR_KERNEL_TIMEOUT: return "a bounded in-kernel wait expired";
+        default: return "unknown status";
+    }
+}
+
+const char* vb200_last_error_detail(void) { return t_detail.c_str(); }
+uint64_t vb200_launch_count(void) { return t_launches; }
+void vb200_reset_launch_count(void) { t_launches = 0; }
+
+void vb200_rope_inv_freq(float theta, int32_t D, float* inv_freq_host) {
+    // src/nn/functional.cpp:433: std::pow(theta, -2.0f * i / dim), all fp32
+    for (int i = 0; i < D / 2; ++i) inv_freq_host[i] = std::pow(theta, -2.0f * i / D);
+}
+
+int vb200_check_kernel_status(int device, void* stream) {
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int host = 0;
+    VB200_CUDA_TRY(cudaMemcpyFromSymbolAsync(&host, g_kernel_status, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
+    VB200_CUDA_TRY(cudaStreamSynchronize(s));
+    if (host == 0) return VB200_OK;
+    int zero = 0;
+    VB200_CUDA_TRY(cudaMemcpyToSymbolAsync(g_kernel_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, s));
+    VB200_CUDA_TRY(cudaStreamSynchronize(s));
+    char buf[96];
+    std::snprintf(buf, sizeof(buf), "kernel wait expired: code %d, site 0x%x", host >> 24, host & 0xFFFFFF);
+    return set_detail(VB200_ERR_KERNEL_TIMEOUT, buf);
+}
+
+size_t vb200_prefill_workspace_bytes(const vb200_prefill_args* a) {
+    if (!a || a->struct_size != sizeof(vb200_prefill_args)) return 0;
+    return plan_prefill(a).total;
+}
+
+int vb200_prefill_fwd(const vb200_prefill_args* a) {
+    if (int rc = validate_prefill(a)) return rc;
+    PrefillPlan pl = plan_prefill(a);
+    if (pl.total > 0) {
+        if (!a->workspace || a->workspace_bytes < pl.total) return set_detail(VB200_ERR_WORKSPACE, "prefill workspace too small (see vb200_prefill_workspace_bytes)");
+        if (reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0) return set_detail(VB200_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+    }
+    DeviceGuard g;
+    if (int rc = g.init(a->device)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(a->stream);
+
+    float2* table = nullptr;
+    unsigned char* ws = static_cast<unsigned char*>(a->workspace);
+    if (pl.need_table) {
+        table = reinterpret_cast<float2*>(ws);
+        InvFreq f;
+        fill_inv_freq(f, a->rope, a->D);
+        if (int rc = launch_rope_table(s, table, a->T, a->D, a->start_pos, f)) return rc;
+    }
+
+    PrefillParams p{};
+    p.dtype = a->dtype;
+    p.B = a->B; p.Hq = a->Hq; p.Hkv = a->Hkv; p.T = a->T; p.D = a->D;
+    p.Skv = a->start_pos + a->T;
+    p.start_pos = a->start_pos;
+    p.causal = a->causal;
+    p.scale = a->scale;
+    p.q = to_view(a->q);
+    p.o = to_view(a->o);
+    p.lse = a->lse;
+    p.q_rope_table = table;
+    p.status = kernel_status_word();
+    if (!p.status) return set_detail(VB200_ERR_CUDA, "cannot resolve the device status word");
+
+    if (a->k_cache.ptr) {
+        // fused RoPE(K) + append; attention then reads K/V straight from the cache
+        if (int rc = launch_kv_append(s, a->dtype, a->B, a->Hkv, a->T, a->D, to_view(a->k), to_view(a->v),
+                                      to_view(a->k_cache), to_view(a->v_cache), a->start_pos, table)) return rc;
+        p.k = to_view(a->k_cache);
+        p.v = to_view(a->v_cache);
+    } else if (pl.need_krot) {
+        View4 krot{ws + pl.table_bytes, static_cast<long long>(a->Hkv) * a->T * a->D, static_cast<long long>(a->T) * a->D, a->D};
+        if (int rc = launch_kv_append(s, a->dtype, a->B, a->Hkv, a->T, a->D, to_view(a->k), View4{nullptr, 0, 0, 0},
+                                      krot, View4{nullptr, 0, 0, 0}, 0, table)) return rc;
+        p.k = krot;
+        p.v = to_view(a->v);
+    } else {
+        p.k = to_view(a->k);
+        p.v = to_view(a->v);
+    }
+
+    if (a->dtype == VB200_F32) return launch_prefill_f32(s, p);
+    return launch_prefill_sm100(s, p);
+}
+
+size_t vb200_decode_workspace_bytes(const vb200_decode_args* a) {
+    if (!a || a->struct_size != sizeof(vb200_decode_args)) return 0;
+    if (a->B <= 0 || a->Hkv <= 0 || a->Hq <= 0 || a->Hq % a->Hkv != 0) return 0;
+    return plan_decode(a).total;
+}
+
+int vb200_decode_fwd(const vb200_decode_args* a) {
+    if (int rc = validate_decode(a)) return rc;
+    if (a->D != 128 || a->dtype == VB200_F32) return set_detail(VB200_ERR_UNSUPPORTED, "decode supports bf16/fp16 with head_dim 128");
+    if (a->k_cache.stride_s != a->D || a->v_cache.stride_s != a->D) return set_detail(VB200_ERR_UNSUPPORTED, "cache rows must be contiguous (stride_s == D)");
+    DecodePlan pl = plan_decode(a);
+    if (!a->workspace || a->workspace_bytes < pl.total) return set_detail(VB200_ERR_WORKSPACE, "decode workspace too small (see vb200_decode_workspace_bytes)");
+    if (reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0) return set_detail(VB200_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+    DeviceGuard g;
+    if (int rc = g.init(a->device)) return rc;
+
+    DecodeParams p{};
+    p.dtype = a->dtype;
+    p.B = a->B; p.Hq = a->Hq; p.Hkv = a->Hkv; p.D = a->D;
+    p.scale = a->scale;
+    p.q = to_view(a->q);
+    p.k_new = to_view(a->k_new);
+    p.v_new = to_view(a->v_new);
+    p.o = to_view(a->o);
+    p.lse = a->lse;
+    p.k_cache = to_view(a->k_cache);
+    p.v_cache = to_view(a->v_cache);
+    p.cache_cap = a->cache_cap;
+    p.seq_lens = a->seq_lens;
+    p.uniform_len = a->uniform_len;
+    p.advance_lens = a->advance_lens;
+    p.append = (a->k_new.ptr != nullptr && a->append_enabled) ? 1 : 0;
+    p.rope = a->rope.enabled;
+    fill_inv_freq(p.inv_freq, a->rope, a->D);
+    p.pos_offset = a->pos_offset;
+    p.q_positions = a->q_positions;
+    p.num_splits = pl.num_splits;
+    p.chunk = pl.chunk;
+    p.partial_out = a->partial_out;
+    p.workspace = static_cast<float*>(a->workspace);
+    p.ws_header = pl.ws_header;
+    p.status = kernel_status_word();
+    if (!p.status) return set_detail(VB200_ERR_CUDA, "cannot resolve the device status word");
+    return launch_decode(static_cast<cudaStream_t>(a->stream), p);
+}
+
+int vb200_lse_combine(int device, void* stream, const float* partials, int32_t R,
+                      int64_t rows, int32_t D, int32_t dtype, void* out, float* lse) {
+    if (!partials || !out || R <= 0 || rows < 0 || D <= 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_lse_combine: bad arguments");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    return launch_lse_combine(static_cast<cudaStream_t>(stream), partials, R, rows, D, dtype, out, lse);
+}
+
+int vb200_kv_append(int device, void* stream, int32_t dtype,
+                    int32_t B, int32_t Hkv, int32_t T, int32_t D, int32_t start_pos,
+                    const vb200_tensor4* k, const vb200_tensor4* v,
+                    const vb200_tensor4* k_cache, const vb200_tensor4* v_cache,
+                    int32_t cache_cap, const vb200_rope* rope) {
+    if (!k || !v || !k_cache || !v_cache || !k->ptr || !v->ptr || !k_cache->ptr || !v_cache->ptr)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_kv_append: null tensor");
+    if (!dtype_ok(dtype)) return set_detail(VB200_ERR_UNSUPPORTED, "unknown dtype");
+    if (B <= 0 || Hkv <= 0 || T <= 0 || D <= 0 || D % 8 != 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_kv_append: bad shape");
+    if (start_pos < 0 || start_pos + T > cache_cap) return set_detail(VB200_ERR_INVALID_ARG, "vb200_kv_append: rows exceed the cache capacity");
+    if (rope && rope->enabled && !rope->inv_freq_host) return set_detail(VB200_ERR_INVALID_ARG, "rope enabled without inv_freq_host");
+    int esz = elem_size(dtype);
+    if (!view_aligned(*k, esz) || !view_aligned(*v, esz) || !view_aligned(*k_cache, esz) || !view_aligned(*v_cache, esz))
+        return set_detail(VB200_ERR_ALIGNMENT, "vb200_kv_append: 16-byte alignment required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    InvFreq f;
+    bool rot = rope && rope->enabled;
+    if (rot) fill_inv_freq(f, *rope, D);
+    return launch_kv_append(static_cast<cudaStream_t>(stream), dtype, B, Hkv, T, D, to_view(*k), to_view(*v),
+                            to_view(*k_cache), to_view(*v_cache), start_pos, nullptr, rot ? &f : nullptr);
+}
+
+int vb200_apply_rope(int device, void* stream, float* x, const float* cos_table,
+                     const float* sin_table, int32_t batch, int32_t heads,
+                     int32_t seq_len, int32_t head_dim) {
+    if (!x || !cos_table || !sin_table || batch <= 0 || heads <= 0 || seq_len <= 0 || head_dim <= 0 || head_dim % 2 != 0)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_apply_rope: bad arguments");
+    if (reinterpret_cast<uintptr_t>(x) % 8 != 0) return set_detail(VB200_ERR_ALIGNMENT, "vb200_apply_rope: x must be 8-byte aligned");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    return launch_apply_rope_f32(static_cast<cudaStream_t>(stream), x, cos_table, sin_table, batch, heads, seq_len, head_dim);
+}
+
+int vb200_repeat_kv(int device, void* stream, int32_t dtype, const vb200_tensor4* in,
+                    void* out, int32_t B, int32_t Hkv, int32_t S, int32_t D, int32_t n_rep) {
+    if (!in || !in->ptr || !out || B <= 0 || Hkv <= 0 || S <= 0 || D <= 0 || n_rep <= 0 || D % 8 != 0)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_repeat_kv: bad arguments");
+    if (!dtype_ok(dtype)) return set_detail(VB200_ERR_UNSUPPORTED, "unknown dtype");
+    if (!view_aligned(*in, elem_size(dtype)) || reinterpret_cast<uintptr_t>(out) % 16 != 0)
+        return set_detail(VB200_ERR_ALIGNMENT, "vb200_repeat_kv: 16-byte alignment required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    return launch_repeat_kv(static_cast<cudaStream_t>(stream), dtype, to_view(*in), out, B, Hkv, S, D, n_rep);
+}
+
+}  // extern "C"

@@ -1,0 +1,426 @@
+// Split-KV decode: one new token per sequence attends to its (ragged) KV cache.
+//
+// Bandwidth-bound by design: every K and V row is read from HBM exactly once
+// per KV head (the Hq/Hkv query heads of a group share the fetch -- the
+// grouped indexing kv_head = q_head / n_rep of src/ops/attention_ops.cpp:47
+// without materialising repeat_kv), streamed by 1-D bulk async copies into a
+// shared-memory ring, with fp32 dot products and accumulation on CUDA cores.
+// RoPE of the new q/k (src/nn/functional.cpp:424-494) and the append of the
+// new k/v row (KVCache::update, src/nn/transformer.cpp:56-93) are fused in.
+//
+// Grid (split, kv_head, batch).  A CTA owns keys [split*chunk, (split+1)*chunk)
+// of one (batch, kv_head) and emits a partial (O/l, m, l) per query head; the
+// combine kernel merges the splits with the log-sum-exp algebra of
+// src/ops/flash_attention.cpp:309-345.
+#include "kernels.h"
+
+namespace vb200 {
+
+namespace {
+
+constexpr int kTile = 64;        // keys per pipeline stage
+constexpr int kStages = 3;
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;   // + 1 producer warp
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale O only when the max grows by > 2^8
+
+// Sum 16 values across the 16 lanes of a group: afterwards lane g (0..15)
+// holds the total of vals[g] in vals[0].  15 shuffles instead of 64.
+__device__ __forceinline__ float group16_reduce_scatter(float (&vals)[16], int l16) {
+#pragma unroll
+    for (int off = 8, n = 16; off >= 1; off >>= 1, n >>= 1) {
+        bool upper = (l16 & off) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            float send = upper ? vals[i] : vals[i + n / 2];
+            float keep = upper ? vals[i + n / 2] : vals[i];
+            vals[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, off);
+        }
+    }
+    return vals[0];
+}
+
+template <typename T, int NREP>
+struct WarpState {
+    float q[NREP][8];     // rotated q * scale * log2(e), this lane's 8 dims
+    float o[NREP][8];     // unnormalised output accumulator
+    float m;              // running reference max (log2 units) of this lane's head
+    float l;              // partial sum of p for this lane's (head, key slot)
+};
+
+// Process `nkeys` consecutive rows of a K buffer and a V buffer in shared
+// memory (row = 128 elements of T).  Rows are dealt to the participating warps
+// in slices of 2*KB keys (KB = 16/NREP keys per half-warp group and batch);
+// `wslot` in [0, nwslots).  The loop trip count is warp-uniform (both
+// half-warps run the same iterations; rows past nkeys are masked) because the
+// body uses full-warp shuffles.
+template <typename T, int NREP>
+__device__ __forceinline__ void process_rows(WarpState<T, NREP>& st, const T* ksm, const T* vsm, int nkeys,
+                                             int wslot, int nwslots, int lane, float* pbuf /* [16] per group */) {
+    constexpr int KB = 16 / NREP;
+    const int l16 = lane & 15;
+    const int my_k = l16 / NREP;
+    for (int wbase = wslot * 2 * KB; wbase < nkeys; wbase += nwslots * 2 * KB) {
+        const int base = wbase + (lane >> 4) * KB;
+        float vals[16];
+#pragma unroll
+        for (int kk = 0; kk < KB; ++kk) {
+            int key = base + kk;
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (key < nkeys) raw = *reinterpret_cast<const uint4*>(ksm + key * 128 + l16 * 8);
+            float kf[8];
+            const uint32_t* u = &raw.x;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { float2 t = Elem<T>::unpack2(u[i]); kf[2 * i] = t.x; kf[2 * i + 1] = t.y; }
+#pragma unroll
+            for (int h = 0; h < NREP; ++h) {
+                float a = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) a = fmaf(st.q[h][i], kf[i], a);
+                vals[kk * NREP + h] = a;
+            }
+        }
+        float s = group16_reduce_scatter(vals, l16);       // score (log2 units) of (key my_k, head my_h)
+        if (base + my_k >= nkeys) s = -INFINITY;
+
+        float bm = s;                                       // max over the batch's keys for my head
+#pragma unroll
+        for (int off = NREP; off < 16; off <<= 1) bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, off));
+        bool grow = bm > st.m + kRescaleThreshold;          // includes the first batch (m = -inf)
+        if (__any_sync(0xFFFFFFFFu, grow)) {
+            float m_new = grow ? bm : st.m;
+            float alpha = (st.m == -INFINITY) ? 0.f : fast_exp2(st.m - m_new);
+            st.l *= alpha;
+            st.m = m_new;
+#pragma unroll
+            for (int h = 0; h < NREP; ++h) {
+                // lane h of the group holds head h (key slot 0)
+                float ah = __shfl_sync(0xFFFFFFFFu, alpha, (threadIdx.x & 16) + h);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) st.o[h][i] *= ah;
+            }
+        }
+        float p = (s == -INFINITY) ? 0.f : fast_exp2(s - st.m);
+        st.l += p;
+        pbuf[l16] = p;
+        __syncwarp();
+#pragma unroll
+        for (int kk = 0; kk < KB; ++kk) {
+            int key = base + kk;
+            if (key < nkeys) {
+                uint4 raw = *reinterpret_cast<const uint4*>(vsm + key * 128 + l16 * 8);
+                float vf[8];
+                const uint32_t* u = &raw.x;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { float2 t = Elem<T>::unpack2(u[i]); vf[2 * i] = t.x; vf[2 * i + 1] = t.y; }
+#pragma unroll
+                for (int h = 0; h < NREP; ++h) {
+                    float ph = pbuf[kk * NREP + h];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) st.o[h][i] = fmaf(ph, vf[i], st.o[h][i]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
+struct __align__(16) DecodeSmem {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    int abort_flag;
+    int pad[3];
+};
+
+// Dynamic shared memory layout (D = 128, 16-bit T):
+//   [0, kStages * 2 * kTile * 256)   K/V ring: stage s -> K at s*32 KB, V at s*32 KB + 16 KB
+//   then 2 rows (rotated new k, new v), then the per-group p buffers, then DecodeSmem.
+template <typename T, int NREP>
+__global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p) {
+    constexpr int D = 128;
+    constexpr int kRowBytes = D * sizeof(T);
+    constexpr int kStageBytes = 2 * kTile * kRowBytes;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    T* ring = reinterpret_cast<T*>(smem_raw);
+    T* newkv = reinterpret_cast<T*>(smem_raw + kStages * kStageBytes);          // [2][128]
+    float* pbuf_all = reinterpret_cast<float*>(smem_raw + kStages * kStageBytes + 2 * kRowBytes);   // [8][16]
+    DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem_raw + kStages * kStageBytes + 2 * kRowBytes + 8 * 16 * sizeof(float));
+
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, l16 = lane & 15;
+
+    const int len = p.seq_lens ? p.seq_lens[b] : p.uniform_len;    // cached keys before this token
+    const int total = len + (p.append ? 1 : 0);
+    const int k_begin = split * p.chunk;
+    if (split == 0 && kvh == 0 && threadIdx.x == 0) {
+        // length this step used, for the combine kernel (stable even when seq_lens advances)
+        reinterpret_cast<int*>(p.workspace)[b] = len;
+    }
+    if (k_begin >= total) return;                                   // nothing for this split
+    const int k_end = min(len, k_begin + p.chunk);                  // cached keys [k_begin, k_end)
+    const bool owns_new = p.append && (len / p.chunk == split);
+    const int ntiles = (k_end > k_begin) ? (k_end - k_begin + kTile - 1) / kTile : 0;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], kConsumerWarps); }
+        sm->abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const WaitCtx abort_flag{&sm->abort_flag, p.status};
+
+    const T* kc = static_cast<const T*>(p.k_cache.ptr) + b * p.k_cache.sb + kvh * p.k_cache.sh;
+    const T* vc = static_cast<const T*>(p.v_cache.ptr) + b * p.v_cache.sb + kvh * p.v_cache.sh;
+
+    if (warp == kConsumerWarps) {
+        // ---------------- producer: one lane streams K/V tiles ----------------
+        if (lane == 0) {
+            for (int t = 0; t < ntiles; ++t) {
+                int s = t % kStages;
+                if (t >= kStages && !mbar_wait(&sm->empty[s], ((t / kStages) - 1) & 1, abort_flag, 0x10)) break;
+                int row0 = k_begin + t * kTile;
+                int nk = min(kTile, k_end - row0);
+                uint32_t bytes = static_cast<uint32_t>(nk) * kRowBytes;
+                mbar_arrive_expect_tx(&sm->full[s], 2 * bytes);
+                unsigned char* dst = smem_raw + s * kStageBytes;
+                bulk_load(dst, kc + static_cast<long long>(row0) * D, bytes, &sm->full[s]);
+                bulk_load(dst + kTile * kRowBytes, vc + static_cast<long long>(row0) * D, bytes, &sm->full[s]);
+            }
+        }
+    } else {
+        // ---------------- consumers ----------------
+        WarpState<T, NREP> st;
+        st.m = -INFINITY; st.l = 0.f;
+#pragma unroll
+        for (int h = 0; h < NREP; ++h)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) st.o[h][i] = 0.f;
+
+        // rotation angles of the query / new token for this lane's 4 pairs
+        float cs[4], sn[4];
+        if (p.rope) {
+            float pos = __int2float_rn(p.q_positions ? p.q_positions[b] : static_cast<int>(p.pos_offset) + len);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sincosf(pos * p.inv_freq.v[l16 * 4 + i], &sn[i], &cs[i]);
+        }
+        const float qscale = p.scale * kLog2e;
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            const T* qp = static_cast<const T*>(p.q.ptr) + b * p.q.sb + (kvh * NREP + h) * p.q.sh + l16 * 8;
+            uint4 raw = *reinterpret_cast<const uint4*>(qp);
+            const uint32_t* u = &raw.x;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float2 t = Elem<T>::unpack2(u[i]);
+                if (p.rope) {
+                    float t1 = __fmul_rn(t.x, cs[i]), t2 = __fmul_rn(t.y, sn[i]);
+                    float t3 = __fmul_rn(t.x, sn[i]), t4 = __fmul_rn(t.y, cs[i]);
+                    t.x = __fsub_rn(t1, t2); t.y = __fadd_rn(t3, t4);
+                }
+                st.q[h][2 * i] = t.x * qscale;
+                st.q[h][2 * i + 1] = t.y * qscale;
+            }
+        }
+
+        // new token: rotate k, stage k/v in shared memory, write the cache row
+        if (owns_new && warp == 0 && lane < 16) {
+            const T* kn = static_cast<const T*>(p.k_new.ptr) + b * p.k_new.sb + kvh * p.k_new.sh + l16 * 8;
+            const T* vn = static_cast<const T*>(p.v_new.ptr) + b * p.v_new.sb + kvh * p.v_new.sh + l16 * 8;
+            uint4 kraw = *reinterpret_cast<const uint4*>(kn);
+            uint4 vraw = *reinterpret_cast<const uint4*>(vn);
+            if (p.rope) {
+                uint32_t* u = &kraw.x;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float2 t = Elem<T>::unpack2(u[i]);
+                    float t1 = __fmul_rn(t.x, cs[i]), t2 = __fmul_rn(t.y, sn[i]);
+                    float t3 = __fmul_rn(t.x, sn[i]), t4 = __fmul_rn(t.y, cs[i]);
+                    u[i] = Elem<T>::pack2(__fsub_rn(t1, t2), __fadd_rn(t3, t4));
+                }
+            }
+            *reinterpret_cast<uint4*>(newkv + l16 * 8) = kraw;
+            *reinterpret_cast<uint4*>(newkv + 128 + l16 * 8) = vraw;
+            T* kdst = const_cast<T*>(kc) + static_cast<long long>(len) * D + l16 * 8;
+            T* vdst = const_cast<T*>(vc) + static_cast<long long>(len) * D + l16 * 8;
+            *reinterpret_cast<uint4*>(kdst) = kraw;
+            *reinterpret_cast<uint4*>(vdst) = vraw;
+        }
+
+        const int group = warp * 2 + (lane >> 4);
+        float* pbuf = pbuf_all + group * 16;
+        bool ok = true;
+        for (int t = 0; t < ntiles && ok; ++t) {
+            int s = t % kStages;
+            ok = mbar_wait(&sm->full[s], (t / kStages) & 1, abort_flag, 0x20);
+            if (!ok) break;
+            const T* ksm = ring + static_cast<size_t>(s) * (kStageBytes / sizeof(T));
+            const T* vsm = ksm + kTile * D;
+            int nk = min(kTile, k_end - (k_begin + t * kTile));
+            process_rows<T, NREP>(st, ksm, vsm, nk, warp, kConsumerWarps, lane, pbuf);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->empty[s]);
+        }
+        if (owns_new && warp == 0) {
+            __syncwarp();
+            // one extra key: lands in half-warp 0's slot, half-warp 1 sees only masked rows
+            process_rows<T, NREP>(st, newkv, newkv + 128, 1, 0, 1, lane, pbuf);
+        }
+
+        // ---- merge the 8 groups of the CTA through shared memory (ring is free now) ----
+        float l = st.l;
+#pragma unroll
+        for (int off = NREP; off < 16; off <<= 1) l += __shfl_xor_sync(0xFFFFFFFFu, l, off);
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");   // all consumers done with the ring
+        float* go = reinterpret_cast<float*>(smem_raw);                             // [8][NREP][128]
+        float* gm = go + 8 * NREP * 128;                                            // [8][NREP]
+        float* gl = gm + 8 * NREP;                                                  // [8][NREP]
+        if (l16 < NREP) { gm[group * NREP + l16] = st.m; gl[group * NREP + l16] = l; }
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            float4* dst = reinterpret_cast<float4*>(go + (group * NREP + h) * 128 + l16 * 8);
+            dst[0] = make_float4(st.o[h][0], st.o[h][1], st.o[h][2], st.o[h][3]);
+            dst[1] = make_float4(st.o[h][4], st.o[h][5], st.o[h][6], st.o[h][7]);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+
+        // thread d (0..127) finishes dim d of every head
+        const int d = tid;
+        float* wsp = p.workspace + p.ws_header;   // after the per-sequence length slots
+        const int nsplits = p.num_splits;
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            float M = -INFINITY;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) M = fmaxf(M, gm[g * NREP + h]);
+            float L = 0.f, acc = 0.f;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                float mg = gm[g * NREP + h];
+                float w = (mg == -INFINITY) ? 0.f : fast_exp2(mg - M);
+                L += gl[g * NREP + h] * w;
+                acc += go[(g * NREP + h) * 128 + d] * w;
+            }
+            float* out = wsp + ((static_cast<long long>(b) * p.Hkv + kvh) * nsplits + split) * NREP * (D + 2) + h * (D + 2);
+            out[d] = acc / L;
+            if (d == 0) { out[D] = M * kLn2; out[D + 1] = L; }
+        }
+    }
+}
+
+// One block per (q_head, batch): merge the valid splits.
+template <typename T>
+__global__ void decode_combine_kernel(DecodeParams p) {
+    constexpr int D = 128;
+    const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const int nrep = p.Hq / p.Hkv, kvh = hq / nrep, h = hq % nrep;
+    const int len = reinterpret_cast<const int*>(p.workspace)[b];
+    const int total = len + (p.append ? 1 : 0);
+    const int nsp = (total + p.chunk - 1) / p.chunk;
+    const float* base = p.workspace + p.ws_header +
+                        ((static_cast<long long>(b) * p.Hkv + kvh) * p.num_splits) * nrep * (D + 2) + h * (D + 2);
+    const long long sstride = static_cast<long long>(nrep) * (D + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < nsp; ++s) M = fmaxf(M, base[s * sstride + D]);
+    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < nsp; ++s) {
+        float w = expf(base[s * sstride + D] - M) * base[s * sstride + D + 1];
+        L += w;
+        acc += w * base[s * sstride + d];
+    }
+    float o = (nsp > 0) ? acc / L : 0.f;
+    if (p.partial_out) {
+        float* po = p.partial_out + (static_cast<long long>(b) * p.Hq + hq) * (D + 2);
+        po[d] = o;
+        if (d == 0) { po[D] = M; po[D + 1] = L; }
+    } else {
+        T* og = static_cast<T*>(p.o.ptr) + b * p.o.sb + hq * p.o.sh;
+        og[d] = Elem<T>::from_f(o);
+        if (p.lse && d == 0) p.lse[static_cast<long long>(b) * p.Hq + hq] = M + logf(L);
+    }
+    if (hq == 0 && d == 0 && p.seq_lens && p.append && p.advance_lens) p.seq_lens[b] = len + 1;
+}
+
+// partials [R, rows, D+2] -> out [rows, D], lse [rows]
+template <typename T>
+__global__ void lse_combine_kernel(const float* __restrict__ partials, int R, long long rows, int D,
+                                   T* __restrict__ out, float* __restrict__ lse) {
+    long long row = blockIdx.x;
+    int d = threadIdx.x;
+    const long long rstride = rows * (D + 2);
+    const float* base = partials + row * (D + 2);
+    float M = -INFINITY;
+    for (int r = 0; r < R; ++r) M = fmaxf(M, base[r * rstride + D]);
+    float L = 0.f, acc = 0.f;
+    for (int r = 0; r < R; ++r) {
+        float mr = base[r * rstride + D];
+        float w = (mr == -INFINITY) ? 0.f : expf(mr - M) * base[r * rstride + D + 1];
+        L += w;
+        if (d < D) acc += w * base[r * rstride + d];
+    }
+    if (d < D) out[row * D + d] = Elem<T>::from_f(acc / L);
+    if (lse && d == 0) lse[row] = M + logf(L);
+}
+
+template <typename T, int NREP>
+int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
+    constexpr int D = 128;
+    size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + 2 * D * sizeof(T) + 8 * 16 * sizeof(float) + sizeof(DecodeSmem);
+    static_assert(8 * NREP * 128 * 4 + 2 * 8 * NREP * 4 <= kStages * 2 * kTile * 128 * 2, "merge buffers must fit in the ring");
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    VB200_CUDA_TRY(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        configured_dev = dev;
+    }
+    dim3 grid(p.num_splits, p.Hkv, p.B);
+    decode_splitkv_kernel<T, NREP><<<grid, kThreads, smem, s>>>(p);
+    note_launch();
+    VB200_CUDA_TRY(cudaPeekAtLastError());
+    decode_combine_kernel<T><<<dim3(p.Hq, p.B), D, 0, s>>>(p);
+    note_launch();
+    VB200_CUDA_TRY(cudaPeekAtLastError());
+    return VB200_OK;
+}
+
+template <typename T>
+int launch_decode_nrep(cudaStream_t s, const DecodeParams& p) {
+    switch (p.Hq / p.Hkv) {
+        case 1: return launch_decode_t<T, 1>(s, p);
+        case 2: return launch_decode_t<T, 2>(s, p);
+        case 4: return launch_decode_t<T, 4>(s, p);
+        case 8: return launch_decode_t<T, 8>(s, p);
+        default: return set_detail(VB200_ERR_UNSUPPORTED, "decode supports Hq/Hkv in {1,2,4,8}");
+    }
+}
+
+}  // namespace
+
+int decode_tile_keys() { return kTile; }
+
+int launch_decode(cudaStream_t s, const DecodeParams& p) {
+    if (p.D != 128) return set_detail(VB200_ERR_UNSUPPORTED, "split-KV decode supports head_dim 128");
+    if (p.dtype == VB200_BF16) return launch_decode_nrep<__nv_bfloat16>(s, p);
+    if (p.dtype == VB200_F16) return launch_decode_nrep<__half>(s, p);
+    return set_detail(VB200_ERR_UNSUPPORTED, "split-KV decode supports bf16 and fp16 caches");
+}
+
+int launch_lse_combine(cudaStream_t s, const float* partials, int R, long long rows, int D,
+                       int dtype, void* out, float* lse) {
+    if (rows <= 0) return VB200_OK;
+    if (D > 1024) return VB200_ERR_UNSUPPORTED;
+    int threads = ((D + 31) / 32) * 32;
+    unsigned grid = static_cast<unsigned>(rows);
+    switch (dtype) {
+        case VB200_BF16: lse_combine_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(partials, R, rows, D, static_cast<__nv_bfloat16*>(out), lse); break;
+        case VB200_F16: lse_combine_kernel<__half><<<grid, threads, 0, s>>>(partials, R, rows, D, static_cast<__half*>(out), lse); break;
+        default: return VB200_ERR_UNSUPPORTED;
+    }
+    note_launch();
+    VB200_CUDA_TRY(cudaPeekAtLastError());
+    return VB200_OK;
+}
+
+}  // namespace vb200

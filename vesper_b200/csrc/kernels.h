@@ -1,0 +1,79 @@
+// Internal launch interfaces between api.cu and the kernel translation units.
+#pragma once
+
+#include "common.cuh"
+
+namespace vb200 {
+
+constexpr int kMaxHalfDim = 64;   // head_dim <= 128
+
+struct InvFreq {
+    float v[kMaxHalfDim];
+};
+
+// A strided [B,H,S,D] view in elements.
+struct View4 {
+    void* ptr;
+    long long sb, sh, ss;
+};
+inline View4 to_view(const vb200_tensor4& t) { return View4{t.ptr, t.stride_b, t.stride_h, t.stride_s}; }
+
+// ---- rope_append.cu ----
+// table[t][i] = (cos, sin)(float(start_pos + t) * inv_freq[i]),  t < T, i < D/2
+int launch_rope_table(cudaStream_t s, float2* table, int T, int D, int start_pos, const InvFreq& f);
+// dst rows [dst_row0, dst_row0+T) of k_dst/v_dst <- rotate(k) / v.  table == nullptr: no rotation.
+// v / v_dst may be null (K only).
+// inv_freq != nullptr (with table == nullptr): angles computed in the kernel for positions dst_row0 + t.
+int launch_kv_append(cudaStream_t s, int dtype, int B, int H, int T, int D,
+                     View4 k, View4 v, View4 k_dst, View4 v_dst, int dst_row0, const float2* table,
+                     const InvFreq* inv_freq = nullptr);
+int launch_apply_rope_f32(cudaStream_t s, float* x, const float* cos_t, const float* sin_t,
+                          int batch, int heads, int seq_len, int head_dim);
+int launch_repeat_kv(cudaStream_t s, int dtype, View4 in, void* out, int B, int Hkv, int S, int D, int n_rep);
+
+// ---- prefill_f32.cu / prefill_sm100.cu ----
+struct PrefillParams {
+    int dtype;
+    int B, Hq, Hkv, T, D;
+    int Skv;            // number of keys = start_pos + T
+    int start_pos;      // causal offset: key j visible to query i iff j <= start_pos + i
+    int causal;
+    float scale;
+    View4 q, k, v, o;   // k, v: the tensors attention reads (cache or inputs), [B,Hkv,>=Skv,D]
+    float* lse;         // [B,Hq,T] or null
+    const float2* q_rope_table;   // [T, D/2] (cos,sin) for the query rows, or null
+    int* status;                  // device status word (bounded waits)
+};
+int launch_prefill_f32(cudaStream_t s, const PrefillParams& p);
+int launch_prefill_sm100(cudaStream_t s, const PrefillParams& p);
+
+// ---- decode_splitkv.cu ----
+struct DecodeParams {
+    int dtype;
+    int B, Hq, Hkv, D;
+    float scale;
+    View4 q, k_new, v_new, o;
+    float* lse;
+    View4 k_cache, v_cache;
+    int cache_cap;
+    int* seq_lens;
+    int uniform_len;
+    int advance_lens;
+    int append;          // 1: k_new/v_new are appended at row len and attended to
+    int rope;
+    InvFreq inv_freq;
+    long long pos_offset;
+    int num_splits;      // resolved (>= 1)
+    int chunk;           // keys per split (multiple of the kernel's tile)
+    float* partial_out;  // null or [B,Hq,D+2]
+    const int* q_positions;  // device int32[B]: absolute position of the query, or null (= pos_offset + len)
+    float* workspace;    // ws_header ints (length used per sequence), then [B,Hkv,num_splits,n_rep,D+2]
+    int ws_header;       // floats reserved at the front of the workspace (multiple of 64)
+    int* status;         // device status word (bounded waits)
+};
+int decode_tile_keys();
+int launch_decode(cudaStream_t s, const DecodeParams& p);
+int launch_lse_combine(cudaStream_t s, const float* partials, int R, long long rows, int D,
+                       int dtype, void* out, float* lse);
+
+}  // namespace vb200
