@@ -1,0 +1,436 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one synthetic batch:
+  * headline workload (N=1): GQA causal prefill in bf16 -- B=4, Hq=32, Hkv=8, S=2048,
+    head_dim 128, RoPE theta 1e4 applied to Q and K, K/V appended into an empty cache of
+    capacity 4096 -- one call of vb200_prefill_fwd.  metric = attention TFLOP/s,
+    FLOPs = 4*B*Hq*D*S*(S+1)/2 (QK^T and PV over the causal triangle only).
+  * also reported in the same line: batched GQA decode (B=32, Hq=32, Hkv=8, D=128, ragged
+    contexts U[1024,8192], 256 consecutive steps) as KV-read GB/s, and -- at N>1 -- the
+    sequence-sharded long-context decode (131072 keys split over the GPUs, one all-gather).
+  * N>1: prefill and batched decode partition by (batch x kv_head) with no collective, so
+    every rank runs the same per-GPU workload on its own units (weak scaling).
+
+Timing: CUDA events on the launching stream; each timed step has its own event pair and
+L2 is flushed (256 MiB write) between steps; max over ranks.  A clock/throttle record is
+sampled with nvidia-smi during the timed region.
+
+--impl reference times the reference's own CPU attention (oracle/_ref when it was built,
+else the plain-C port) on a bounded sample of the same workload, on all host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# headline workload (the configuration the metric is quoted on)
+C2 = dict(B=4, Hq=32, Hkv=8, S=2048, D=128, cap=4096, theta=10000.0)
+C3 = dict(B=32, Hq=32, Hkv=8, D=128, lo=1024, hi=8192, steps=256)
+C4 = dict(B=1, Hq=64, Hkv=8, D=128, L=131072)
+
+
+def prefill_flops(c):
+    return 4.0 * c["B"] * c["Hq"] * c["D"] * c["S"] * (c["S"] + 1) / 2.0
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=float(d["hbm_gbs"]), tf=float(d["bf16_tflops"]), tf_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(hbm=6650.0, tf=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+def load_traffic():
+    """DRAM bytes per launch of the dominant kernels, from the committed ncu summaries."""
+    p = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    return json.load(open(p)) if os.path.exists(p) else {}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        mhz, mx, reasons = [], None, set()
+        for ts, line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9 or not (t0 - 0.05 <= ts <= t1 + 0.15):
+                continue
+            try:
+                mhz.append(float(f[1])); mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the reference's own CPU attention on a bounded sample, all host threads
+# ----------------------------------------------------------------------------------------------
+def cpu_prefill_sample(target_seconds=12.0, threads=None):
+    """Time flash_attention_cpu_dispatch (src/ops/flash_attention.cpp:218-364) on (batch, head)
+    slices of the headline workload (S=2048, D=128, causal; RoPE applied to the slice first with
+    the reference's functions), independent slices on `threads` host threads.  Returns TFLOP/s."""
+    import numpy as np
+    from oracle.binding import Oracle, Ref, ref_available
+    kind = "reference" if ref_available() else "port"
+    eng = Ref() if kind == "reference" else Oracle()
+    threads = threads or max(1, min(os.cpu_count() or 1, 64))
+    S, D = C2["S"], C2["D"]
+    rng = np.random.default_rng(1)
+    q = (0.5 * rng.standard_normal((1, 1, S, D))).astype(np.float32)
+    k = (0.5 * rng.standard_normal((1, 1, S, D))).astype(np.float32)
+    v = (0.5 * rng.standard_normal((1, 1, S, D))).astype(np.float32)
+    scale = float(1.0 / np.sqrt(D))
+
+    def one_slice():
+        qr = eng.apply_rope(q, 0, C2["theta"])
+        kr = eng.apply_rope(k, 0, C2["theta"])
+        eng.flash_attention(qr, kr, v, scale, True)
+
+    t0 = time.time(); one_slice(); t_one = time.time() - t0          # calibrate (single thread)
+    per_thread = max(1, int(target_seconds / max(t_one, 1e-3)))
+    per_thread = min(per_thread, 64)
+    done = [0] * threads
+
+    def work(i):
+        for _ in range(per_thread):
+            one_slice()
+            done[i] += 1
+
+    ths = [threading.Thread(target=work, args=(i,)) for i in range(threads)]
+    t0 = time.time()
+    for t in ths: t.start()
+    for t in ths: t.join()
+    dt = time.time() - t0
+    slices = sum(done)
+    flops = slices * 4.0 * D * S * (S + 1) / 2.0
+    return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=threads, kind=kind,
+                sample=f"{slices} of {C2['B'] * C2['Hq']} (batch, head) slices of the headline prefill (S={S}, D={D}, fp32, RoPE + causal flash), "
+                       f"{threads} host threads x {per_thread} slices, {dt:.1f} s; single-thread slice {t_one * 1e3:.0f} ms"), dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb, dt = cpu_prefill_sample(target_seconds=10.0)
+    steps = max(1, args.steps)
+    line = {
+        "impl": "reference", "metric": "prefill attn TFLOP/s & decode KV-read GB/s vs B200 roofline",
+        "value": cb["value"], "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": dt * 1e3 / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "GQA causal prefill B=4 Hq=32 Hkv=8 S=2048 D=128, RoPE theta 1e4 (reference CPU code, bounded sample)"},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from vesper_b200 import capi
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    capi.load()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    peaks = load_peaks()
+    traffic = load_traffic()
+    K, W = max(1, args.steps), max(3, args.warmup)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def flush_l2():
+        flush_buf.fill_(1)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ------------------------------------------------------------------ prefill (headline)
+    c = C2
+    B, Hq, Hkv, S, D = c["B"], c["Hq"], c["Hkv"], c["S"], c["D"]
+    g = torch.Generator(device="cpu").manual_seed(1 + rank)
+    hq = (0.5 * torch.randn(B, Hq, S, D, generator=g)).to(torch.bfloat16).pin_memory()
+    hk = (0.5 * torch.randn(B, Hkv, S, D, generator=g)).to(torch.bfloat16).pin_memory()
+    hv = (0.5 * torch.randn(B, Hkv, S, D, generator=g)).to(torch.bfloat16).pin_memory()
+    ho = torch.empty(B, Hq, S, D, dtype=torch.bfloat16).pin_memory()
+    hl = torch.empty(B, Hq, S, dtype=torch.float32).pin_memory()
+    q, k, v = hq.to(dev), hk.to(dev), hv.to(dev)
+    o = torch.empty_like(q)
+    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=dev)
+    kc = torch.zeros(B, Hkv, c["cap"], D, dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    scale = float(1.0 / np.sqrt(D))
+    a = capi.prefill_args(q, k, v, o, lse, scale=scale, causal=True, theta=c["theta"], k_cache=kc, v_cache=vc)
+    import ctypes as C
+    L = capi.load()
+    ws = torch.empty(max(256, L.vb200_prefill_workspace_bytes(C.byref(a))), dtype=torch.uint8, device=dev)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+
+    def prefill_step():
+        capi.check(L.vb200_prefill_fwd(C.byref(a)))
+
+    for _ in range(W):
+        prefill_step()
+    sync_all()
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.25)
+    L.vb200_reset_launch_count()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    sync_all()
+    t_wall0 = time.time()
+    for i in range(K):
+        flush_l2()
+        evs[i][0].record()
+        prefill_step()
+        evs[i][1].record()
+    sync_all()
+    t_wall1 = time.time()
+    launches = int(L.vb200_launch_count())
+    step_ms = [s.elapsed_time(e) for s, e in evs]
+    # separate pass for the dominant kernel's own duration (event brackets inside the library
+    # serialise consecutive calls, so they stay out of the whole-job timing above)
+    capi.profile_enable(True)
+    for _ in range(min(K, 10)):
+        flush_l2()
+        prefill_step()
+    torch.cuda.synchronize()
+    kern_ms, kern_n = capi.profile_read()
+    capi.profile_enable(False)
+    total_ms = max_over_ranks(sum(step_ms))
+    ms_per_step = total_ms / K
+    flops = prefill_flops(c)
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    kern_avg_ms = kern_ms / max(1, kern_n)
+    achieved_tf = flops / (kern_avg_ms * 1e-3) / 1e12
+
+    # ------------------------------------------------------------------ prefill end to end (host buffers)
+    def e2e_step():
+        q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True); v.copy_(hv, non_blocking=True)
+        prefill_step()
+        ho.copy_(o, non_blocking=True); hl.copy_(lse, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    Ke = min(K, 10)
+    e0.record()
+    for _ in range(Ke):
+        e2e_step()
+    e1.record()
+    sync_all()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / Ke
+    e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
+    h2d = (hq.numel() + hk.numel() + hv.numel()) * 2
+    d2h = ho.numel() * 2 + hl.numel() * 4
+    capi.check_kernel_status(local)
+    del hq, hk, hv, ho, hl, q, k, v, o, lse, kc, vc
+
+    # ------------------------------------------------------------------ batched ragged decode
+    d = C3
+    B, Hq, Hkv, D = d["B"], d["Hq"], d["Hkv"], d["D"]
+    rs = np.random.RandomState(2)
+    lens0 = rs.randint(d["lo"], d["hi"] + 1, size=B).astype(np.int32)
+    nsteps = d["steps"]
+    nprof = 32
+    cap = d["hi"] + nsteps + nprof + W + 8
+    gd = torch.Generator(device=dev).manual_seed(3 + rank)
+    kc = torch.randn(B, Hkv, cap, D, generator=gd, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn(B, Hkv, cap, D, generator=gd, device=dev, dtype=torch.bfloat16)
+    q1 = torch.randn(B, Hq, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
+    k1 = torch.randn(B, Hkv, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
+    v1 = torch.randn(B, Hkv, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
+    o1 = torch.empty_like(q1)
+    seq = torch.from_numpy(lens0).to(dev)
+    da = capi.decode_args(q1, o1, kc, vc, scale=scale, k_new=k1, v_new=v1, theta=10000.0, seq_lens=seq,
+                          advance_lens=True, max_len=int(lens0.max()) + nsteps + nprof + W + 1)
+    dws = torch.empty(L.vb200_decode_workspace_bytes(C.byref(da)), dtype=torch.uint8, device=dev)
+    da.workspace, da.workspace_bytes = dws.data_ptr(), dws.numel()
+    for _ in range(W):
+        capi.check(L.vb200_decode_fwd(C.byref(da)))
+    sync_all()
+    lens_start = lens0.astype(np.int64) + W
+    L.vb200_reset_launch_count()
+    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    d0.record()
+    for _ in range(nsteps):
+        capi.check(L.vb200_decode_fwd(C.byref(da)))
+    d1.record()
+    sync_all()
+    dec_launches = int(L.vb200_launch_count())
+    dec_ms = max_over_ranks(d0.elapsed_time(d1))
+    # K and V rows read once per KV head, including the token appended in the step
+    step_bytes = lambda t: float(np.sum(2 * Hkv * (lens_start + t + 1) * D * 2))
+    dec_bytes = sum(step_bytes(t) for t in range(nsteps))
+    dec_gbs = world * dec_bytes / (dec_ms * 1e-3) / 1e9
+    capi.profile_enable(True)          # kernel-only pass over the next nprof steps
+    for _ in range(nprof):
+        capi.check(L.vb200_decode_fwd(C.byref(da)))
+    torch.cuda.synchronize()
+    dkern_ms, dkern_n = capi.profile_read()
+    capi.profile_enable(False)
+    prof_bytes = sum(step_bytes(t) for t in range(nsteps, nsteps + nprof))
+    dec_kernel_gbs = prof_bytes / (dkern_ms * 1e-3) / 1e9 if dkern_ms > 0 else None
+    capi.check_kernel_status(local)
+    assert seq.cpu().numpy().tolist() == (lens0 + W + nsteps + nprof).tolist()
+    decode = {
+        "metric": "decode KV-read GB/s", "value": dec_gbs, "unit": "GB/s", "ms_per_step": dec_ms / nsteps, "steps": nsteps,
+        "config": {"workload": f"batched GQA decode B={B} Hq={Hq} Hkv={Hkv} D={D} bf16 cache, ragged contexts U[{d['lo']},{d['hi']}] (seed 2), "
+                               f"{nsteps} consecutive steps each appending one token; inputs larger than L2 ({dec_bytes / nsteps / 1e6:.0f} MB/step)"},
+        "gpu_launches": dec_launches,
+        "roofline": {"bound": "hbm", "achieved": dec_kernel_gbs, "peak": peaks["hbm"], "unit": "GB/s",
+                     "frac": (dec_kernel_gbs / peaks["hbm"]) if dec_kernel_gbs else None, "peak_source": peaks["source"],
+                     "frac_of_nominal_8TBs": (dec_kernel_gbs / 8000.0) if dec_kernel_gbs else None,
+                     "traffic": traffic.get("decode_splitkv_bytes_per_launch")},
+    }
+    del kc, vc, dws
+
+    # ------------------------------------------------------------------ sequence-sharded long-context decode
+    from vesper_b200.sharded import ShardedDecodeStep, cuda_step, shard_range
+    s4 = C4
+    Bq, Hq4, Hkv4, L4 = s4["B"], s4["Hq"], s4["Hkv"], s4["L"]
+    begin, end = shard_range(L4, world, rank)
+    g4 = torch.Generator(device=dev).manual_seed(5)
+    ks = torch.randn(Bq, Hkv4, end - begin, D, generator=g4, device=dev, dtype=torch.bfloat16)
+    vs = torch.randn(Bq, Hkv4, end - begin, D, generator=g4, device=dev, dtype=torch.bfloat16)
+    q4 = torch.randn(Bq, Hq4, 1, D, generator=torch.Generator(device=dev).manual_seed(6), device=dev, dtype=torch.bfloat16)
+    part = torch.empty(Bq * Hq4, D + 2, dtype=torch.float32, device=dev)
+    gath = torch.empty(world, Bq * Hq4, D + 2, dtype=torch.float32, device=dev)
+    out4 = torch.empty(Bq * Hq4, D, dtype=torch.bfloat16, device=dev)
+    step4 = ShardedDecodeStep(world, rank, L4)
+    ws4 = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    n4 = 50
+    for _ in range(5):
+        cuda_step(step4, q4, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out4, gathered=gath, workspace=ws4, dist=dist if world > 1 else None)
+    sync_all()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(n4):
+        cuda_step(step4, q4, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out4, gathered=gath, workspace=ws4, dist=dist if world > 1 else None)
+    s1.record()
+    sync_all()
+    sh_ms = max_over_ranks(s0.elapsed_time(s1)) / n4
+    sh_bytes = 2.0 * Hkv4 * L4 * D * 2
+    capi.check_kernel_status(local)
+    sharded = {
+        "metric": "long-context decode KV-read GB/s (aggregate)", "value": sh_bytes / (sh_ms * 1e-3) / 1e9, "unit": "GB/s",
+        "ms_per_step": sh_ms, "scaling": "strong",
+        "config": {"workload": f"split-KV decode B=1 Hq={Hq4} Hkv={Hkv4} D={D} bf16, context {L4} sharded over {world} GPU(s); "
+                               f"partial (O/l, m, l) all-gather of {Hq4 * (D + 2) * 4} B per rank, then LSE combine"},
+        "roofline": {"bound": "hbm", "achieved": sh_bytes / world / (sh_ms * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s per GPU",
+                     "frac": sh_bytes / world / (sh_ms * 1e-3) / 1e9 / peaks["hbm"], "peak_source": peaks["source"]},
+    }
+
+    clocks = sampler.stop(t_wall0, t_wall1)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_baseline, _ = cpu_prefill_sample(target_seconds=12.0)
+
+    if rank == 0:
+        line = {
+            "metric": "prefill attn TFLOP/s & decode KV-read GB/s vs B200 roofline",
+            "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"GQA causal prefill B={C2['B']} Hq={C2['Hq']} Hkv={C2['Hkv']} S={C2['S']} D={C2['D']} bf16 (fp32 accumulate), "
+                                   f"RoPE theta 1e4 on Q and K, K/V appended into an empty cache of capacity {C2['cap']}; per GPU, units (batch x kv_head) "
+                                   "partitioned with no collective",
+                       "l2": "256 MiB flush write between timed steps", "flops": "4*B*Hq*D*S*(S+1)/2"},
+            "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peaks["tf"], "unit": "TFLOP/s",
+                         "frac": achieved_tf / peaks["tf"], "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                         "frac_of_sustained": achieved_tf / peaks["tf_sustained"], "frac_of_nominal_2250": achieved_tf / 2250.0,
+                         "kernel": "prefill_sm100_kernel", "kernel_ms": kern_avg_ms,
+                         "traffic": traffic.get("prefill_sm100_bytes_per_launch")},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "decode": decode,
+            "decode_sharded": sharded,
+        }
+        if cpu_baseline is not None:
+            line["cpu_baseline"] = cpu_baseline
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -200,6 +200,16 @@ int vb200_abi_version(void);
  * the last reset (used by the benchmark's launch count). */
 uint64_t vb200_launch_count(void);
 void vb200_reset_launch_count(void);
+/* Optional timing of the dominant kernel of each call (the attention kernel of
+ * vb200_prefill_fwd, the split-KV kernel of vb200_decode_fwd), for roofline
+ * reports: while enabled, the launch is bracketed by two CUDA events on the
+ * caller's stream; vb200_profile_read returns the summed kernel time and the
+ * number of brackets since the last enable (it waits for the last one).
+ * Per calling thread.  Because a bracket is folded in when the next one starts,
+ * enabling this makes consecutive calls wait for each other's kernels: do not
+ * leave it on in production. */
+int vb200_profile_enable(int enable);
+int vb200_profile_read(double* total_ms, uint64_t* launches);
 /* Reads and clears the device-side status word that bounded waits set
  * (synchronises the given stream).  Returns VB200_OK or VB200_ERR_KERNEL_TIMEOUT. */
 int vb200_check_kernel_status(int device, void* stream);

@@ -1,0 +1,54 @@
+"""The C-ABI library loads and exports every symbol include/vesper_b200.h declares
+(no compute calls: this runs without a GPU)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "vesper_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(vb200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib):
+    from vesper_b200 import capi
+    names = declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/vesper_b200.h but not exported"
+    assert sorted(capi.EXPORTS) == names
+
+
+def test_struct_layout_and_host_helpers(lib):
+    from vesper_b200 import capi
+    assert lib.vb200_abi_version() == 1
+    assert lib.vb200_strerror(0) == b"ok" and b"workspace" in lib.vb200_strerror(-4)
+    # a struct_size mismatch is rejected before anything touches a device
+    a = capi.PrefillArgs()
+    a.struct_size = 4
+    assert lib.vb200_prefill_fwd(C.byref(a)) == -1
+    assert lib.vb200_prefill_workspace_bytes(C.byref(a)) == 0
+    d = capi.DecodeArgs()
+    assert lib.vb200_decode_fwd(C.byref(d)) == -1
+    # inv_freq is the reference's fp32 expression pow(theta, -2i/D) (src/nn/functional.cpp:433)
+    f = capi.inv_freq(10000.0, 128)
+    from oracle.binding import Oracle
+    want = Oracle().rope_frequencies(2, 128, 1, 10000.0)[0]     # position 1 -> angle == inv_freq
+    assert np.array_equal(np.array(list(f), np.float32), want)
+
+
+def test_decode_workspace_plan_is_consistent(lib):
+    from vesper_b200 import capi
+    d = capi.DecodeArgs()
+    d.struct_size = C.sizeof(capi.DecodeArgs)
+    d.B, d.Hq, d.Hkv, d.D, d.cache_cap, d.max_len = 32, 32, 8, 128, 8448, 8193
+    n = lib.vb200_decode_workspace_bytes(C.byref(d))
+    # [B,Hkv,splits,n_rep,D+2] fp32 with 512-key splits -> 17 splits
+    assert n >= 32 * 8 * 17 * 4 * 130 * 4 and n % 256 == 0
+    d.num_splits = 1
+    assert lib.vb200_decode_workspace_bytes(C.byref(d)) < n

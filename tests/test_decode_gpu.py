@@ -1,0 +1,161 @@
+"""Parity of the split-KV decode path (through the C ABI) with the CPU oracle.
+
+Decode oracle: the reference's standard attention path applied per sequence on
+contiguous fp32 copies of the cache (src/nn/functional.cpp:399-421), RoPE and
+cache update as in src/nn/gqa_attention.cpp:124-137.  Gates: bf16 max-abs <= 1e-2,
+fp16 <= 2e-3, LSE <= 1e-3.
+"""
+import numpy as np
+import pytest
+
+from helpers import bf16_round, fp16_round, from_torch, maxabs, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def make_cache(rng, B, Hkv, cap, D, lens, rnd):
+    k = np.zeros((B, Hkv, cap, D), np.float32)
+    v = np.zeros_like(k)
+    for b, L in enumerate(lens):
+        k[b, :, :L] = rnd(rng.standard_normal((Hkv, L, D), dtype=np.float32))
+        v[b, :, :L] = rnd(rng.standard_normal((Hkv, L, D), dtype=np.float32))
+    return k, v
+
+
+@pytest.mark.parametrize("n_rep", [1, 2, 4, 8])
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_decode_uniform_no_append(lib, cuda, oracle, n_rep, dt):
+    import torch
+    from vesper_b200 import capi
+    B, Hkv, D, L, cap = 2, 2, 128, 300, 320
+    Hq = Hkv * n_rep
+    rnd = bf16_round if dt == "bf16" else fp16_round
+    tdt = torch.bfloat16 if dt == "bf16" else torch.float16
+    rng = np.random.default_rng(40 + n_rep)
+    k, v = make_cache(rng, B, Hkv, cap, D, [L] * B, rnd)
+    q = rnd(rng.standard_normal((B, Hq, 1, D), dtype=np.float32))
+    tq, tk, tv = to_torch(q, tdt, cuda), to_torch(k, tdt, cuda), to_torch(v, tdt, cuda)
+    o = torch.empty_like(tq)
+    lse = torch.empty(B, Hq, dtype=torch.float32, device=cuda)
+    scale = float(1.0 / np.sqrt(D))
+    capi.decode(tq, o, tk, tv, scale=scale, lse=lse, uniform_len=L, max_len=L)
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)
+    want_o, want_lse = oracle.decode_ragged(q[:, :, 0], k, v, [L] * B)
+    assert maxabs(from_torch(o)[:, :, 0], want_o) <= (1e-2 if dt == "bf16" else 2e-3)
+    assert maxabs(from_torch(lse), want_lse) <= 1e-3
+
+
+@pytest.mark.parametrize("num_splits", [0, 1, 3, 11])
+def test_decode_ragged_rope_append_steps(lib, cuda, oracle, num_splits):
+    """Ragged lengths (incl. 1 and tile multiples), RoPE at position len, append, attend; three
+    consecutive steps with the kernel advancing seq_lens on the device."""
+    import torch
+    from vesper_b200 import capi
+    B, Hq, Hkv, D, cap = 5, 8, 2, 128, 800
+    lens = [1, 63, 64, 700, 512]
+    rng = np.random.default_rng(50)
+    k, v = make_cache(rng, B, Hkv, cap, D, lens, bf16_round)
+    tk, tv = to_torch(k, torch.bfloat16, cuda), to_torch(v, torch.bfloat16, cuda)
+    seq = torch.tensor(lens, dtype=torch.int32, device=cuda)
+    scale = float(1.0 / np.sqrt(D))
+    cur = list(lens)
+    for step in range(3):
+        q = bf16_round(rng.standard_normal((B, Hq, 1, D), dtype=np.float32))
+        kn = bf16_round(rng.standard_normal((B, Hkv, 1, D), dtype=np.float32))
+        vn = bf16_round(rng.standard_normal((B, Hkv, 1, D), dtype=np.float32))
+        tq, tkn, tvn = (to_torch(x, torch.bfloat16, cuda) for x in (q, kn, vn))
+        o = torch.empty_like(tq)
+        lse = torch.empty(B, Hq, dtype=torch.float32, device=cuda)
+        capi.decode(tq, o, tk, tv, scale=scale, k_new=tkn, v_new=tvn, lse=lse, theta=10000.0, seq_lens=seq,
+                    advance_lens=True, max_len=max(cur) + 1, num_splits=num_splits)
+        torch.cuda.synchronize()
+        capi.check_kernel_status(0)
+        for b in range(B):
+            kc1, vc1 = k[b:b + 1].copy(), v[b:b + 1].copy()
+            want_o, want_lse, n = oracle.gqa_attention_cached(q[b:b + 1], kn[b:b + 1], vn[b:b + 1], kc1, vc1, cur[b], cur[b])
+            k[b], v[b] = kc1[0], vc1[0]
+            assert n == cur[b] + 1
+            assert maxabs(from_torch(o)[b], want_o[0]) <= 1e-2, f"step {step} seq {b}"
+            assert maxabs(from_torch(lse)[b], want_lse[0, :, 0]) <= 1e-3
+            cur[b] += 1
+        assert seq.tolist() == cur
+        # the oracle cache keeps fp32 rotated K; the device cache holds its bf16 rounding: carry the device values on
+        k = from_torch(tk); v = from_torch(tv)
+    # appended rows: V exact, K within one bf16 rounding; nothing written past the new length
+    gk, gv = from_torch(tk), from_torch(tv)
+    for b in range(B):
+        assert not gk[b, :, cur[b]:].any() and not gv[b, :, cur[b]:].any()
+
+
+def test_decode_sharded_partials_combine(lib, cuda, oracle):
+    """Sequence-sharded form on one GPU: R shards of the KV sequence each emit (O/l, m, l);
+    vb200_lse_combine merges them to the unsharded result (the algebra of
+    src/ops/flash_attention.cpp:309-345 across shards)."""
+    import torch
+    from vesper_b200 import capi
+    B, Hq, Hkv, D, L, R = 1, 16, 2, 128, 4096, 4
+    rng = np.random.default_rng(60)
+    k, v = make_cache(rng, B, Hkv, L, D, [L], bf16_round)
+    q = bf16_round(rng.standard_normal((B, Hq, 1, D), dtype=np.float32))
+    scale = float(1.0 / np.sqrt(D))
+    # q is rotated at the absolute position L (no new token appended): oracle applies the same
+    q_rot = oracle.apply_rope(q, L, 10000.0)
+    want_o, want_lse = oracle.decode_ragged(q_rot[:, :, 0], k, v, [L])
+    tq = to_torch(q, torch.bfloat16, cuda)
+    partials = torch.empty(R, B * Hq, D + 2, dtype=torch.float32, device=cuda)
+    qpos = torch.tensor([L], dtype=torch.int32, device=cuda)
+    per = L // R
+    for r in range(R):
+        tk = to_torch(k[:, :, r * per:(r + 1) * per], torch.bfloat16, cuda)
+        tv = to_torch(v[:, :, r * per:(r + 1) * per], torch.bfloat16, cuda)
+        capi.decode(tq, None, tk, tv, scale=scale, theta=10000.0, uniform_len=per, max_len=per,
+                    pos_offset=r * per, q_positions=qpos, partial_out=partials[r])
+    out = torch.empty(B * Hq, D, dtype=torch.bfloat16, device=cuda)
+    lse = torch.empty(B * Hq, dtype=torch.float32, device=cuda)
+    capi.lse_combine(partials, out, lse)
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)
+    # q was rotated in bf16 storage by neither side: both rotate the same bf16 values in fp32
+    assert maxabs(from_torch(out), want_o[0]) <= 1e-2
+    assert maxabs(from_torch(lse), want_lse[0]) <= 1e-3
+
+
+def test_config3_full_size_one_step(lib, cuda, oracle):
+    """Batched GQA decode at the benchmark size: B=32, Hq=32, Hkv=8, D=128, ragged lengths
+    U[1024, 8192]; one step with RoPE + append.  Oracle parity on 4 sequences x all heads."""
+    import torch
+    from vesper_b200 import capi
+    B, Hq, Hkv, D = 32, 32, 8, 128
+    rs = np.random.RandomState(2)
+    lens = rs.randint(1024, 8193, size=B).astype(np.int32)
+    cap = 8192 + 256
+    g = torch.Generator(device="cuda").manual_seed(3)
+    tk = torch.randn(B, Hkv, cap, D, generator=g, device=cuda, dtype=torch.float32).to(torch.bfloat16)
+    tv = torch.randn(B, Hkv, cap, D, generator=g, device=cuda, dtype=torch.float32).to(torch.bfloat16)
+    for b in range(B):
+        tk[b, :, lens[b]:] = 0
+        tv[b, :, lens[b]:] = 0
+    tq = torch.randn(B, Hq, 1, D, generator=g, device=cuda).to(torch.bfloat16)
+    tkn = torch.randn(B, Hkv, 1, D, generator=g, device=cuda).to(torch.bfloat16)
+    tvn = torch.randn(B, Hkv, 1, D, generator=g, device=cuda).to(torch.bfloat16)
+    seq = torch.from_numpy(lens).to(cuda)
+    o = torch.empty_like(tq)
+    lse = torch.empty(B, Hq, dtype=torch.float32, device=cuda)
+    scale = float(1.0 / np.sqrt(D))
+    check = [0, 7, int(np.argmin(lens)), int(np.argmax(lens))]
+    before = {b: (from_torch(tk[b:b + 1]), from_torch(tv[b:b + 1])) for b in check}
+    capi.decode(tq, o, tk, tv, scale=scale, k_new=tkn, v_new=tvn, lse=lse, theta=10000.0, seq_lens=seq,
+                advance_lens=True, max_len=int(lens.max()) + 1)
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)
+    assert torch.isfinite(o.float()).all()
+    assert seq.tolist() == (lens + 1).tolist()
+    for b in check:
+        kc1, vc1 = before[b]
+        L = int(lens[b])
+        want_o, want_lse, _ = oracle.gqa_attention_cached(from_torch(tq[b:b + 1]), from_torch(tkn[b:b + 1]), from_torch(tvn[b:b + 1]),
+                                                          kc1, vc1, L, L)
+        assert maxabs(from_torch(o[b]), want_o[0]) <= 1e-2
+        assert maxabs(from_torch(lse[b]), want_lse[0, :, 0]) <= 1e-3
+        assert torch.equal(tv[b, :, L], tvn[b, :, 0])

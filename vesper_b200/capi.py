@@ -53,7 +53,7 @@ EXPORTS = [
     "vb200_prefill_workspace_bytes", "vb200_prefill_fwd", "vb200_decode_workspace_bytes", "vb200_decode_fwd",
     "vb200_lse_combine", "vb200_kv_append", "vb200_apply_rope", "vb200_repeat_kv", "vb200_rope_inv_freq",
     "vb200_strerror", "vb200_last_error_detail", "vb200_abi_version", "vb200_launch_count",
-    "vb200_reset_launch_count", "vb200_check_kernel_status",
+    "vb200_reset_launch_count", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
 ]
 
 _lib = None
@@ -91,6 +91,8 @@ def load():
     L.vb200_launch_count.restype = C.c_uint64
     L.vb200_reset_launch_count.restype = None
     L.vb200_check_kernel_status.argtypes = [C.c_int, C.c_void_p]
+    L.vb200_profile_enable.argtypes = [C.c_int]
+    L.vb200_profile_read.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
     _lib = L
     return L
 
@@ -225,3 +227,14 @@ def lse_combine(partials, out, lse=None, stream=None):
 
 def check_kernel_status(device=0, stream=None):
     check(load().vb200_check_kernel_status(device, _stream_ptr(stream)))
+
+
+def profile_enable(on=True):
+    check(load().vb200_profile_enable(int(on)))
+
+
+def profile_read():
+    """(summed dominant-kernel milliseconds, number of bracketed launches) since profile_enable(True)."""
+    ms, n = C.c_double(0.0), C.c_uint64(0)
+    check(load().vb200_profile_read(C.byref(ms), C.byref(n)))
+    return ms.value, n.value

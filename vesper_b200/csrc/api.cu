@@ -32,6 +32,40 @@ thread_local uint64_t t_launches = 0;
 
 void note_launch(int n) { t_launches += static_cast<uint64_t>(n); }
 
+namespace {
+struct ProfileState {
+    bool enabled = false;
+    int dev = -1;
+    cudaEvent_t ev[2] = {nullptr, nullptr};
+    double total_ms = 0.0;
+    uint64_t count = 0;
+    bool pending = false;
+};
+thread_local ProfileState t_prof;
+
+// fold the last bracket into the running total (waits for its end event)
+void profile_flush() {
+    if (!t_prof.pending) return;
+    float ms = 0.f;
+    if (cudaEventSynchronize(t_prof.ev[1]) == cudaSuccess && cudaEventElapsedTime(&ms, t_prof.ev[0], t_prof.ev[1]) == cudaSuccess) {
+        t_prof.total_ms += ms;
+        t_prof.count += 1;
+    }
+    t_prof.pending = false;
+}
+}  // namespace
+
+void profile_mark_begin(cudaStream_t s) {
+    if (!t_prof.enabled) return;
+    profile_flush();
+    cudaEventRecord(t_prof.ev[0], s);
+}
+void profile_mark_end(cudaStream_t s) {
+    if (!t_prof.enabled) return;
+    cudaEventRecord(t_prof.ev[1], s);
+    t_prof.pending = true;
+}
+
 int cuda_fail(cudaError_t e, const char* what) {
     t_detail = std::string(what) + ": " + cudaGetErrorString(e);
     return VB200_ERR_CUDA;
@@ -198,6 +232,35 @@ int vb200_check_kernel_status(int device, void* stream) {
     char buf[96];
     std::snprintf(buf, sizeof(buf), "kernel wait expired: code %d, site 0x%x", host >> 24, host & 0xFFFFFF);
     return set_detail(VB200_ERR_KERNEL_TIMEOUT, buf);
+}
+
+int vb200_profile_enable(int enable) {
+    if (enable) {
+        int dev = 0;
+        VB200_CUDA_TRY(cudaGetDevice(&dev));
+        if (t_prof.ev[0] && t_prof.dev != dev) {
+            cudaEventDestroy(t_prof.ev[0]); cudaEventDestroy(t_prof.ev[1]);
+            t_prof.ev[0] = t_prof.ev[1] = nullptr;
+        }
+        if (!t_prof.ev[0]) {
+            VB200_CUDA_TRY(cudaEventCreate(&t_prof.ev[0]));
+            VB200_CUDA_TRY(cudaEventCreate(&t_prof.ev[1]));
+            t_prof.dev = dev;
+        }
+        t_prof.total_ms = 0.0; t_prof.count = 0; t_prof.pending = false;
+        t_prof.enabled = true;
+    } else {
+        profile_flush();
+        t_prof.enabled = false;
+    }
+    return VB200_OK;
+}
+
+int vb200_profile_read(double* total_ms, uint64_t* launches) {
+    profile_flush();
+    if (total_ms) *total_ms = t_prof.total_ms;
+    if (launches) *launches = t_prof.count;
+    return VB200_OK;
 }
 
 size_t vb200_prefill_workspace_bytes(const vb200_prefill_args* a) {

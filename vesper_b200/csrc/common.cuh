@@ -18,6 +18,10 @@ namespace vb200 {
 void note_launch(int n = 1);
 int cuda_fail(cudaError_t e, const char* what);   // records detail, returns VB200_ERR_CUDA
 int set_detail(int status, const char* msg);      // records detail, returns status
+// Optional timing of the dominant kernel of a call (vb200_profile_enable): the
+// launch site brackets the kernel with two events on the launching stream.
+void profile_mark_begin(cudaStream_t s);
+void profile_mark_end(cudaStream_t s);
 
 #define VB200_CUDA_TRY(expr)                                              \
     do {                                                                  \

@@ -56,8 +56,10 @@ struct WarpState {
 // `wslot` in [0, nwslots).  The loop trip count is warp-uniform (both
 // half-warps run the same iterations; rows past nkeys are masked) because the
 // body uses full-warp shuffles.
-template <typename T, int NREP>
-__device__ __forceinline__ void process_rows(WarpState<T, NREP>& st, const T* ksm, const T* vsm, int nkeys,
+// KF32: the K rows are fp32 (used for the new token, whose rotated key is
+// scored at full precision in the step that appends it).
+template <typename T, int NREP, bool KF32 = false>
+__device__ __forceinline__ void process_rows(WarpState<T, NREP>& st, const void* ksm_raw, const T* vsm, int nkeys,
                                              int wslot, int nwslots, int lane, float* pbuf /* [16] per group */) {
     constexpr int KB = 16 / NREP;
     const int l16 = lane & 15;
@@ -68,12 +70,21 @@ __device__ __forceinline__ void process_rows(WarpState<T, NREP>& st, const T* ks
 #pragma unroll
         for (int kk = 0; kk < KB; ++kk) {
             int key = base + kk;
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (key < nkeys) raw = *reinterpret_cast<const uint4*>(ksm + key * 128 + l16 * 8);
             float kf[8];
-            const uint32_t* u = &raw.x;
+            if constexpr (KF32) {
+                float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+                if (key < nkeys) {
+                    const float* kp = static_cast<const float*>(ksm_raw) + key * 128 + l16 * 8;
+                    a0 = *reinterpret_cast<const float4*>(kp); a1 = *reinterpret_cast<const float4*>(kp + 4);
+                }
+                kf[0] = a0.x; kf[1] = a0.y; kf[2] = a0.z; kf[3] = a0.w; kf[4] = a1.x; kf[5] = a1.y; kf[6] = a1.z; kf[7] = a1.w;
+            } else {
+                uint4 raw = make_uint4(0, 0, 0, 0);
+                if (key < nkeys) raw = *reinterpret_cast<const uint4*>(static_cast<const T*>(ksm_raw) + key * 128 + l16 * 8);
+                const uint32_t* u = &raw.x;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { float2 t = Elem<T>::unpack2(u[i]); kf[2 * i] = t.x; kf[2 * i + 1] = t.y; }
+                for (int i = 0; i < 4; ++i) { float2 t = Elem<T>::unpack2(u[i]); kf[2 * i] = t.x; kf[2 * i + 1] = t.y; }
+            }
 #pragma unroll
             for (int h = 0; h < NREP; ++h) {
                 float a = 0.f;
@@ -142,16 +153,19 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p
     constexpr int D = 128;
     constexpr int kRowBytes = D * sizeof(T);
     constexpr int kStageBytes = 2 * kTile * kRowBytes;
+    constexpr int kNewBytes = D * sizeof(float) + kRowBytes;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     T* ring = reinterpret_cast<T*>(smem_raw);
-    T* newkv = reinterpret_cast<T*>(smem_raw + kStages * kStageBytes);          // [2][128]
-    float* pbuf_all = reinterpret_cast<float*>(smem_raw + kStages * kStageBytes + 2 * kRowBytes);   // [8][16]
-    DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem_raw + kStages * kStageBytes + 2 * kRowBytes + 8 * 16 * sizeof(float));
+    float* newk = reinterpret_cast<float*>(smem_raw + kStages * kStageBytes);   // rotated new key, fp32 [128]
+    T* newv = reinterpret_cast<T*>(smem_raw + kStages * kStageBytes + kNewBytes - kRowBytes);   // new value [128]
+    float* pbuf_all = reinterpret_cast<float*>(smem_raw + kStages * kStageBytes + kNewBytes);   // [8][16]
+    DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem_raw + kStages * kStageBytes + kNewBytes + 8 * 16 * sizeof(float));
 
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, l16 = lane & 15;
 
-    const int len = p.seq_lens ? p.seq_lens[b] : p.uniform_len;    // cached keys before this token
+    int len = p.seq_lens ? p.seq_lens[b] : p.uniform_len;          // cached keys before this token
+    len = max(0, min(len, p.cache_cap));
     const int total = len + (p.append ? 1 : 0);
     const int k_begin = split * p.chunk;
     if (split == 0 && kvh == 0 && threadIdx.x == 0) {
@@ -230,22 +244,29 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p
             const T* vn = static_cast<const T*>(p.v_new.ptr) + b * p.v_new.sb + kvh * p.v_new.sh + l16 * 8;
             uint4 kraw = *reinterpret_cast<const uint4*>(kn);
             uint4 vraw = *reinterpret_cast<const uint4*>(vn);
-            if (p.rope) {
+            {
+                // this step scores the new key in fp32; the cache gets its 16-bit rounding
                 uint32_t* u = &kraw.x;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     float2 t = Elem<T>::unpack2(u[i]);
-                    float t1 = __fmul_rn(t.x, cs[i]), t2 = __fmul_rn(t.y, sn[i]);
-                    float t3 = __fmul_rn(t.x, sn[i]), t4 = __fmul_rn(t.y, cs[i]);
-                    u[i] = Elem<T>::pack2(__fsub_rn(t1, t2), __fadd_rn(t3, t4));
+                    if (p.rope) {
+                        float t1 = __fmul_rn(t.x, cs[i]), t2 = __fmul_rn(t.y, sn[i]);
+                        float t3 = __fmul_rn(t.x, sn[i]), t4 = __fmul_rn(t.y, cs[i]);
+                        t.x = __fsub_rn(t1, t2); t.y = __fadd_rn(t3, t4);
+                        u[i] = Elem<T>::pack2(t.x, t.y);
+                    }
+                    newk[l16 * 8 + 2 * i] = t.x;
+                    newk[l16 * 8 + 2 * i + 1] = t.y;
                 }
             }
-            *reinterpret_cast<uint4*>(newkv + l16 * 8) = kraw;
-            *reinterpret_cast<uint4*>(newkv + 128 + l16 * 8) = vraw;
-            T* kdst = const_cast<T*>(kc) + static_cast<long long>(len) * D + l16 * 8;
-            T* vdst = const_cast<T*>(vc) + static_cast<long long>(len) * D + l16 * 8;
-            *reinterpret_cast<uint4*>(kdst) = kraw;
-            *reinterpret_cast<uint4*>(vdst) = vraw;
+            *reinterpret_cast<uint4*>(newv + l16 * 8) = vraw;
+            if (len < p.cache_cap) {    // never write past the cache, whatever seq_lens holds
+                T* kdst = const_cast<T*>(kc) + static_cast<long long>(len) * D + l16 * 8;
+                T* vdst = const_cast<T*>(vc) + static_cast<long long>(len) * D + l16 * 8;
+                *reinterpret_cast<uint4*>(kdst) = kraw;
+                *reinterpret_cast<uint4*>(vdst) = vraw;
+            }
         }
 
         const int group = warp * 2 + (lane >> 4);
@@ -265,7 +286,7 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p
         if (owns_new && warp == 0) {
             __syncwarp();
             // one extra key: lands in half-warp 0's slot, half-warp 1 sees only masked rows
-            process_rows<T, NREP>(st, newkv, newkv + 128, 1, 0, 1, lane, pbuf);
+            process_rows<T, NREP, true>(st, newk, newv, 1, 0, 1, lane, pbuf);
         }
 
         // ---- merge the 8 groups of the CTA through shared memory (ring is free now) ----
@@ -366,7 +387,7 @@ __global__ void lse_combine_kernel(const float* __restrict__ partials, int R, lo
 template <typename T, int NREP>
 int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
     constexpr int D = 128;
-    size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + 2 * D * sizeof(T) + 8 * 16 * sizeof(float) + sizeof(DecodeSmem);
+    size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + D * sizeof(float) + D * sizeof(T) + 8 * 16 * sizeof(float) + sizeof(DecodeSmem);
     static_assert(8 * NREP * 128 * 4 + 2 * 8 * NREP * 4 <= kStages * 2 * kTile * 128 * 2, "merge buffers must fit in the ring");
     static thread_local int configured_dev = -1;
     int dev = 0;
@@ -376,7 +397,9 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
         configured_dev = dev;
     }
     dim3 grid(p.num_splits, p.Hkv, p.B);
+    profile_mark_begin(s);
     decode_splitkv_kernel<T, NREP><<<grid, kThreads, smem, s>>>(p);
+    profile_mark_end(s);
     note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());
     decode_combine_kernel<T><<<dim3(p.Hq, p.B), D, 0, s>>>(p);

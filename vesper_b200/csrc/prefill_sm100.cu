@@ -403,7 +403,9 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
     }
     const int n_pairs = (p.T + 2 * kBlockM - 1) / (2 * kBlockM);
     dim3 grid(static_cast<unsigned>(n_pairs) * p.B * p.Hq);
+    profile_mark_begin(s);
     prefill_sm100_kernel<T, D><<<grid, kThreads, Cfg<D>::kSmemBytes, s>>>(maps, p);
+    profile_mark_end(s);
     note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());
     return VB200_OK;

@@ -1,0 +1,97 @@
+"""Sequence-sharded long-context decode across the GPUs of one node.
+
+The KV sequence of each (batch, kv_head) is split into ``world`` contiguous
+shards, shard r living on GPU r.  One decode step is
+
+    local split-KV decode  ->  partial (O/l, m, l) per query head   [vb200_decode_fwd, partial_out]
+    all-gather of the partials (Hq*(D+2) floats per rank)           [NCCL via torch.distributed]
+    log-sum-exp combine, identical on every rank                    [vb200_lse_combine]
+
+There is no other exchange on the attention path; prefill and batched decode
+partition by (batch x kv_head) with no collective at all (``unit_range``).
+The reference has no multi-device code; numerically the result must equal the
+single-device attention (src/ops/flash_attention.cpp:309-345 is the combine
+algebra).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+def shard_range(total: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [begin, end) of a length-``total`` sequence owned by ``rank``: equal
+    contiguous shards, the remainder spread over the first ranks."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError("bad world/rank")
+    base, rem = divmod(total, world)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+def unit_range(n_units: int, world: int, rank: int) -> tuple[int, int]:
+    """Independent (batch x kv_head) units [begin, end) owned by ``rank``."""
+    return shard_range(n_units, world, rank)
+
+
+def owner_of_row(total: int, world: int, row: int) -> int:
+    """Rank whose shard contains ``row`` (rows past the end belong to the last rank,
+    which is where new tokens are appended)."""
+    for r in range(world):
+        b, e = shard_range(total, world, r)
+        if b <= row < e:
+            return r
+    return world - 1
+
+
+@dataclass
+class ShardedDecodeStep:
+    """One rank's view of a sequence-sharded decode step.
+
+    ``local_partial(rank_begin, q_position) -> tensor [B*Hq, D+2]`` computes this
+    rank's partial; ``combine(gathered [world, B*Hq, D+2]) -> (out, lse)`` merges.
+    On GPUs they are the C-ABI calls (see ``cuda_step``); the CPU tests plug in the
+    oracle to exercise the sharding and gather logic under gloo.
+    """
+    world: int
+    rank: int
+    context_len: int
+    validate: bool = False   # exchange the partial's shape first and fail on the host if ranks disagree
+
+    def run(self, local_partial, combine, dist=None):
+        import torch
+        begin, end = shard_range(self.context_len, self.world, self.rank)
+        part = local_partial(begin, end, self.context_len)
+        if self.world == 1:
+            gathered = part.unsqueeze(0)
+        else:
+            part = part.contiguous()
+            if self.validate:
+                mine = torch.tensor(list(part.shape) + [0] * (4 - part.dim()), dtype=torch.int64, device=part.device)
+                shapes = torch.empty(self.world * 4, dtype=torch.int64, device=part.device)
+                dist.all_gather_into_tensor(shapes, mine)
+                if not all(torch.equal(shapes[4 * r:4 * r + 4], mine) for r in range(self.world)):
+                    raise ValueError(f"rank {self.rank}: partial shapes differ across ranks: {shapes.view(self.world, 4).tolist()}")
+            flat = torch.empty((self.world * part.shape[0],) + tuple(part.shape[1:]), dtype=part.dtype, device=part.device)
+            dist.all_gather_into_tensor(flat, part)       # rank-major concatenation along dim 0
+            gathered = flat.view((self.world,) + tuple(part.shape))
+        return combine(gathered)
+
+
+def cuda_step(step: ShardedDecodeStep, q, k_shard, v_shard, *, scale, theta, partial_buf, out, lse=None,
+              gathered=None, workspace=None, dist=None, stream=None):
+    """GPU implementation of one step on this rank.  ``k_shard``/``v_shard`` hold rows
+    [begin, end) of the sequence; ``q`` is the unrotated query [B,Hq,1,D] (replicated)."""
+    import torch
+    from . import capi
+    begin, end = shard_range(step.context_len, step.world, step.rank)
+    B, Hq, _, D = q.shape
+    qpos = torch.full((B,), step.context_len, dtype=torch.int32, device=q.device)
+    capi.decode(q, None, k_shard, v_shard, scale=scale, theta=theta, uniform_len=end - begin, max_len=end - begin,
+                pos_offset=begin, q_positions=qpos, partial_out=partial_buf, workspace=workspace, stream=stream)
+    if step.world == 1:
+        g = partial_buf.view(1, B * Hq, D + 2)
+    else:
+        g = gathered if gathered is not None else torch.empty(step.world, B * Hq, D + 2, dtype=torch.float32, device=q.device)
+        dist.all_gather_into_tensor(g.view(step.world * B * Hq, D + 2), partial_buf.view(B * Hq, D + 2))
+    capi.lse_combine(g, out, lse, stream=stream)
+    return out
