@@ -156,6 +156,25 @@ typedef struct vb200_decode_args {
 size_t vb200_decode_workspace_bytes(const vb200_decode_args* a);
 int vb200_decode_fwd(const vb200_decode_args* a);
 
+/* The same decode step for callers that cannot supply a workspace and may not
+ * allocate device memory -- e.g. a serving process that has already handed all
+ * free HBM to its KV-cache pool, or plugin code inside a framework that owns
+ * every device allocation.  No counterpart in the reference (its backends get
+ * their buffers from the caller's allocator).  `workspace` and
+ * `workspace_bytes` of the argument struct are ignored; the split partials go
+ * to an array of VB200_STATIC_SCRATCH_BYTES that is part of the library image
+ * on each GPU.  The call allocates and frees nothing.
+ *   - A step whose plan needs more than the array holds (compare
+ *     vb200_decode_workspace_bytes) returns VB200_ERR_WORKSPACE: lower num_splits
+ *     or use vb200_decode_fwd.
+ *   - Every call on a GPU shares the array, which keeps the previous call's
+ *     contents (none of it needs clearing: a step writes each slot before it
+ *     reads it).  Calls that may overlap on one GPU race: keep them on one stream.
+ *   - The first call on a device resolves the array's device address; make that
+ *     first call before starting any stream capture. */
+#define VB200_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+int vb200_decode_fwd_static(const vb200_decode_args* a);
+
 /* Merge R partial results [R, rows, D+2] (layout of partial_out) into
  * out [rows, D] of `dtype` and lse [rows] (nullable):
  *   m* = max m_r,  l* = sum l_r e^{m_r - m*},  O* = sum O_r l_r e^{m_r - m*} / l*

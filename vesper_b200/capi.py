@@ -51,6 +51,7 @@ class DecodeArgs(C.Structure):
 
 EXPORTS = [
     "vb200_prefill_workspace_bytes", "vb200_prefill_fwd", "vb200_decode_workspace_bytes", "vb200_decode_fwd",
+    "vb200_decode_fwd_static",
     "vb200_lse_combine", "vb200_kv_append", "vb200_apply_rope", "vb200_repeat_kv", "vb200_rope_inv_freq",
     "vb200_strerror", "vb200_last_error_detail", "vb200_abi_version", "vb200_launch_count",
     "vb200_reset_launch_count", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
@@ -79,6 +80,7 @@ def load():
     L.vb200_decode_workspace_bytes.argtypes = [C.POINTER(DecodeArgs)]
     L.vb200_decode_workspace_bytes.restype = C.c_size_t
     L.vb200_decode_fwd.argtypes = [C.POINTER(DecodeArgs)]
+    L.vb200_decode_fwd_static.argtypes = [C.POINTER(DecodeArgs)]
     L.vb200_lse_combine.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
     L.vb200_kv_append.argtypes = [C.c_int, C.c_void_p, C.c_int32] + [C.c_int32] * 5 + [C.POINTER(Tensor4)] * 4 + [C.c_int32, C.POINTER(Rope)]
     L.vb200_apply_rope.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int32] * 4
