@@ -169,48 +169,56 @@ def run_reference(args):
 # ----------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------
-def run_ours(args):
-    import numpy as np
-    import torch
-    import torch.distributed as dist
-    from vesper_b200 import capi
+class Ctx:
+    """Per-process state of the GPU arm: device, ranks, helpers."""
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU arm)")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    capi.load()
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        from vesper_b200 import capi
+        self.torch, self.dist, self.capi = torch, dist, capi
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU arm)")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        self.L = capi.load()
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.peaks = load_peaks()
+        self.traffic = load_traffic()
+        self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=self.dev)
 
-    peaks = load_peaks()
-    traffic = load_traffic()
-    K, W = max(1, args.steps), max(3, args.warmup)
-    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    def flush_l2(self):
+        self.flush_buf.fill_(1)
 
-    def flush_l2():
-        flush_buf.fill_(1)
+    def sync_all(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
 
-    def sync_all():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def max_over_ranks(x):
-        if world == 1:
+    def max_over_ranks(self, x):
+        if self.world == 1:
             return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t = self.torch.tensor([x], dtype=self.torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ------------------------------------------------------------------ prefill (headline)
+    def event(self):
+        return self.torch.cuda.Event(enable_timing=True)
+
+
+def bench_prefill(cx, K, W, quick=False):
+    """Headline: C2 prefill.  Returns the fields of the JSON line that come from it."""
+    import ctypes as C
+    import numpy as np
+    torch, capi, L, dev = cx.torch, cx.capi, cx.L, cx.dev
     c = C2
     B, Hq, Hkv, S, D = c["B"], c["Hq"], c["Hkv"], c["S"], c["D"]
-    g = torch.Generator(device="cpu").manual_seed(1 + rank)
+    g = torch.Generator(device="cpu").manual_seed(1 + cx.rank)
     hq = (0.5 * torch.randn(B, Hq, S, D, generator=g)).to(torch.bfloat16).pin_memory()
     hk = (0.5 * torch.randn(B, Hkv, S, D, generator=g)).to(torch.bfloat16).pin_memory()
     hv = (0.5 * torch.randn(B, Hkv, S, D, generator=g)).to(torch.bfloat16).pin_memory()
@@ -223,81 +231,98 @@ def run_ours(args):
     vc = torch.zeros_like(kc)
     scale = float(1.0 / np.sqrt(D))
     a = capi.prefill_args(q, k, v, o, lse, scale=scale, causal=True, theta=c["theta"], k_cache=kc, v_cache=vc)
-    import ctypes as C
-    L = capi.load()
     ws = torch.empty(max(256, L.vb200_prefill_workspace_bytes(C.byref(a))), dtype=torch.uint8, device=dev)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
 
-    def prefill_step():
+    def step():
         capi.check(L.vb200_prefill_fwd(C.byref(a)))
 
     for _ in range(W):
-        prefill_step()
-    sync_all()
-    sampler = ClockSampler(local)
+        step()
+    cx.sync_all()
+    sampler = ClockSampler(cx.local)
     sampler.start()
-    time.sleep(0.25)
+    time.sleep(0.3)
     L.vb200_reset_launch_count()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    sync_all()
-    t_wall0 = time.time()
+    evs = [(cx.event(), cx.event()) for _ in range(K)]
+    cx.sync_all()
+    t0 = time.time()
     for i in range(K):
-        flush_l2()
+        cx.flush_l2()
         evs[i][0].record()
-        prefill_step()
+        step()
         evs[i][1].record()
-    sync_all()
-    t_wall1 = time.time()
+    cx.sync_all()
+    t1 = time.time()
     launches = int(L.vb200_launch_count())
-    step_ms = [s.elapsed_time(e) for s, e in evs]
-    # separate pass for the dominant kernel's own duration (event brackets inside the library
-    # serialise consecutive calls, so they stay out of the whole-job timing above)
+    total_ms = cx.max_over_ranks(sum(s.elapsed_time(e) for s, e in evs))
+    ms_per_step = total_ms / K
+    # the dominant kernel's own duration: a separate pass, because the event brackets inside the
+    # library make consecutive calls wait for each other
     capi.profile_enable(True)
     for _ in range(min(K, 10)):
-        flush_l2()
-        prefill_step()
+        cx.flush_l2()
+        step()
     torch.cuda.synchronize()
     kern_ms, kern_n = capi.profile_read()
     capi.profile_enable(False)
-    total_ms = max_over_ranks(sum(step_ms))
-    ms_per_step = total_ms / K
+    # the timed region lasts only milliseconds: keep the same step running a little longer so
+    # the 100 ms clock sampler sees this load (skipped in profiling runs)
+    if not quick:
+        t_busy = time.time()
+        while time.time() - t_busy < 0.6:
+            step()
+        torch.cuda.synchronize()
+        t1 = time.time()
+    clocks = sampler.stop(t0, t1)
     flops = prefill_flops(c)
-    value = world * flops / (ms_per_step * 1e-3) / 1e12
     kern_avg_ms = kern_ms / max(1, kern_n)
-    achieved_tf = flops / (kern_avg_ms * 1e-3) / 1e12
+    achieved = flops / (kern_avg_ms * 1e-3) / 1e12
 
-    # ------------------------------------------------------------------ prefill end to end (host buffers)
+    # end to end through the C ABI with host buffers: H2D of q,k,v and D2H of O,LSE every step
     def e2e_step():
         q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True); v.copy_(hv, non_blocking=True)
-        prefill_step()
+        step()
         ho.copy_(o, non_blocking=True); hl.copy_(lse, non_blocking=True)
 
     for _ in range(2):
         e2e_step()
-    sync_all()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    cx.sync_all()
+    e0, e1 = cx.event(), cx.event()
     Ke = min(K, 10)
     e0.record()
     for _ in range(Ke):
         e2e_step()
     e1.record()
-    sync_all()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / Ke
-    e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
-    h2d = (hq.numel() + hk.numel() + hv.numel()) * 2
-    d2h = ho.numel() * 2 + hl.numel() * 4
-    capi.check_kernel_status(local)
-    del hq, hk, hv, ho, hl, q, k, v, o, lse, kc, vc
+    cx.sync_all()
+    e2e_ms = cx.max_over_ranks(e0.elapsed_time(e1)) / Ke
+    capi.check_kernel_status(cx.local)
+    pk = cx.peaks
+    return {
+        "value": cx.world * flops / (ms_per_step * 1e-3) / 1e12, "ms_per_step": ms_per_step, "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tf"], "unit": "TFLOP/s", "frac": achieved / pk["tf"],
+                     "peak_source": pk["source"] + " (burst cuBLAS bf16)", "frac_of_sustained": achieved / pk["tf_sustained"],
+                     "frac_of_nominal_2250": achieved / 2250.0, "kernel": "prefill_sm100_kernel", "kernel_ms": kern_avg_ms,
+                     "traffic": cx.traffic.get("prefill_sm100_bytes_per_launch")},
+        "e2e": {"value": cx.world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": (hq.numel() + hk.numel() + hv.numel()) * 2, "d2h_bytes_per_step": ho.numel() * 2 + hl.numel() * 4,
+                "ms_per_step": e2e_ms},
+        "clocks": clocks,
+    }
 
-    # ------------------------------------------------------------------ batched ragged decode
+
+def bench_decode(cx, nsteps, W):
+    """C3: batched ragged GQA decode, `nsteps` consecutive steps each appending one token."""
+    import ctypes as C
+    import numpy as np
+    torch, capi, L, dev = cx.torch, cx.capi, cx.L, cx.dev
     d = C3
     B, Hq, Hkv, D = d["B"], d["Hq"], d["Hkv"], d["D"]
     rs = np.random.RandomState(2)
     lens0 = rs.randint(d["lo"], d["hi"] + 1, size=B).astype(np.int32)
-    nsteps = d["steps"]
-    nprof = 32
+    nprof = min(32, nsteps)
     cap = d["hi"] + nsteps + nprof + W + 8
-    gd = torch.Generator(device=dev).manual_seed(3 + rank)
+    gd = torch.Generator(device=dev).manual_seed(3 + cx.rank)
     kc = torch.randn(B, Hkv, cap, D, generator=gd, device=dev, dtype=torch.bfloat16)
     vc = torch.randn(B, Hkv, cap, D, generator=gd, device=dev, dtype=torch.bfloat16)
     q1 = torch.randn(B, Hq, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
@@ -305,117 +330,134 @@ def run_ours(args):
     v1 = torch.randn(B, Hkv, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
     o1 = torch.empty_like(q1)
     seq = torch.from_numpy(lens0).to(dev)
+    scale = float(1.0 / np.sqrt(D))
     da = capi.decode_args(q1, o1, kc, vc, scale=scale, k_new=k1, v_new=v1, theta=10000.0, seq_lens=seq,
                           advance_lens=True, max_len=int(lens0.max()) + nsteps + nprof + W + 1)
     dws = torch.empty(L.vb200_decode_workspace_bytes(C.byref(da)), dtype=torch.uint8, device=dev)
     da.workspace, da.workspace_bytes = dws.data_ptr(), dws.numel()
-    for _ in range(W):
+
+    def step():
         capi.check(L.vb200_decode_fwd(C.byref(da)))
-    sync_all()
+
+    for _ in range(W):
+        step()
+    cx.sync_all()
     lens_start = lens0.astype(np.int64) + W
     L.vb200_reset_launch_count()
-    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    d0, d1 = cx.event(), cx.event()
     d0.record()
     for _ in range(nsteps):
-        capi.check(L.vb200_decode_fwd(C.byref(da)))
+        step()
     d1.record()
-    sync_all()
-    dec_launches = int(L.vb200_launch_count())
-    dec_ms = max_over_ranks(d0.elapsed_time(d1))
+    cx.sync_all()
+    launches = int(L.vb200_launch_count())
+    dec_ms = cx.max_over_ranks(d0.elapsed_time(d1))
     # K and V rows read once per KV head, including the token appended in the step
     step_bytes = lambda t: float(np.sum(2 * Hkv * (lens_start + t + 1) * D * 2))
     dec_bytes = sum(step_bytes(t) for t in range(nsteps))
-    dec_gbs = world * dec_bytes / (dec_ms * 1e-3) / 1e9
     capi.profile_enable(True)          # kernel-only pass over the next nprof steps
     for _ in range(nprof):
-        capi.check(L.vb200_decode_fwd(C.byref(da)))
+        step()
     torch.cuda.synchronize()
-    dkern_ms, dkern_n = capi.profile_read()
+    kern_ms, _ = capi.profile_read()
     capi.profile_enable(False)
     prof_bytes = sum(step_bytes(t) for t in range(nsteps, nsteps + nprof))
-    dec_kernel_gbs = prof_bytes / (dkern_ms * 1e-3) / 1e9 if dkern_ms > 0 else None
-    capi.check_kernel_status(local)
+    kgbs = prof_bytes / (kern_ms * 1e-3) / 1e9 if kern_ms > 0 else None
+    capi.check_kernel_status(cx.local)
     assert seq.cpu().numpy().tolist() == (lens0 + W + nsteps + nprof).tolist()
-    decode = {
-        "metric": "decode KV-read GB/s", "value": dec_gbs, "unit": "GB/s", "ms_per_step": dec_ms / nsteps, "steps": nsteps,
+    pk = cx.peaks
+    return {
+        "metric": "decode KV-read GB/s", "value": cx.world * dec_bytes / (dec_ms * 1e-3) / 1e9, "unit": "GB/s",
+        "ms_per_step": dec_ms / nsteps, "steps": nsteps,
         "config": {"workload": f"batched GQA decode B={B} Hq={Hq} Hkv={Hkv} D={D} bf16 cache, ragged contexts U[{d['lo']},{d['hi']}] (seed 2), "
-                               f"{nsteps} consecutive steps each appending one token; inputs larger than L2 ({dec_bytes / nsteps / 1e6:.0f} MB/step)"},
-        "gpu_launches": dec_launches,
-        "roofline": {"bound": "hbm", "achieved": dec_kernel_gbs, "peak": peaks["hbm"], "unit": "GB/s",
-                     "frac": (dec_kernel_gbs / peaks["hbm"]) if dec_kernel_gbs else None, "peak_source": peaks["source"],
-                     "frac_of_nominal_8TBs": (dec_kernel_gbs / 8000.0) if dec_kernel_gbs else None,
-                     "traffic": traffic.get("decode_splitkv_bytes_per_launch")},
+                               f"{nsteps} consecutive steps each appending one token (RoPE + append fused); inputs larger than L2 "
+                               f"({dec_bytes / nsteps / 1e6:.0f} MB of K/V per step)"},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": kgbs, "peak": pk["hbm"], "unit": "GB/s", "frac": (kgbs / pk["hbm"]) if kgbs else None,
+                     "peak_source": pk["source"], "frac_of_nominal_8TBs": (kgbs / 8000.0) if kgbs else None,
+                     "kernel": "decode_splitkv_kernel", "kernel_ms": kern_ms / max(1, nprof),
+                     "traffic": cx.traffic.get("decode_splitkv_bytes_per_launch")},
     }
-    del kc, vc, dws
 
-    # ------------------------------------------------------------------ sequence-sharded long-context decode
+
+def bench_sharded(cx, nsteps=50):
+    """C4: long-context decode with the KV sequence sharded over the ranks."""
+    import numpy as np
     from vesper_b200.sharded import ShardedDecodeStep, cuda_step, shard_range
+    torch, capi, dev, world = cx.torch, cx.capi, cx.dev, cx.world
     s4 = C4
-    Bq, Hq4, Hkv4, L4 = s4["B"], s4["Hq"], s4["Hkv"], s4["L"]
-    begin, end = shard_range(L4, world, rank)
+    Bq, Hq, Hkv, D, L4 = s4["B"], s4["Hq"], s4["Hkv"], s4["D"], s4["L"]
+    begin, end = shard_range(L4, world, cx.rank)
     g4 = torch.Generator(device=dev).manual_seed(5)
-    ks = torch.randn(Bq, Hkv4, end - begin, D, generator=g4, device=dev, dtype=torch.bfloat16)
-    vs = torch.randn(Bq, Hkv4, end - begin, D, generator=g4, device=dev, dtype=torch.bfloat16)
-    q4 = torch.randn(Bq, Hq4, 1, D, generator=torch.Generator(device=dev).manual_seed(6), device=dev, dtype=torch.bfloat16)
-    part = torch.empty(Bq * Hq4, D + 2, dtype=torch.float32, device=dev)
-    gath = torch.empty(world, Bq * Hq4, D + 2, dtype=torch.float32, device=dev)
-    out4 = torch.empty(Bq * Hq4, D, dtype=torch.bfloat16, device=dev)
-    step4 = ShardedDecodeStep(world, rank, L4)
+    ks = torch.randn(Bq, Hkv, end - begin, D, generator=g4, device=dev, dtype=torch.bfloat16)
+    vs = torch.randn(Bq, Hkv, end - begin, D, generator=g4, device=dev, dtype=torch.bfloat16)
+    q4 = torch.randn(Bq, Hq, 1, D, generator=torch.Generator(device=dev).manual_seed(6), device=dev, dtype=torch.bfloat16)
+    part = torch.empty(Bq * Hq, D + 2, dtype=torch.float32, device=dev)
+    gath = torch.empty(world, Bq * Hq, D + 2, dtype=torch.float32, device=dev)
+    out4 = torch.empty(Bq * Hq, D, dtype=torch.bfloat16, device=dev)
+    step4 = ShardedDecodeStep(world, cx.rank, L4)
     ws4 = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
-    n4 = 50
+    scale = float(1.0 / np.sqrt(D))
+    dist = cx.dist if world > 1 else None
+
+    def step():
+        cuda_step(step4, q4, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out4, gathered=gath, workspace=ws4, dist=dist)
+
     for _ in range(5):
-        cuda_step(step4, q4, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out4, gathered=gath, workspace=ws4, dist=dist if world > 1 else None)
-    sync_all()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        step()
+    cx.sync_all()
+    s0, s1 = cx.event(), cx.event()
     s0.record()
-    for _ in range(n4):
-        cuda_step(step4, q4, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out4, gathered=gath, workspace=ws4, dist=dist if world > 1 else None)
+    for _ in range(nsteps):
+        step()
     s1.record()
-    sync_all()
-    sh_ms = max_over_ranks(s0.elapsed_time(s1)) / n4
-    sh_bytes = 2.0 * Hkv4 * L4 * D * 2
-    capi.check_kernel_status(local)
-    sharded = {
-        "metric": "long-context decode KV-read GB/s (aggregate)", "value": sh_bytes / (sh_ms * 1e-3) / 1e9, "unit": "GB/s",
-        "ms_per_step": sh_ms, "scaling": "strong",
-        "config": {"workload": f"split-KV decode B=1 Hq={Hq4} Hkv={Hkv4} D={D} bf16, context {L4} sharded over {world} GPU(s); "
-                               f"partial (O/l, m, l) all-gather of {Hq4 * (D + 2) * 4} B per rank, then LSE combine"},
-        "roofline": {"bound": "hbm", "achieved": sh_bytes / world / (sh_ms * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s per GPU",
-                     "frac": sh_bytes / world / (sh_ms * 1e-3) / 1e9 / peaks["hbm"], "peak_source": peaks["source"]},
+    cx.sync_all()
+    ms = cx.max_over_ranks(s0.elapsed_time(s1)) / nsteps
+    nbytes = 2.0 * Hkv * L4 * D * 2
+    capi.check_kernel_status(cx.local)
+    per_gpu = nbytes / world / (ms * 1e-3) / 1e9
+    return {
+        "metric": "long-context decode KV-read GB/s (aggregate)", "value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
+        "ms_per_step": ms, "scaling": "strong",
+        "config": {"workload": f"split-KV decode B=1 Hq={Hq} Hkv={Hkv} D={D} bf16, context {L4} sharded over {world} GPU(s); "
+                               f"partial (O/l, m, l) all-gather of {Hq * (D + 2) * 4} B per rank, then LSE combine"},
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": cx.peaks["hbm"], "unit": "GB/s per GPU",
+                     "frac": per_gpu / cx.peaks["hbm"], "peak_source": cx.peaks["source"]},
     }
 
-    clocks = sampler.stop(t_wall0, t_wall1)
 
+def run_ours(args):
+    cx = Ctx()
+    K, W = max(1, args.steps), max(3, args.warmup)
+    only = args.only
+    pre = bench_prefill(cx, K, W, quick=args.no_cpu_baseline) if only in ("all", "prefill") else None
+    dec = bench_decode(cx, args.decode_steps, W) if only in ("all", "decode") else None
+    shd = bench_sharded(cx) if only in ("all", "sharded") else None
     cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if cx.rank == 0 and cx.world == 1 and not args.no_cpu_baseline and only == "all":
         cpu_baseline, _ = cpu_prefill_sample(target_seconds=12.0)
-
-    if rank == 0:
+    if cx.rank == 0:
         line = {
             "metric": "prefill attn TFLOP/s & decode KV-read GB/s vs B200 roofline",
-            "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "value": pre["value"] if pre else None, "unit": "TFLOP/s", "n_gpus": cx.world, "steps": K, "warmup": W,
+            "ms_per_step": pre["ms_per_step"] if pre else None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"GQA causal prefill B={C2['B']} Hq={C2['Hq']} Hkv={C2['Hkv']} S={C2['S']} D={C2['D']} bf16 (fp32 accumulate), "
-                                   f"RoPE theta 1e4 on Q and K, K/V appended into an empty cache of capacity {C2['cap']}; per GPU, units (batch x kv_head) "
-                                   "partitioned with no collective",
+                                   f"RoPE theta 1e4 on Q and K, K/V appended into an empty cache of capacity {C2['cap']}; per GPU, units "
+                                   "(batch x kv_head) partitioned over ranks with no collective",
                        "l2": "256 MiB flush write between timed steps", "flops": "4*B*Hq*D*S*(S+1)/2"},
-            "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peaks["tf"], "unit": "TFLOP/s",
-                         "frac": achieved_tf / peaks["tf"], "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
-                         "frac_of_sustained": achieved_tf / peaks["tf_sustained"], "frac_of_nominal_2250": achieved_tf / 2250.0,
-                         "kernel": "prefill_sm100_kernel", "kernel_ms": kern_avg_ms,
-                         "traffic": traffic.get("prefill_sm100_bytes_per_launch")},
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-            "gpu_launches": launches,
-            "clocks": clocks,
-            "decode": decode,
-            "decode_sharded": sharded,
+            "roofline": pre["roofline"] if pre else None,
+            "e2e": pre["e2e"] if pre else None,
+            "gpu_launches": pre["gpu_launches"] if pre else (dec["gpu_launches"] if dec else 0),
+            "clocks": pre["clocks"] if pre else None,
+            "decode": dec,
+            "decode_sharded": shd,
         }
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if cx.world > 1:
+        cx.dist.destroy_process_group()
 
 
 def main():
@@ -424,7 +466,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU sample (profiling runs)")
+    ap.add_argument("--decode-steps", type=int, default=C3["steps"], help="consecutive decode steps (default: the workload's 256)")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "sharded"], help="run one section (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -71,9 +71,10 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
-        raise FileNotFoundError(f"{LIB_PATH} is missing: run `python -m vesper_b200.build` (needs nvcc)")
-    L = C.CDLL(LIB_PATH)
+    path = os.environ.get("VESPER_B200_LIB", LIB_PATH)     # override: a differently tuned build of the same library
+    if not os.path.exists(path):
+        raise FileNotFoundError(f"{path} is missing: run `python -m vesper_b200.build` (needs nvcc)")
+    L = C.CDLL(path)
     L.vb200_prefill_workspace_bytes.argtypes = [C.POINTER(PrefillArgs)]
     L.vb200_prefill_workspace_bytes.restype = C.c_size_t
     L.vb200_prefill_fwd.argtypes = [C.POINTER(PrefillArgs)]

@@ -299,6 +299,7 @@ int vb200_prefill_fwd(const vb200_prefill_args* a) {
     p.o = to_view(a->o);
     p.lse = a->lse;
     p.q_rope_table = table;
+    fill_inv_freq(p.inv_freq, a->rope, a->D);
     p.status = kernel_status_word();
     if (!p.status) return set_detail(VB200_ERR_CUDA, "cannot resolve the device status word");
 

@@ -104,6 +104,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// 3-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float m;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+    return m;
+}
+
 __device__ __forceinline__ float fast_log2(float x) {
     float y;
     asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -42,6 +42,7 @@ struct PrefillParams {
     View4 q, k, v, o;   // k, v: the tensors attention reads (cache or inputs), [B,Hkv,>=Skv,D]
     float* lse;         // [B,Hq,T] or null
     const float2* q_rope_table;   // [T, D/2] (cos,sin) for the query rows, or null
+    InvFreq inv_freq;             // rotation frequencies (valid when q_rope_table is set)
     int* status;                  // device status word (bounded waits)
 };
 int launch_prefill_f32(cudaStream_t s, const PrefillParams& p);

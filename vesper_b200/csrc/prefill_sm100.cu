@@ -1,18 +1,23 @@
 // bf16 / fp16 attention forward for sm_100a: TMA-staged Q/K/V tiles,
 // tcgen05.mma with TMEM accumulators for S = Q K^T and O = P V, online softmax
 // in registers (one thread per query row), causal block skipping, GQA by
-// head-group indexing, RoPE of the Q tile fused into the prologue.
+// head-group indexing, RoPE of the Q tiles fused in (rotated in shared memory
+// by two otherwise idle warps while the previous work item computes).
 //
 // Math (same as flash_attention_cpu_dispatch, src/ops/flash_attention.cpp:218-364):
 //   s_ij = scale * q_i . k_j ;  key j visible to query i iff j <= start_pos + i
 //   O_i = sum_j softmax_j(s_ij) v_j ;  LSE_i = ln sum_j exp(s_ij)
 //
-// CTA = two 128-row query tiles of one (batch, q_head), processed ping-pong so
-// the tensor pipe works on one tile while the other is in softmax:
-//   warps 0-3   softmax / correction / epilogue of tile 0   (TMEM lanes 0..127)
-//   warps 4-7   the same for tile 1
-//   warp  8     TMA producer (Q tiles, then the K/V ring)
-//   warp  9     tcgen05.mma issuer, TMEM owner
+// Persistent kernel, one CTA per SM.  A work item is two adjacent 128-row
+// query tiles of one (batch, q_head), processed ping-pong so the tensor pipe
+// works on one tile while the other is in softmax.  Items are sorted by work
+// (last query rows first) and dealt to the CTAs in snake order.
+//   warps 0-3    softmax / correction / epilogue of tile 0   (TMEM lanes 0..127)
+//   warps 4-7    the same for tile 1
+//   warp  8      TMA producer: Q tiles (3 rotating buffers, so the next item's
+//                tiles load while this one computes) and the K/V ring (4 slots)
+//   warp  9      tcgen05.mma issuer, TMEM owner
+//   warps 10-11  RoPE of freshly loaded Q tiles, in place in swizzled smem
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D);
 // P (16-bit, packed two per column) overwrites the first 64 columns of its S.
 //
@@ -28,17 +33,43 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kStages = 4;
-constexpr int kSoftmaxThreads = 256;
+constexpr int kStages = 4;        // K/V ring slots
+constexpr int kQBufs = 3;         // rotating Q tile buffers
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kRopeWarp0 = 10;    // warps 10, 11
+constexpr int kRopeThreads = 64;
+constexpr int kThreads = 384;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;
 
+// tuning knobs (compile-time)
+#ifndef VB_REG_SOFTMAX
+#define VB_REG_SOFTMAX 216     // registers per thread of the two softmax warpgroups
+#endif
+#ifndef VB_REG_OTHER
+#define VB_REG_OTHER 72        // registers per thread of the producer / MMA / RoPE warpgroup
+#endif
+#ifndef VB_PACKED_MATH
+#define VB_PACKED_MATH 1       // fp32x2 FMA/add in the softmax
+#endif
+#ifndef VB_MAX3
+#define VB_MAX3 0              // 3-input max in the row maximum
+#endif
+static_assert(VB_REG_SOFTMAX * 256 + VB_REG_OTHER * 128 <= 168 * 384, "register budget");
+
+#ifdef VB_TIMING
+// Development aid: per-CTA cycle counters, [cta][item][slot], written when the buffer is set.
+__device__ long long* g_timing_buf = nullptr;
+#define VB_T(slot, value)                                                                   \
+    do { if (g_timing_buf && item_no < 16) g_timing_buf[(blockIdx.x * 16 + item_no) * 16 + (slot)] = (value); } while (0)
+#else
+#define VB_T(slot, value) do { } while (0)
+#endif
+
 struct __align__(8) Barriers {
-    uint64_t q_full[2], q_ready[2];
+    uint64_t q_full[kQBufs], q_rot[kQBufs], q_free[kQBufs];
     uint64_t kv_full[kStages], kv_empty[kStages];
     uint64_t s_full[2], p_ready[2], o_done[2];
     uint64_t mma_done;
@@ -55,8 +86,46 @@ struct Cfg {
     static constexpr int kHalves = D / 64;                       // 64-column (128-byte) boxes per row
     static constexpr int kHalfBytes = 128 * 128;                 // one [128 rows][64 cols] 16-bit box
     static constexpr int kTileBytes = kHalves * kHalfBytes;      // one [128][D] tile
-    static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + 1024 /*alignment slack*/ + 256 /*Barriers*/;
+    static constexpr int kSmemBytes = (kQBufs + kStages) * kTileBytes + 1024 /*alignment slack*/ + 256 /*Barriers*/;
 };
+
+// One unit of work: two adjacent 128-row query tiles of one (batch, q_head).
+struct Item {
+    int b, hq, hkv;
+    int r0[2];      // first query row of each tile
+    int nblk[2];    // key blocks each tile visits (0: tile not present)
+    int nmax;
+};
+
+__device__ __forceinline__ Item get_item(const PrefillParams& p, int it, int n_bh, int n_pairs) {
+    Item w;
+    const int pair = n_pairs - 1 - it / n_bh;      // heaviest (last) query pairs first
+    const int bh = it % n_bh;
+    w.b = bh / p.Hq;
+    w.hq = bh % p.Hq;
+    w.hkv = w.hq / (p.Hq / p.Hkv);
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        w.r0[t] = (2 * pair + t) * kBlockM;
+        if (w.r0[t] >= p.T) { w.nblk[t] = 0; continue; }
+        int kv_end = p.Skv;
+        if (p.causal) kv_end = min(p.Skv, p.start_pos + min(w.r0[t] + kBlockM, p.T));
+        w.nblk[t] = (kv_end + kBlockN - 1) / kBlockN;
+    }
+    w.nmax = max(w.nblk[0], w.nblk[1]);
+    return w;
+}
+
+// Snake dealing of the sorted items: round r gives CTA c item r*G + c (even r)
+// or r*G + G-1-c (odd r), which evens out the per-CTA totals.  -1: none.
+__device__ __forceinline__ int item_of_round(int round, int n_items) {
+    const int G = gridDim.x, c = blockIdx.x;
+    const int idx = round * G + ((round & 1) ? (G - 1 - c) : c);
+    return idx < n_items ? idx : -1;
+}
+
+template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -65,36 +134,24 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
     extern __shared__ unsigned char smem_dyn[];
     // 128B-swizzled tiles need 1024-byte alignment
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-    unsigned char* q_smem = smem;                               // 2 tiles
-    unsigned char* kv_smem = smem + 2 * C::kTileBytes;          // kStages tiles
-    Barriers* bar = reinterpret_cast<Barriers*>(smem + (2 + kStages) * C::kTileBytes);
+    unsigned char* q_smem = smem;                                   // kQBufs tiles
+    unsigned char* kv_smem = smem + kQBufs * C::kTileBytes;         // kStages tiles
+    Barriers* bar = reinterpret_cast<Barriers*>(smem + (kQBufs + kStages) * C::kTileBytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-    // ---- work item: heaviest (last) query pairs first ----
     const int n_bh = p.B * p.Hq;
     const int n_pairs = (p.T + 2 * kBlockM - 1) / (2 * kBlockM);
-    const int pair = n_pairs - 1 - static_cast<int>(blockIdx.x) / n_bh;
-    const int bh = static_cast<int>(blockIdx.x) % n_bh;
-    const int b = bh / p.Hq, hq = bh % p.Hq;
-    const int hkv = hq / (p.Hq / p.Hkv);
-
-    int r0[2], nblk[2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        r0[t] = (2 * pair + t) * kBlockM;
-        if (r0[t] >= p.T) { nblk[t] = 0; continue; }
-        int kv_end = p.Skv;
-        if (p.causal) kv_end = min(p.Skv, p.start_pos + min(r0[t] + kBlockM, p.T));
-        nblk[t] = (kv_end + kBlockN - 1) / kBlockN;
-    }
-    const int nmax = max(nblk[0], nblk[1]);
+    const int n_items = n_bh * n_pairs;
+    const int n_rounds = (n_items + gridDim.x - 1) / gridDim.x;
+    const bool rope = p.q_rope_table != nullptr;
 
     // ---- setup ----
     if (warp == kMmaWarp) {
         if (lane == 0) {
+            for (int b = 0; b < kQBufs; ++b) {
+                mbar_init(&bar->q_full[b], 1); mbar_init(&bar->q_rot[b], kRopeThreads); mbar_init(&bar->q_free[b], 1);
+            }
             for (int t = 0; t < 2; ++t) {
-                mbar_init(&bar->q_full[t], 1); mbar_init(&bar->q_ready[t], kBlockM);
                 mbar_init(&bar->s_full[t], 1); mbar_init(&bar->p_ready[t], kBlockM); mbar_init(&bar->o_done[t], 1);
             }
             for (int s = 0; s < kStages; ++s) { mbar_init(&bar->kv_full[s], 1); mbar_init(&bar->kv_empty[s], 1); }
@@ -114,231 +171,392 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
     const uint32_t tmem_base = bar->tmem_base;
     const WaitCtx abort_flag{&bar->abort_flag, p.status};
 
-    if (warp == kProducerWarp) {
-        // =========================== TMA producer ===========================
-        if (lane == 0) {
-            for (int t = 0; t < 2; ++t) {
-                if (nblk[t] == 0) continue;
-                mbar_arrive_expect_tx(&bar->q_full[t], C::kTileBytes);
-                for (int h = 0; h < C::kHalves; ++h)
-                    tma_load_4d(q_smem + t * C::kTileBytes + h * C::kHalfBytes, &maps.q, &bar->q_full[t], h * 64, r0[t], hq, b);
-            }
-            bool ok = true;
-            for (int item = 0; item < 2 * nmax && ok; ++item) {     // item 2j = K_j, 2j+1 = V_j
-                const int slot = item % kStages, j = item >> 1;
-                if (item >= kStages) ok = mbar_wait(&bar->kv_empty[slot], ((item / kStages) - 1) & 1, abort_flag, 0x100 + item);
-                if (!ok) break;
-                mbar_arrive_expect_tx(&bar->kv_full[slot], C::kTileBytes);
-                const CUtensorMap* m = (item & 1) ? &maps.v : &maps.k;
-                for (int h = 0; h < C::kHalves; ++h)
-                    tma_load_4d(kv_smem + slot * C::kTileBytes + h * C::kHalfBytes, m, &bar->kv_full[slot], h * 64, j * kBlockN, hkv, b);
-            }
-        }
-    } else if (warp == kMmaWarp) {
-        // =========================== MMA issuer ===========================
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = make_idesc_f16(Elem<T>::kFormat, 0, 0, kBlockM, kBlockN);
-            constexpr uint32_t idesc_pv = make_idesc_f16(Elem<T>::kFormat, 0, 1, kBlockM, D);
-            const uint32_t q_addr = smem_u32(q_smem), kv_addr = smem_u32(kv_smem);
-            auto tmem_s = [&](int t) { return tmem_base + static_cast<uint32_t>(t * 128); };
-            auto tmem_o = [&](int t) { return tmem_base + static_cast<uint32_t>(256 + t * 128); };
-            auto issue_qk = [&](int t, int slot) {
+    if (warp >= 8) {
+        // the data-movement / issue / RoPE warpgroup needs few registers; the softmax warpgroups take them
+        reg_dec<VB_REG_OTHER>();
+        if (warp == kProducerWarp) {
+            // =========================== TMA producer ===========================
+            if (lane == 0) {
+                int kv_item = 0;                 // running index into the K/V ring over all work items
+                int q_seq = 0;                   // running index of Q tiles -> buffer q_seq % 3
+                bool ok = true;
+                auto load_q = [&](const Item& w, int t) {
+                    if (w.nblk[t] == 0 || !ok) return;
+                    const int b = q_seq % kQBufs, use = q_seq / kQBufs;
+                    // the tile that used this buffer before must have had its last QK issued and retired
+                    if (use > 0) ok = mbar_wait(&bar->q_free[b], (use - 1) & 1, abort_flag, 0x110 + b);
+                    if (!ok) return;
+                    ++q_seq;
+                    mbar_arrive_expect_tx(&bar->q_full[b], C::kTileBytes);
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    uint32_t off = (kk >> 2) * C::kHalfBytes + (kk & 3) * 32;
-                    uint64_t a = make_smem_desc_sw128(q_addr + t * C::kTileBytes + off, 16, 1024);
-                    uint64_t bd = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes + off, 16, 1024);
-                    umma_ss(tmem_s(t), a, bd, idesc_qk, kk > 0 ? 1u : 0u);
-                }
-            };
-            auto issue_pv = [&](int t, int slot, bool accumulate) {
+                    for (int h = 0; h < C::kHalves; ++h)
+                        tma_load_4d(q_smem + b * C::kTileBytes + h * C::kHalfBytes, &maps.q, &bar->q_full[b], h * 64, w.r0[t], w.hq, w.b);
+                };
+                int round = 0;
+                int idx = -1;
+                while (round < n_rounds && (idx = item_of_round(round, n_items)) < 0) ++round;
+                Item w;
+                if (idx >= 0) { w = get_item(p, idx, n_bh, n_pairs); load_q(w, 0); load_q(w, 1); }
+                while (idx >= 0 && ok) {
+                    // look one item ahead so its first Q tile streams in (and gets rotated) during this item
+                    int round2 = round + 1, idx2 = -1;
+                    while (round2 < n_rounds && (idx2 = item_of_round(round2, n_items)) < 0) ++round2;
+                    Item wn;
+                    if (idx2 >= 0) { wn = get_item(p, idx2, n_bh, n_pairs); load_q(wn, 0); }
+                    for (int x = 0; x < 2 * w.nmax && ok; ++x, ++kv_item) {     // x = 2j: K_j, 2j+1: V_j
+                        const int slot = kv_item % kStages;
+                        if (kv_item >= kStages) ok = mbar_wait(&bar->kv_empty[slot], ((kv_item / kStages) - 1) & 1, abort_flag, 0x100);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(&bar->kv_full[slot], C::kTileBytes);
+                        const CUtensorMap* m = (x & 1) ? &maps.v : &maps.k;
 #pragma unroll
-                for (int kk = 0; kk < kBlockN / 16; ++kk) {
-                    // V tile is MN-major for this product: 16 keys = 2048 bytes per step,
-                    // second 64-column box one half-tile further (leading offset)
-                    uint64_t bd = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes + kk * 2048, C::kHalfBytes, 1024);
-                    umma_ts(tmem_o(t), tmem_s(t) + kk * 8, bd, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
-                }
-            };
-            bool ok = true;
-            if (nmax > 0) {
-                ok = mbar_wait(&bar->kv_full[0], 0, abort_flag, 0x200);
-                for (int t = 0; t < 2 && ok; ++t) {
-                    if (nblk[t] == 0) continue;
-                    ok = mbar_wait(&bar->q_ready[t], 0, abort_flag, 0x210 + t);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_qk(t, 0);
-                    umma_commit(&bar->s_full[t]);
-                }
-                if (ok) umma_commit(&bar->kv_empty[0]);
-            }
-            for (int j = 0; j < nmax && ok; ++j) {
-                const int v_item = 2 * j + 1, k_item = 2 * j + 2;
-                const int v_slot = v_item % kStages, k_slot = k_item % kStages;
-                ok = mbar_wait(&bar->kv_full[v_slot], (v_item / kStages) & 1, abort_flag, 0x300 + j);
-                bool k_ready = false;
-                for (int t = 0; t < 2 && ok; ++t) {
-                    if (j >= nblk[t]) continue;
-                    ok = mbar_wait(&bar->p_ready[t], j & 1, abort_flag, 0x400 + 2 * j + t);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_pv(t, v_slot, j > 0);
-                    umma_commit(&bar->o_done[t]);
-                    if (j + 1 < nblk[t]) {
-                        if (!k_ready) {
-                            ok = mbar_wait(&bar->kv_full[k_slot], (k_item / kStages) & 1, abort_flag, 0x500 + j);
-                            if (!ok) break;
-                            tc_fence_after();
-                            k_ready = true;
-                        }
-                        issue_qk(t, k_slot);
-                        umma_commit(&bar->s_full[t]);
+                        for (int h = 0; h < C::kHalves; ++h)
+                            tma_load_4d(kv_smem + slot * C::kTileBytes + h * C::kHalfBytes, m, &bar->kv_full[slot], h * 64, (x >> 1) * kBlockN, w.hkv, w.b);
                     }
+                    // the second tile of the next item reuses the buffer this item's first tile frees
+                    if (idx2 >= 0) load_q(wn, 1);
+                    idx = idx2; round = round2; w = wn;
                 }
-                if (!ok) break;
-                umma_commit(&bar->kv_empty[v_slot]);
-                if (j + 1 < nmax) umma_commit(&bar->kv_empty[k_slot]);
             }
-            // everything issued so far has to retire before TMEM is released
-            umma_commit(&bar->mma_done);
-            mbar_wait(&bar->mma_done, 0, abort_flag, 0x600);
+        } else if (warp == kMmaWarp) {
+            // =========================== MMA issuer ===========================
+            if (lane == 0) {
+                constexpr uint32_t idesc_qk = make_idesc_f16(Elem<T>::kFormat, 0, 0, kBlockM, kBlockN);
+                constexpr uint32_t idesc_pv = make_idesc_f16(Elem<T>::kFormat, 0, 1, kBlockM, D);
+                const uint32_t q_addr = smem_u32(q_smem), kv_addr = smem_u32(kv_smem);
+                auto tmem_s = [&](int t) { return tmem_base + static_cast<uint32_t>(t * 128); };
+                auto tmem_o = [&](int t) { return tmem_base + static_cast<uint32_t>(256 + t * 128); };
+                auto issue_qk = [&](int t, int qbuf, int slot) {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        uint32_t off = (kk >> 2) * C::kHalfBytes + (kk & 3) * 32;
+                        uint64_t a = make_smem_desc_sw128(q_addr + qbuf * C::kTileBytes + off, 16, 1024);
+                        uint64_t bd = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes + off, 16, 1024);
+                        umma_ss(tmem_s(t), a, bd, idesc_qk, kk > 0 ? 1u : 0u);
+                    }
+                };
+                auto issue_pv = [&](int t, int slot, bool accumulate) {
+#pragma unroll
+                    for (int kk = 0; kk < kBlockN / 16; ++kk) {
+                        // V tile is MN-major for this product: 16 keys = 2048 bytes per step,
+                        // second 64-column box one half-tile further (leading offset)
+                        uint64_t bd = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes + kk * 2048, C::kHalfBytes, 1024);
+                        umma_ts(tmem_o(t), tmem_s(t) + kk * 8, bd, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+                    }
+                };
+                int kv_item = 0, q_seq = 0;
+                int blk0 = 0, blk1 = 0;          // running count of score tiles per query tile (barrier phases)
+                bool ok = true;
+                int item_no = -1;
+                for (int round = 0; round < n_rounds && ok; ++round) {
+                    const int idx = item_of_round(round, n_items);
+                    if (idx < 0) continue;
+                    ++item_no;
+                    const Item w = get_item(p, idx, n_bh, n_pairs);
+                    int qbuf[2] = {0, 0};
+                    const int k0_slot = kv_item % kStages;
+                    long long tm0 = clock64();
+                    VB_T(0, tm0);
+                    ok = mbar_wait(&bar->kv_full[k0_slot], (kv_item / kStages) & 1, abort_flag, 0x200);
+                    VB_T(1, clock64() - tm0);
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (w.nblk[t] == 0 || !ok) continue;
+                        qbuf[t] = q_seq % kQBufs;
+                        const int ph = (q_seq / kQBufs) & 1;
+                        ++q_seq;
+                        // S of this tile is free: every PV of the previous item was issued before this point
+                        long long tq0 = clock64();
+                        ok = mbar_wait(rope ? &bar->q_rot[qbuf[t]] : &bar->q_full[qbuf[t]], ph, abort_flag, 0x210 + t);
+                        VB_T(2 + t, clock64() - tq0);
+                        if (!ok) continue;
+                        tc_fence_after();
+                        issue_qk(t, qbuf[t], k0_slot);
+                        umma_commit(&bar->s_full[t]);
+                        if (w.nblk[t] == 1) umma_commit(&bar->q_free[qbuf[t]]);
+                    }
+                    if (!ok) break;
+                    umma_commit(&bar->kv_empty[k0_slot]);
+                    for (int j = 0; j < w.nmax && ok; ++j) {
+                        const int v_item = kv_item + 2 * j + 1, k_item = kv_item + 2 * j + 2;
+                        const int v_slot = v_item % kStages, k_slot = k_item % kStages;
+                        ok = mbar_wait(&bar->kv_full[v_slot], (v_item / kStages) & 1, abort_flag, 0x300);
+                        bool k_ready = false;
+#pragma unroll
+                        for (int t = 0; t < 2; ++t) {
+                            if (j >= w.nblk[t] || !ok) continue;
+                            int& blk = t ? blk1 : blk0;
+                            ok = mbar_wait(&bar->p_ready[t], blk & 1, abort_flag, 0x400 + t);
+                            if (!ok) continue;
+                            ++blk;
+                            tc_fence_after();
+                            issue_pv(t, v_slot, j > 0);
+                            umma_commit(&bar->o_done[t]);
+                            if (j + 1 < w.nblk[t]) {
+                                if (!k_ready) {
+                                    ok = mbar_wait(&bar->kv_full[k_slot], (k_item / kStages) & 1, abort_flag, 0x500);
+                                    if (!ok) continue;
+                                    tc_fence_after();
+                                    k_ready = true;
+                                }
+                                issue_qk(t, qbuf[t], k_slot);
+                                umma_commit(&bar->s_full[t]);
+                                if (j + 2 == w.nblk[t]) umma_commit(&bar->q_free[qbuf[t]]);   // last QK of this tile
+                            }
+                        }
+                        if (!ok) break;
+                        umma_commit(&bar->kv_empty[v_slot]);
+                        if (j + 1 < w.nmax) umma_commit(&bar->kv_empty[k_slot]);
+                    }
+                    kv_item += 2 * w.nmax;
+                    VB_T(4, clock64() - tm0);
+                    VB_T(5, w.nmax);
+                }
+                // everything issued so far has to retire before TMEM is released
+                umma_commit(&bar->mma_done);
+                mbar_wait(&bar->mma_done, 0, abort_flag, 0x600);
+            }
+            __syncwarp();
+        } else if (rope) {
+            // =========================== RoPE of the Q tiles ===========================
+            // 2 warps; warp w owns rows [64w, 64w+64) of each tile.  A step handles two rows: lane l
+            // takes 16-byte chunk (l & 15) of row 2*step + (l >> 4), so the (cos,sin) table reads of a
+            // warp are two contiguous 512-byte rows and the swizzled smem accesses are conflict-free.
+            const int rw = warp - kRopeWarp0;
+            const int c = lane & 15;                          // 16-byte chunk of the row (D = 128: 16 chunks)
+            constexpr int kRopeSeed = 8;                      // steps (of two rows) between exact table reads
+            float step_c[4], step_s[4];                       // rotation by two positions for this lane's 4 pairs
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sincosf(2.0f * p.inv_freq.v[(c * 4 + e) & (kMaxHalfDim - 1)], &step_s[e], &step_c[e]);
+            int q_seq = 0;
+            bool ok = true;
+            int item_no = -1;
+            for (int round = 0; round < n_rounds && ok; ++round) {
+                const int idx = item_of_round(round, n_items);
+                if (idx < 0) continue;
+                ++item_no;
+                const Item w = get_item(p, idx, n_bh, n_pairs);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (w.nblk[t] == 0 || !ok) continue;
+                    const int b = q_seq % kQBufs, ph = (q_seq / kQBufs) & 1;
+                    ++q_seq;
+                    long long tr0 = clock64();
+                    ok = mbar_wait_warp(&bar->q_full[b], ph, abort_flag, 0x700 + b);
+                    long long tr1 = clock64();
+                    if (tid == kRopeWarp0 * 32) { VB_T(6 + 4 * t, tr0); VB_T(7 + 4 * t, tr1 - tr0); }
+                    if (!ok) continue;
+                    if (c < D / 8) {
+                        unsigned char* qtile = q_smem + b * C::kTileBytes + (c >> 3) * C::kHalfBytes;
+                        // A lane walks rows r, r+2, r+4, ... of its chunk.  The (cos,sin) of a row come from
+                        // the exact table every kRopeSeed steps and from a rotation by 2*f in between
+                        // (angle-addition recurrence), which cuts the table traffic by kRopeSeed.
+                        const int r_first = rw * 64 + (lane >> 4);
+                        float4 seed0, seed1;
+                        {
+                            const int row = min(w.r0[t] + r_first, p.T - 1);
+                            const float4* tab = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(row) * (D / 2)) + c * 2;
+                            seed0 = __ldg(tab); seed1 = __ldg(tab + 1);
+                        }
+#pragma unroll 1
+                        for (int s0 = 0; s0 < 32; s0 += kRopeSeed) {
+                            float cs[4] = {seed0.x, seed0.z, seed1.x, seed1.z};
+                            float sn[4] = {seed0.y, seed0.w, seed1.y, seed1.w};
+                            if (s0 + kRopeSeed < 32) {             // prefetch the next exact seed
+                                const int row = min(w.r0[t] + r_first + 2 * (s0 + kRopeSeed), p.T - 1);
+                                const float4* tab = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(row) * (D / 2)) + c * 2;
+                                seed0 = __ldg(tab); seed1 = __ldg(tab + 1);
+                            }
+#pragma unroll
+                            for (int i = 0; i < kRopeSeed; ++i) {
+                                const int r = r_first + 2 * (s0 + i);
+                                uint4* ptr = reinterpret_cast<uint4*>(qtile + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+                                uint4 raw = *ptr;
+                                uint32_t* u = &raw.x;
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    float2 x = Elem<T>::unpack2(u[e]);
+                                    float t1 = __fmul_rn(x.x, cs[e]), t2 = __fmul_rn(x.y, sn[e]);
+                                    float t3 = __fmul_rn(x.x, sn[e]), t4 = __fmul_rn(x.y, cs[e]);
+                                    u[e] = Elem<T>::pack2(__fsub_rn(t1, t2), __fadd_rn(t3, t4));
+                                    // advance this pair's angle by two positions
+                                    const float cn = fmaf(cs[e], step_c[e], -sn[e] * step_s[e]);
+                                    sn[e] = fmaf(sn[e], step_c[e], cs[e] * step_s[e]);
+                                    cs[e] = cn;
+                                }
+                                *ptr = raw;                     // rows past T are zero: rotating them is harmless
+                            }
+                        }
+                    }
+                    fence_proxy_async_smem();        // generic-proxy writes -> visible to the tensor core's smem reads
+                    mbar_arrive(&bar->q_rot[b]);
+                    if (tid == kRopeWarp0 * 32) { VB_T(8 + 4 * t, clock64() - tr1); VB_T(9 + 4 * t, clock64()); }
+                }
+            }
         }
-        __syncwarp();
     } else {
         // =========================== softmax / correction / epilogue ===========================
+        reg_inc<VB_REG_SOFTMAX>();
         const int t = warp >> 2;                     // tile of this warpgroup
         const int r = tid & 127;                     // row inside the tile = TMEM lane
-        const int row = r0[t] + r;                   // query row in [0, T)
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t s_addr = tmem_base + lane_base + static_cast<uint32_t>(t * 128);
         const uint32_t o_addr = tmem_base + lane_base + static_cast<uint32_t>(256 + t * 128);
-        const int n = nblk[t];
-        bool ok = true;
-
-        if (n > 0) {
-            ok = mbar_wait_warp(&bar->q_full[t], 0, abort_flag, 0x700 + t);
-            if (ok && p.q_rope_table != nullptr && row < p.T) {
-                // rotate this thread's row of the swizzled Q tile in place
-                const float2* tab = p.q_rope_table + static_cast<long long>(row) * (D / 2);
-                unsigned char* qrow = q_smem + t * C::kTileBytes + r * 128;
-#pragma unroll
-                for (int c = 0; c < D / 8; ++c) {
-                    uint4* ptr = reinterpret_cast<uint4*>(qrow + (c >> 3) * C::kHalfBytes + (((c & 7) ^ (r & 7)) << 4));
-                    uint4 raw = *ptr;
-                    uint32_t* u = &raw.x;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float2 x = Elem<T>::unpack2(u[i]);
-                        float2 cs = __ldg(tab + c * 4 + i);
-                        float t1 = __fmul_rn(x.x, cs.x), t2 = __fmul_rn(x.y, cs.y);
-                        float t3 = __fmul_rn(x.x, cs.y), t4 = __fmul_rn(x.y, cs.x);
-                        u[i] = Elem<T>::pack2(__fsub_rn(t1, t2), __fadd_rn(t3, t4));
-                    }
-                    *ptr = raw;
-                }
-                fence_proxy_async_smem();
-            }
-            mbar_arrive(&bar->q_ready[t]);
-        }
-
         const float scale_log2 = p.scale * kLog2e;
-        float m_ref = -INFINITY, l_sum = 0.f;
+        int g = 0;                                   // running count of score tiles of this query tile
+        bool ok = true;
+        int item_no = -1;
 
-        for (int j = 0; j < n && ok; ++j) {
-            ok = mbar_wait_warp(&bar->s_full[t], j & 1, abort_flag, 0x800 + 2 * j + t);
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t s[4][32];
+        for (int round = 0; round < n_rounds && ok; ++round) {
+            const int idx = item_of_round(round, n_items);
+            if (idx < 0) continue;
+            ++item_no;
+            const Item w = get_item(p, idx, n_bh, n_pairs);
+            long long t_wait = 0, t_comp = 0, t_epi = 0;
+            const int n = t ? w.nblk[1] : w.nblk[0];
+            if (n == 0) continue;
+            const int tile_r0 = t ? w.r0[1] : w.r0[0];
+            const int row = tile_r0 + r;             // query row in [0, T)
+
+            float m_ref = -INFINITY, l_sum = 0.f;
+            for (int j = 0; j < n; ++j, ++g) {
+#ifdef VB_TIMING
+                long long ta = clock64();
+#endif
+                ok = mbar_wait_warp(&bar->s_full[t], g & 1, abort_flag, 0x800 + t);
+                if (!ok) break;
+#ifdef VB_TIMING
+                long long tb_ = clock64();
+                t_wait += tb_ - ta;
+#endif
+                tc_fence_after();
+                uint32_t s[4][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
-            tmem_ld_wait();
+                for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
+                tmem_ld_wait();
 
-            const int k0 = j * kBlockN;
-            const bool need_mask = (k0 + kBlockN > p.Skv) || (p.causal && (k0 + kBlockN - 1 > p.start_pos + r0[t]));
-            if (need_mask) {
-                const int limit = p.causal ? min(p.Skv - 1, p.start_pos + row) : p.Skv - 1;   // last visible key
+                const int k0 = j * kBlockN;
+                const bool need_mask = (k0 + kBlockN > p.Skv) || (p.causal && (k0 + kBlockN - 1 > p.start_pos + tile_r0));
+                if (need_mask) {
+                    const int limit = p.causal ? min(p.Skv - 1, p.start_pos + row) : p.Skv - 1;   // last visible key
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (k0 + c * 32 + i > limit) s[c][i] = 0xFF800000u;   // -inf
+                }
+                // row max: 8 independent chains of 3-input max (one thread owns the whole row)
+                float mx8[8];
+#pragma unroll
+                for (int a = 0; a < 8; ++a) mx8[a] = -INFINITY;
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (k0 + c * 32 + i > limit) s[c][i] = 0xFF800000u;   // -inf
-            }
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
-            const float m_cand = mx * scale_log2;
-            const bool grow = m_cand > m_ref + kRescaleThreshold;      // true on the first block
-            if (__any_sync(0xFFFFFFFFu, grow)) {
-                const float m_new = grow ? m_cand : m_ref;
-                const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
-                if (j > 0) {
-                    // all PV products issued so far for this tile must have landed in O
-                    ok = mbar_wait_warp(&bar->o_done[t], (j - 1) & 1, abort_flag, 0x900 + 2 * j + t);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(o_addr + c * 32, o);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(o_addr + c * 32, o);
+                    for (int i = 0; i < 32; i += 2) {
+#if VB_MAX3
+                        mx8[(i >> 1) & 7] = fmax3(mx8[(i >> 1) & 7], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+#else
+                        mx8[(i >> 1) & 7] = fmaxf(mx8[(i >> 1) & 7], fmaxf(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
+#endif
                     }
-                    tmem_st_wait();
+                const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+                const float m_cand = mx * scale_log2;
+                const bool grow = m_cand > m_ref + kRescaleThreshold;      // true on the first block of an item
+                if (__any_sync(0xFFFFFFFFu, grow)) {
+                    const float m_new = grow ? m_cand : m_ref;
+                    const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
+                    if (j > 0) {
+                        // all PV products issued so far for this tile must have landed in O
+                        ok = mbar_wait_warp(&bar->o_done[t], (g - 1) & 1, abort_flag, 0x900 + t);
+                        if (!ok) break;
+                        tc_fence_after();
+#pragma unroll
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t o[32];
+                            tmem_ld32(o_addr + c * 32, o);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(o_addr + c * 32, o);
+                        }
+                        tmem_st_wait();
+                    }
+                    l_sum *= alpha;
+                    m_ref = m_new;
                 }
-                l_sum *= alpha;
-                m_ref = m_new;
-            }
-            // p = 2^(s*scale*log2e - m_ref); packed to 16 bit two per column
-            float row_sum = 0.f;
-            uint32_t pk[2][32];
+                // p = 2^(s*scale*log2e - m_ref); packed to 16 bit two per column
+                float2 rs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+                const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_ref, -m_ref);
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t pk[32];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), scale_log2, -m_ref));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, -m_ref));
-                    row_sum += p0 + p1;
-                    pk[c >> 1][(c & 1) * 16 + (i >> 1)] = Elem<T>::pack2(p0, p1);
-                }
-            l_sum += row_sum;
-            tmem_st32(s_addr, pk[0]);
-            tmem_st32(s_addr + 32, pk[1]);
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(&bar->p_ready[t]);
-        }
-
-        if (n > 0 && ok) {
-            ok = mbar_wait_warp(&bar->o_done[t], (n - 1) & 1, abort_flag, 0xA00 + t);
-            if (ok) {
-                tc_fence_after();
-                const float inv_l = 1.0f / l_sum;
-                T* orow = static_cast<T*>(p.o.ptr) + b * p.o.sb + hq * p.o.sh + static_cast<long long>(row) * p.o.ss;
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int c = 2 * half + cc;
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t o[32];
-                    tmem_ld32(o_addr + c * 32, o);
-                    tmem_ld_wait();
-                    if (row < p.T) {
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint4 out;
-                            out.x = Elem<T>::pack2(__uint_as_float(o[8 * v + 0]) * inv_l, __uint_as_float(o[8 * v + 1]) * inv_l);
-                            out.y = Elem<T>::pack2(__uint_as_float(o[8 * v + 2]) * inv_l, __uint_as_float(o[8 * v + 3]) * inv_l);
-                            out.z = Elem<T>::pack2(__uint_as_float(o[8 * v + 4]) * inv_l, __uint_as_float(o[8 * v + 5]) * inv_l);
-                            out.w = Elem<T>::pack2(__uint_as_float(o[8 * v + 6]) * inv_l, __uint_as_float(o[8 * v + 7]) * inv_l);
-                            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = out;
+                        for (int i = 0; i < 32; i += 2) {
+#if VB_PACKED_MATH
+                            // packed fp32x2: one FMA and one add per pair of columns
+                            const float2 e = __ffma2_rn(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nm2);
+                            const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+                            rs[(i >> 1) & 3] = __fadd2_rn(rs[(i >> 1) & 3], pp);
+#else
+                            const float2 pp = make_float2(fast_exp2(fmaf(__uint_as_float(s[c][i]), sc2.x, nm2.x)),
+                                                          fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), sc2.x, nm2.x)));
+                            rs[(i >> 1) & 3].x += pp.x;
+                            rs[(i >> 1) & 3].y += pp.y;
+#endif
+                            pk[cc * 16 + (i >> 1)] = Elem<T>::pack2(pp.x, pp.y);
                         }
                     }
+                    tmem_st32(s_addr + half * 32, pk);
                 }
-                if (p.lse != nullptr && row < p.T)
-                    p.lse[(static_cast<long long>(b) * p.Hq + hq) * p.T + row] = (m_ref + fast_log2(l_sum)) * kLn2;
+                l_sum += ((rs[0].x + rs[0].y) + (rs[1].x + rs[1].y)) + ((rs[2].x + rs[2].y) + (rs[3].x + rs[3].y));
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(&bar->p_ready[t]);
+#ifdef VB_TIMING
+                t_comp += clock64() - tb_;
+#endif
             }
+            if (!ok) break;
+#ifdef VB_TIMING
+            long long te0 = clock64();
+#endif
+
+            // ---- epilogue of this item: O / l -> global, LSE ----
+            ok = mbar_wait_warp(&bar->o_done[t], (g - 1) & 1, abort_flag, 0xA00 + t);
+            if (!ok) break;
+            tc_fence_after();
+            const float inv_l = 1.0f / l_sum;
+            T* orow = static_cast<T*>(p.o.ptr) + w.b * p.o.sb + w.hq * p.o.sh + static_cast<long long>(row) * p.o.ss;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(o_addr + c * 32, o);
+                tmem_ld_wait();
+                if (row < p.T) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 out;
+                        out.x = Elem<T>::pack2(__uint_as_float(o[8 * v + 0]) * inv_l, __uint_as_float(o[8 * v + 1]) * inv_l);
+                        out.y = Elem<T>::pack2(__uint_as_float(o[8 * v + 2]) * inv_l, __uint_as_float(o[8 * v + 3]) * inv_l);
+                        out.z = Elem<T>::pack2(__uint_as_float(o[8 * v + 4]) * inv_l, __uint_as_float(o[8 * v + 5]) * inv_l);
+                        out.w = Elem<T>::pack2(__uint_as_float(o[8 * v + 6]) * inv_l, __uint_as_float(o[8 * v + 7]) * inv_l);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = out;
+                    }
+                }
+            }
+            // O has been read out: the next item's first PV (issued only after this thread's next
+            // p_ready arrival) may overwrite it
+            tc_fence_before();
+            if (p.lse != nullptr && row < p.T)
+                p.lse[(static_cast<long long>(w.b) * p.Hq + w.hq) * p.T + row] = (m_ref + fast_log2(l_sum)) * kLn2;
+#ifdef VB_TIMING
+            t_epi = clock64() - te0;
+            if ((tid & 127) == 0) { VB_T(14 - 4 * t, t_wait); VB_T(15 - 4 * t, t_comp); if (t == 1) VB_T(9, t_epi); }
+#endif
+            (void)t_wait; (void)t_comp; (void)t_epi;
         }
     }
 
@@ -402,7 +620,11 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
         configured_dev = dev;
     }
     const int n_pairs = (p.T + 2 * kBlockM - 1) / (2 * kBlockM);
-    dim3 grid(static_cast<unsigned>(n_pairs) * p.B * p.Hq);
+    const int n_items = n_pairs * p.B * p.Hq;
+    int sms = 0;
+    VB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    // persistent: one CTA per SM walks the work items (heaviest first, round-robin)
+    dim3 grid(static_cast<unsigned>(n_items < sms ? n_items : sms));
     profile_mark_begin(s);
     prefill_sm100_kernel<T, D><<<grid, kThreads, Cfg<D>::kSmemBytes, s>>>(maps, p);
     profile_mark_end(s);
@@ -412,6 +634,13 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
 }
 
 }  // namespace
+
+#ifdef VB_TIMING
+extern "C" int vb200_debug_set_timing_buffer(void* buf) {
+    long long* b = static_cast<long long*>(buf);
+    return cudaMemcpyToSymbol(g_timing_buf, &b, sizeof(b)) == cudaSuccess ? 0 : -5;
+}
+#endif
 
 int launch_prefill_sm100(cudaStream_t s, const PrefillParams& p) {
     if (p.D != 128 && p.D != 64) return set_detail(VB200_ERR_UNSUPPORTED, "bf16/fp16 attention supports head_dim 64 and 128");
