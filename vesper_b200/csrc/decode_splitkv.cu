@@ -18,10 +18,7 @@ namespace vb200 {
 
 namespace {
 
-constexpr int kTile = 64;        // keys per pipeline stage
-constexpr int kStages = 3;
-constexpr int kConsumerWarps = 4;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;   // + 1 producer warp
+constexpr int kTile = 64;        // keys per pipeline stage (K 16 KB + V 16 KB)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale O only when the max grows by > 2^8
@@ -44,8 +41,8 @@ __device__ __forceinline__ float group16_reduce_scatter(float (&vals)[16], int l
 
 template <typename T, int NREP>
 struct WarpState {
-    float q[NREP][8];     // rotated q * scale * log2(e), this lane's 8 dims
-    float o[NREP][8];     // unnormalised output accumulator
+    float2 q[NREP][4];    // rotated q * scale * log2(e), this lane's 8 dims as 4 pairs
+    float2 o[NREP][4];    // unnormalised output accumulator
     float m;              // running reference max (log2 units) of this lane's head
     float l;              // partial sum of p for this lane's (head, key slot)
 };
@@ -55,7 +52,7 @@ struct WarpState {
 // in slices of 2*KB keys (KB = 16/NREP keys per half-warp group and batch);
 // `wslot` in [0, nwslots).  The loop trip count is warp-uniform (both
 // half-warps run the same iterations; rows past nkeys are masked) because the
-// body uses full-warp shuffles.
+// body uses full-warp shuffles.  All multiply-adds are packed fp32x2.
 // KF32: the K rows are fp32 (used for the new token, whose rotated key is
 // scored at full precision in the step that appends it).
 template <typename T, int NREP, bool KF32 = false>
@@ -70,27 +67,28 @@ __device__ __forceinline__ void process_rows(WarpState<T, NREP>& st, const void*
 #pragma unroll
         for (int kk = 0; kk < KB; ++kk) {
             int key = base + kk;
-            float kf[8];
+            float2 kf[4];
             if constexpr (KF32) {
                 float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
                 if (key < nkeys) {
                     const float* kp = static_cast<const float*>(ksm_raw) + key * 128 + l16 * 8;
                     a0 = *reinterpret_cast<const float4*>(kp); a1 = *reinterpret_cast<const float4*>(kp + 4);
                 }
-                kf[0] = a0.x; kf[1] = a0.y; kf[2] = a0.z; kf[3] = a0.w; kf[4] = a1.x; kf[5] = a1.y; kf[6] = a1.z; kf[7] = a1.w;
+                kf[0] = make_float2(a0.x, a0.y); kf[1] = make_float2(a0.z, a0.w);
+                kf[2] = make_float2(a1.x, a1.y); kf[3] = make_float2(a1.z, a1.w);
             } else {
                 uint4 raw = make_uint4(0, 0, 0, 0);
                 if (key < nkeys) raw = *reinterpret_cast<const uint4*>(static_cast<const T*>(ksm_raw) + key * 128 + l16 * 8);
                 const uint32_t* u = &raw.x;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { float2 t = Elem<T>::unpack2(u[i]); kf[2 * i] = t.x; kf[2 * i + 1] = t.y; }
+                for (int i = 0; i < 4; ++i) kf[i] = Elem<T>::unpack2(u[i]);
             }
 #pragma unroll
             for (int h = 0; h < NREP; ++h) {
-                float a = 0.f;
+                float2 a = __fmul2_rn(st.q[h][0], kf[0]);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) a = fmaf(st.q[h][i], kf[i], a);
-                vals[kk * NREP + h] = a;
+                for (int i = 1; i < 4; ++i) a = __ffma2_rn(st.q[h][i], kf[i], a);
+                vals[kk * NREP + h] = a.x + a.y;
             }
         }
         float s = group16_reduce_scatter(vals, l16);       // score (log2 units) of (key my_k, head my_h)
@@ -109,8 +107,9 @@ __device__ __forceinline__ void process_rows(WarpState<T, NREP>& st, const void*
             for (int h = 0; h < NREP; ++h) {
                 // lane h of the group holds head h (key slot 0)
                 float ah = __shfl_sync(0xFFFFFFFFu, alpha, (threadIdx.x & 16) + h);
+                const float2 ah2 = make_float2(ah, ah);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) st.o[h][i] *= ah;
+                for (int i = 0; i < 4; ++i) st.o[h][i] = __fmul2_rn(st.o[h][i], ah2);
             }
         }
         float p = (s == -INFINITY) ? 0.f : fast_exp2(s - st.m);
@@ -122,15 +121,28 @@ __device__ __forceinline__ void process_rows(WarpState<T, NREP>& st, const void*
             int key = base + kk;
             if (key < nkeys) {
                 uint4 raw = *reinterpret_cast<const uint4*>(vsm + key * 128 + l16 * 8);
-                float vf[8];
+                float2 vf[4];
                 const uint32_t* u = &raw.x;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { float2 t = Elem<T>::unpack2(u[i]); vf[2 * i] = t.x; vf[2 * i + 1] = t.y; }
+                for (int i = 0; i < 4; ++i) vf[i] = Elem<T>::unpack2(u[i]);
+                float ph[NREP];
+                if constexpr (NREP == 8) {
+                    float4 x = *reinterpret_cast<const float4*>(pbuf + kk * 8), y = *reinterpret_cast<const float4*>(pbuf + kk * 8 + 4);
+                    ph[0] = x.x; ph[1] = x.y; ph[2] = x.z; ph[3] = x.w; ph[4] = y.x; ph[5] = y.y; ph[6] = y.z; ph[7] = y.w;
+                } else if constexpr (NREP == 4) {
+                    float4 x = *reinterpret_cast<const float4*>(pbuf + kk * 4);
+                    ph[0] = x.x; ph[1] = x.y; ph[2] = x.z; ph[3] = x.w;
+                } else if constexpr (NREP == 2) {
+                    float2 x = *reinterpret_cast<const float2*>(pbuf + kk * 2);
+                    ph[0] = x.x; ph[1] = x.y;
+                } else {
+                    ph[0] = pbuf[kk];
+                }
 #pragma unroll
                 for (int h = 0; h < NREP; ++h) {
-                    float ph = pbuf[kk * NREP + h];
+                    const float2 p2 = make_float2(ph[h], ph[h]);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) st.o[h][i] = fmaf(ph, vf[i], st.o[h][i]);
+                    for (int i = 0; i < 4; ++i) st.o[h][i] = __ffma2_rn(p2, vf[i], st.o[h][i]);
                 }
             }
         }
@@ -138,6 +150,7 @@ __device__ __forceinline__ void process_rows(WarpState<T, NREP>& st, const void*
     }
 }
 
+template <int CW, int kStages>
 struct __align__(16) DecodeSmem {
     uint64_t full[kStages];
     uint64_t empty[kStages];
@@ -147,19 +160,22 @@ struct __align__(16) DecodeSmem {
 
 // Dynamic shared memory layout (D = 128, 16-bit T):
 //   [0, kStages * 2 * kTile * 256)   K/V ring: stage s -> K at s*32 KB, V at s*32 KB + 16 KB
-//   then 2 rows (rotated new k, new v), then the per-group p buffers, then DecodeSmem.
-template <typename T, int NREP>
-__global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p) {
+//   then the new token's rotated key (fp32) and value, the per-group p buffers, DecodeSmem.
+// CW = consumer warps (one more warp streams the tiles); kStages = ring depth;
+// MINB = CTAs per SM the register allocation is sized for.
+template <typename T, int NREP, int CW, int kStages, int MINB>
+__global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(DecodeParams p) {
     constexpr int D = 128;
     constexpr int kRowBytes = D * sizeof(T);
     constexpr int kStageBytes = 2 * kTile * kRowBytes;
     constexpr int kNewBytes = D * sizeof(float) + kRowBytes;
+    constexpr int kGroups = 2 * CW;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     T* ring = reinterpret_cast<T*>(smem_raw);
     float* newk = reinterpret_cast<float*>(smem_raw + kStages * kStageBytes);   // rotated new key, fp32 [128]
     T* newv = reinterpret_cast<T*>(smem_raw + kStages * kStageBytes + kNewBytes - kRowBytes);   // new value [128]
-    float* pbuf_all = reinterpret_cast<float*>(smem_raw + kStages * kStageBytes + kNewBytes);   // [8][16]
-    DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem_raw + kStages * kStageBytes + kNewBytes + 8 * 16 * sizeof(float));
+    float* pbuf_all = reinterpret_cast<float*>(smem_raw + kStages * kStageBytes + kNewBytes);   // [kGroups][16]
+    DecodeSmem<CW, kStages>* sm = reinterpret_cast<DecodeSmem<CW, kStages>*>(smem_raw + kStages * kStageBytes + kNewBytes + kGroups * 16 * sizeof(float));
 
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, l16 = lane & 15;
@@ -178,7 +194,7 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p
     const int ntiles = (k_end > k_begin) ? (k_end - k_begin + kTile - 1) / kTile : 0;
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], kConsumerWarps); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], CW); }
         sm->abort_flag = 0;
         mbar_fence_init();
     }
@@ -188,7 +204,7 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p
     const T* kc = static_cast<const T*>(p.k_cache.ptr) + b * p.k_cache.sb + kvh * p.k_cache.sh;
     const T* vc = static_cast<const T*>(p.v_cache.ptr) + b * p.v_cache.sb + kvh * p.v_cache.sh;
 
-    if (warp == kConsumerWarps) {
+    if (warp == CW) {
         // ---------------- producer: one lane streams K/V tiles ----------------
         if (lane == 0) {
             for (int t = 0; t < ntiles; ++t) {
@@ -210,7 +226,7 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p
 #pragma unroll
         for (int h = 0; h < NREP; ++h)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) st.o[h][i] = 0.f;
+            for (int i = 0; i < 4; ++i) st.o[h][i] = make_float2(0.f, 0.f);
 
         // rotation angles of the query / new token for this lane's 4 pairs
         float cs[4], sn[4];
@@ -233,8 +249,7 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p
                     float t3 = __fmul_rn(t.x, sn[i]), t4 = __fmul_rn(t.y, cs[i]);
                     t.x = __fsub_rn(t1, t2); t.y = __fadd_rn(t3, t4);
                 }
-                st.q[h][2 * i] = t.x * qscale;
-                st.q[h][2 * i + 1] = t.y * qscale;
+                st.q[h][i] = make_float2(t.x * qscale, t.y * qscale);
             }
         }
 
@@ -279,7 +294,7 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p
             const T* ksm = ring + static_cast<size_t>(s) * (kStageBytes / sizeof(T));
             const T* vsm = ksm + kTile * D;
             int nk = min(kTile, k_end - (k_begin + t * kTile));
-            process_rows<T, NREP>(st, ksm, vsm, nk, warp, kConsumerWarps, lane, pbuf);
+            process_rows<T, NREP>(st, ksm, vsm, nk, warp, CW, lane, pbuf);
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm->empty[s]);
         }
@@ -289,52 +304,60 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(DecodeParams p
             process_rows<T, NREP, true>(st, newk, newv, 1, 0, 1, lane, pbuf);
         }
 
-        // ---- merge the 8 groups of the CTA through shared memory (ring is free now) ----
+        // ---- merge the half-warp groups of the CTA through shared memory (the ring is free now) ----
         float l = st.l;
 #pragma unroll
         for (int off = NREP; off < 16; off <<= 1) l += __shfl_xor_sync(0xFFFFFFFFu, l, off);
-        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");   // all consumers done with the ring
-        float* go = reinterpret_cast<float*>(smem_raw);                             // [8][NREP][128]
-        float* gm = go + 8 * NREP * 128;                                            // [8][NREP]
-        float* gl = gm + 8 * NREP;                                                  // [8][NREP]
+        asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");   // all consumers done with the ring
+        float* go = reinterpret_cast<float*>(smem_raw);                             // [kGroups][NREP][128]
+        float* gm = go + kGroups * NREP * 128;                                      // [kGroups][NREP]
+        float* gl = gm + kGroups * NREP;                                            // [kGroups][NREP]
         if (l16 < NREP) { gm[group * NREP + l16] = st.m; gl[group * NREP + l16] = l; }
 #pragma unroll
         for (int h = 0; h < NREP; ++h) {
             float4* dst = reinterpret_cast<float4*>(go + (group * NREP + h) * 128 + l16 * 8);
-            dst[0] = make_float4(st.o[h][0], st.o[h][1], st.o[h][2], st.o[h][3]);
-            dst[1] = make_float4(st.o[h][4], st.o[h][5], st.o[h][6], st.o[h][7]);
+            dst[0] = make_float4(st.o[h][0].x, st.o[h][0].y, st.o[h][1].x, st.o[h][1].y);
+            dst[1] = make_float4(st.o[h][2].x, st.o[h][2].y, st.o[h][3].x, st.o[h][3].y);
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
 
         // thread d (0..127) finishes dim d of every head
-        const int d = tid;
-        float* wsp = p.workspace + p.ws_header;   // after the per-sequence length slots
-        const int nsplits = p.num_splits;
+        if (tid < 128) {
+            const int d = tid;
+            float* wsp = p.workspace + p.ws_header;   // after the per-sequence length slots
+            const int nsplits = p.num_splits;
 #pragma unroll
-        for (int h = 0; h < NREP; ++h) {
-            float M = -INFINITY;
+            for (int h = 0; h < NREP; ++h) {
+                float M = -INFINITY;
 #pragma unroll
-            for (int g = 0; g < 8; ++g) M = fmaxf(M, gm[g * NREP + h]);
-            float L = 0.f, acc = 0.f;
+                for (int g = 0; g < kGroups; ++g) M = fmaxf(M, gm[g * NREP + h]);
+                float L = 0.f, acc = 0.f;
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                float mg = gm[g * NREP + h];
-                float w = (mg == -INFINITY) ? 0.f : fast_exp2(mg - M);
-                L += gl[g * NREP + h] * w;
-                acc += go[(g * NREP + h) * 128 + d] * w;
+                for (int g = 0; g < kGroups; ++g) {
+                    float mg = gm[g * NREP + h];
+                    float w = (mg == -INFINITY) ? 0.f : fast_exp2(mg - M);
+                    L += gl[g * NREP + h] * w;
+                    acc += go[(g * NREP + h) * 128 + d] * w;
+                }
+                float* out = wsp + ((static_cast<long long>(b) * p.Hkv + kvh) * nsplits + split) * NREP * (D + 2) + h * (D + 2);
+                out[d] = acc / L;
+                if (d == 0) { out[D] = M * kLn2; out[D + 1] = L; }
             }
-            float* out = wsp + ((static_cast<long long>(b) * p.Hkv + kvh) * nsplits + split) * NREP * (D + 2) + h * (D + 2);
-            out[d] = acc / L;
-            if (d == 0) { out[D] = M * kLn2; out[D + 1] = L; }
         }
     }
 }
 
-// One block per (q_head, batch): merge the valid splits.
+// One block per (q_head, batch): merge the valid splits.  512 threads = 4 groups of 128
+// (thread d of a group owns output dim d); each group takes a quarter of the splits.
+constexpr int kCombineGroups = 4;
+
 template <typename T>
-__global__ void decode_combine_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(128 * kCombineGroups) decode_combine_kernel(DecodeParams p) {
     constexpr int D = 128;
-    const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    __shared__ float s_red[kCombineGroups * 32];
+    __shared__ float s_acc[kCombineGroups][D];
+    __shared__ float s_l[kCombineGroups];
+    const int hq = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, d = tid & 127, grp = tid >> 7;
     const int nrep = p.Hq / p.Hkv, kvh = hq / nrep, h = hq % nrep;
     const int len = reinterpret_cast<const int*>(p.workspace)[b];
     const int total = len + (p.append ? 1 : 0);
@@ -342,14 +365,37 @@ __global__ void decode_combine_kernel(DecodeParams p) {
     const float* base = p.workspace + p.ws_header +
                         ((static_cast<long long>(b) * p.Hkv + kvh) * p.num_splits) * nrep * (D + 2) + h * (D + 2);
     const long long sstride = static_cast<long long>(nrep) * (D + 2);
+
+    // global max over the splits
     float M = -INFINITY;
-    for (int s = 0; s < nsp; ++s) M = fmaxf(M, base[s * sstride + D]);
+    for (int s = tid; s < nsp; s += blockDim.x) M = fmaxf(M, base[s * sstride + D]);
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+    if ((tid & 31) == 0) s_red[tid >> 5] = M;
+    __syncthreads();
+    M = s_red[0];
+#pragma unroll
+    for (int i = 1; i < kCombineGroups * 4; ++i) M = fmaxf(M, s_red[i]);
+
+    // each group accumulates its quarter of the splits (rows of 128 floats: coalesced)
+    const int per = (nsp + kCombineGroups - 1) / kCombineGroups;
+    const int s_lo = grp * per, s_hi = min(nsp, s_lo + per);
     float L = 0.f, acc = 0.f;
-    for (int s = 0; s < nsp; ++s) {
-        float w = expf(base[s * sstride + D] - M) * base[s * sstride + D + 1];
+#pragma unroll 4
+    for (int s = s_lo; s < s_hi; ++s) {
+        const float* row = base + s * sstride;
+        float w = expf(row[D] - M) * row[D + 1];
         L += w;
-        acc += w * base[s * sstride + d];
+        acc += w * row[d];
     }
+    s_acc[grp][d] = acc;
+    if (d == 0) s_l[grp] = L;
+    __syncthreads();
+    if (grp != 0) return;
+    acc = 0.f; L = 0.f;
+#pragma unroll
+    for (int g = 0; g < kCombineGroups; ++g) { acc += s_acc[g][d]; L += s_l[g]; }
+
     float o = (nsp > 0) ? acc / L : 0.f;
     if (p.partial_out) {
         float* po = p.partial_out + (static_cast<long long>(b) * p.Hq + hq) * (D + 2);
@@ -387,22 +433,28 @@ __global__ void lse_combine_kernel(const float* __restrict__ partials, int R, lo
 template <typename T, int NREP>
 int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
     constexpr int D = 128;
-    size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + D * sizeof(float) + D * sizeof(T) + 8 * 16 * sizeof(float) + sizeof(DecodeSmem);
-    static_assert(8 * NREP * 128 * 4 + 2 * 8 * NREP * 4 <= kStages * 2 * kTile * 128 * 2, "merge buffers must fit in the ring");
+    // Measured on B200: 4 consumer warps per CTA beat 6 and 8 (fewer keys per warp and tile, costlier
+    // merge); for groups of up to 4 query heads three CTAs per SM with a 2-deep ring are fastest
+    // (128 registers suffice), 8-head groups need ~170 registers: two CTAs per SM, 3-deep ring.
+    constexpr int CW = 4;
+    constexpr int kStages = (NREP <= 4) ? 2 : 3;
+    constexpr int MINB = (NREP <= 4) ? 3 : 2;
+    size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + D * sizeof(float) + D * sizeof(T) + 2 * CW * 16 * sizeof(float) + sizeof(DecodeSmem<CW, kStages>);
+    static_assert(2 * CW * NREP * 128 * 4 + 2 * 2 * CW * NREP * 4 <= kStages * 2 * kTile * 128 * 2, "merge buffers must fit in the ring");
     static thread_local int configured_dev = -1;
     int dev = 0;
     VB200_CUDA_TRY(cudaGetDevice(&dev));
     if (configured_dev != dev) {
-        VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured_dev = dev;
     }
     dim3 grid(p.num_splits, p.Hkv, p.B);
     profile_mark_begin(s);
-    decode_splitkv_kernel<T, NREP><<<grid, kThreads, smem, s>>>(p);
+    decode_splitkv_kernel<T, NREP, CW, kStages, MINB><<<grid, (CW + 1) * 32, smem, s>>>(p);
     profile_mark_end(s);
     note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());
-    decode_combine_kernel<T><<<dim3(p.Hq, p.B), D, 0, s>>>(p);
+    decode_combine_kernel<T><<<dim3(p.Hq, p.B), 128 * kCombineGroups, 0, s>>>(p);
     note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());
     return VB200_OK;
