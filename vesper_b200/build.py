@@ -75,9 +75,34 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+HOST_DIR = os.path.join(PKG, "host")
+HOST_LIB = os.path.join(LIBDIR, "libvesper_b200_host.so")
+HOST_SOURCES = ["tensor.cpp", "attention.cpp"]
+
+
+def build_host(force: bool = False) -> str:
+    """C++17 host layer with Vesper's class and function names (vesper_b200/host) on top of the C ABI."""
+    build(force=False)
+    nvcc = _nvcc()
+    srcs = [os.path.join(HOST_DIR, "src", s) for s in HOST_SOURCES]
+    hdrs = []
+    for root, _, files in os.walk(os.path.join(HOST_DIR, "include")):
+        hdrs += [os.path.join(root, f) for f in files]
+    if force or _stale(HOST_LIB, srcs + hdrs + [LIB, os.path.join(PKG, "..", "include", "vesper_b200.h")]):
+        cmd = [nvcc, "-shared", "-std=c++17", "-O2", "-Xcompiler", "-fPIC,-Wall",
+               "-I", os.path.join(HOST_DIR, "include"), "-I", os.path.join(PKG, "..", "include")] + srcs + \
+              ["-o", HOST_LIB, "-L", LIBDIR, "-lvesper_b200", "-Xlinker", "-rpath,$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("host layer build failed")
+    return HOST_LIB
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     a = ap.parse_args()
     print(build(a.force, a.verbose))
+    print(build_host(a.force))
