@@ -57,6 +57,15 @@ constexpr float kRescaleThreshold = 8.0f;
 #ifndef VB_MAX3
 #define VB_MAX3 0              // 3-input max in the row maximum
 #endif
+#ifndef VB_TWO_PASS
+#define VB_TWO_PASS 0          // read the score tile from TMEM twice (max, then exp) instead of holding it
+#endif
+#ifndef VB_POLY_NUM
+#define VB_POLY_NUM 0          // of every VB_POLY_DEN column pairs, this many take exp2 on the FMA pipe
+#endif
+#ifndef VB_POLY_DEN
+#define VB_POLY_DEN 1
+#endif
 static_assert(VB_REG_SOFTMAX * 256 + VB_REG_OTHER * 128 <= 168 * 384, "register budget");
 
 #ifdef VB_TIMING
@@ -122,6 +131,25 @@ __device__ __forceinline__ int item_of_round(int round, int n_items) {
     const int G = gridDim.x, c = blockIdx.x;
     const int idx = round * G + ((round & 1) ? (G - 1 - c) : c);
     return idx < n_items ? idx : -1;
+}
+
+// 2^x for a pair of values on the FMA pipe instead of the special-function unit, which the
+// softmax otherwise saturates (128 ex2 per row against 16 results per clock and SM).
+// x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3 polynomial (max relative
+// error 7.5e-5, far below the 16-bit rounding of P); 2^n by adding n to the exponent field.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    const float magic = 12582912.0f;                       // 1.5 * 2^23: the sum keeps round(x) in its low mantissa bits
+    const float2 r = __fadd2_rn(x, make_float2(magic, magic));
+    const float2 n = __fadd2_rn(r, make_float2(-magic, -magic));
+    const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
+    float2 p = __ffma2_rn(f, make_float2(0.055171650f, 0.055171650f), make_float2(0.24261113f, 0.24261113f));
+    p = __ffma2_rn(p, f, make_float2(0.69326097f, 0.69326097f));
+    p = __ffma2_rn(p, f, make_float2(0.99992806f, 0.99992806f));
+    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(r.x) << 23));
+    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23));
+    return p;
 }
 
 template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
@@ -430,35 +458,47 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 t_wait += tb_ - ta;
 #endif
                 tc_fence_after();
+                const int k0 = j * kBlockN;
+                const bool need_mask = (k0 + kBlockN > p.Skv) || (p.causal && (k0 + kBlockN - 1 > p.start_pos + tile_r0));
+                const int limit = p.causal ? min(p.Skv - 1, p.start_pos + row) : p.Skv - 1;   // last visible key
+                auto mask_chunk = [&](uint32_t (&v)[32], int c) {
+                    if (need_mask) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (k0 + c * 32 + i > limit) v[i] = 0xFF800000u;   // -inf
+                    }
+                };
+                // row max: 8 independent chains (one thread owns the whole row)
+                float mx8[8];
+#pragma unroll
+                for (int a = 0; a < 8; ++a) mx8[a] = -INFINITY;
+                auto max_chunk = [&](const uint32_t (&v)[32]) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2)
+                        mx8[(i >> 1) & 7] = fmaxf(mx8[(i >> 1) & 7], fmaxf(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+                };
+#if VB_TWO_PASS
+                // Pass 1 reads the score tile from TMEM chunk by chunk for the maximum only; pass 2
+                // reads it again for the exponentials.  Only two 32-column chunks are live at a time,
+                // so the row never has to sit in 128 registers.
+                uint32_t s[2][32];
+                tmem_ld32(s_addr, s[0]);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    tmem_ld_wait();
+                    if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, s[(c + 1) & 1]);
+                    else tmem_ld32(s_addr, s[0]);                  // first chunk of pass 2
+                    mask_chunk(s[c & 1], c);
+                    max_chunk(s[c & 1]);
+                }
+#else
                 uint32_t s[4][32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
                 tmem_ld_wait();
-
-                const int k0 = j * kBlockN;
-                const bool need_mask = (k0 + kBlockN > p.Skv) || (p.causal && (k0 + kBlockN - 1 > p.start_pos + tile_r0));
-                if (need_mask) {
-                    const int limit = p.causal ? min(p.Skv - 1, p.start_pos + row) : p.Skv - 1;   // last visible key
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (k0 + c * 32 + i > limit) s[c][i] = 0xFF800000u;   // -inf
-                }
-                // row max: 8 independent chains of 3-input max (one thread owns the whole row)
-                float mx8[8];
-#pragma unroll
-                for (int a = 0; a < 8; ++a) mx8[a] = -INFINITY;
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-#if VB_MAX3
-                        mx8[(i >> 1) & 7] = fmax3(mx8[(i >> 1) & 7], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
-#else
-                        mx8[(i >> 1) & 7] = fmaxf(mx8[(i >> 1) & 7], fmaxf(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
+                for (int c = 0; c < 4; ++c) { mask_chunk(s[c], c); max_chunk(s[c]); }
 #endif
-                    }
                 const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
                 const float m_cand = mx * scale_log2;
                 const bool grow = m_cand > m_ref + kRescaleThreshold;      // true on the first block of an item
@@ -493,16 +533,25 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
 #pragma unroll
                     for (int cc = 0; cc < 2; ++cc) {
                         const int c = 2 * half + cc;
+#if VB_TWO_PASS
+                        tmem_ld_wait();                            // chunk c (issued one step earlier)
+                        if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, s[(c + 1) & 1]);
+                        mask_chunk(s[c & 1], c);
+                        const uint32_t (&sv)[32] = s[c & 1];
+#else
+                        const uint32_t (&sv)[32] = s[c];
+#endif
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
 #if VB_PACKED_MATH
                             // packed fp32x2: one FMA and one add per pair of columns
-                            const float2 e = __ffma2_rn(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nm2);
-                            const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+                            const float2 e = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sc2, nm2);
+                            const float2 pp = (((i >> 1) % VB_POLY_DEN) < VB_POLY_NUM) ? exp2_poly2(e)
+                                                                                       : make_float2(fast_exp2(e.x), fast_exp2(e.y));
                             rs[(i >> 1) & 3] = __fadd2_rn(rs[(i >> 1) & 3], pp);
 #else
-                            const float2 pp = make_float2(fast_exp2(fmaf(__uint_as_float(s[c][i]), sc2.x, nm2.x)),
-                                                          fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), sc2.x, nm2.x)));
+                            const float2 pp = make_float2(fast_exp2(fmaf(__uint_as_float(sv[i]), sc2.x, nm2.x)),
+                                                          fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sc2.x, nm2.x)));
                             rs[(i >> 1) & 3].x += pp.x;
                             rs[(i >> 1) & 3].y += pp.y;
 #endif
