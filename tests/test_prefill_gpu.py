@@ -199,3 +199,35 @@ def test_argument_errors_are_status_codes(lib, cuda):
     assert lib.vb200_prefill_fwd(C.byref(a)) == -1
     torch.cuda.synchronize()
     capi.check_kernel_status(0)
+
+
+def test_prefill_chunk_at_far_position(lib, cuda, oracle):
+    """A prompt chunk appended behind 20000 cached keys: RoPE angles ~2e4 rad (where the fp32
+    angle pos*f of the reference is itself coarse, so every row must use the exact table) and a
+    bottom-right aligned causal mask over 158 key blocks."""
+    import torch
+    from vesper_b200 import capi
+    B, Hq, Hkv, D, P, T = 1, 2, 1, 128, 20000, 200
+    cap = P + 256
+    rng = np.random.default_rng(77)
+    okc = np.zeros((B, Hkv, cap, D), np.float32)
+    ovc = np.zeros_like(okc)
+    okc[:, :, :P] = bf16_round(rng.standard_normal((B, Hkv, P, D), dtype=np.float32))
+    ovc[:, :, :P] = bf16_round(rng.standard_normal((B, Hkv, P, D), dtype=np.float32))
+    kc, vc = to_torch(okc, torch.bfloat16, cuda), to_torch(ovc, torch.bfloat16, cuda)
+    q = bf16_round(rng.standard_normal((B, Hq, T, D), dtype=np.float32))
+    k = bf16_round(rng.standard_normal((B, Hkv, T, D), dtype=np.float32))
+    v = bf16_round(rng.standard_normal((B, Hkv, T, D), dtype=np.float32))
+    tq, tk, tv = (to_torch(x, torch.bfloat16, cuda) for x in (q, k, v))
+    o = torch.empty_like(tq)
+    lse = torch.empty(B, Hq, T, dtype=torch.float32, device=cuda)
+    scale = float(1.0 / np.sqrt(D))
+    capi.prefill(tq, tk, tv, o, lse, scale=scale, causal=True, start_pos=P, theta=10000.0, k_cache=kc, v_cache=vc)
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)
+    want_o, want_lse, cur = oracle.gqa_attention_cached(q, k, v, okc, ovc, P, P)
+    assert cur == P + T
+    assert maxabs(from_torch(o), want_o) <= 1e-2
+    assert maxabs(from_torch(lse), want_lse) <= 2e-3     # scores of |s| ~ 10 with K rounded to bf16 in the cache
+    gk = from_torch(kc)
+    assert np.all(np.abs(gk[:, :, P:P + T] - okc[:, :, P:P + T]) <= 2.0 ** -8 * np.abs(okc[:, :, P:P + T]) + 1e-6)

@@ -353,6 +353,7 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
             const int rw = warp - kRopeWarp0;
             const int c = lane & 15;                          // 16-byte chunk of the row (D = 128: 16 chunks)
             constexpr int kRopeSeed = 8;                      // steps (of two rows) between exact table reads
+            const bool exact_rope = p.start_pos + p.T > 16384; // beyond this, every row's angle comes from the table
             float step_c[4], step_s[4];                       // rotation by two positions for this lane's 4 pairs
 #pragma unroll
             for (int e = 0; e < 4; ++e) sincosf(2.0f * p.inv_freq.v[(c * 4 + e) & (kMaxHalfDim - 1)], &step_s[e], &step_c[e]);
@@ -413,6 +414,15 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                                     cs[e] = cn;
                                 }
                                 *ptr = raw;                     // rows past T are zero: rotating them is harmless
+                                if (exact_rope && i + 1 < kRopeSeed) {
+                                    // far positions: the reference's fp32 angle pos*f is itself rounded to ~6e-8*pos,
+                                    // which the recurrence does not reproduce -- read every row from the table there
+                                    const int rown = min(w.r0[t] + r + 2, p.T - 1);
+                                    const float4* tabn = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(rown) * (D / 2)) + c * 2;
+                                    const float4 a0 = __ldg(tabn), a1 = __ldg(tabn + 1);
+                                    cs[0] = a0.x; cs[1] = a0.z; cs[2] = a1.x; cs[3] = a1.z;
+                                    sn[0] = a0.y; sn[1] = a0.w; sn[2] = a1.y; sn[3] = a1.w;
+                                }
                             }
                         }
                     }
