@@ -57,6 +57,9 @@ constexpr float kRescaleThreshold = 8.0f;
 #ifndef VB_MAX3
 #define VB_MAX3 0              // 3-input max in the row maximum
 #endif
+#ifndef VB_PINGPONG
+#define VB_PINGPONG 1          // the two softmax warpgroups take turns in the exp2 (special-function) phase
+#endif
 #ifndef VB_TWO_PASS
 #define VB_TWO_PASS 0          // read the score tile from TMEM twice (max, then exp) instead of holding it
 #endif
@@ -81,6 +84,7 @@ struct __align__(8) Barriers {
     uint64_t q_full[kQBufs], q_rot[kQBufs], q_free[kQBufs];
     uint64_t kv_full[kStages], kv_empty[kStages];
     uint64_t s_full[2], p_ready[2], o_done[2];
+    uint64_t turn[2];           // exp-phase token passed between the two softmax warpgroups
     uint64_t mma_done;
     uint32_t tmem_base;
     int abort_flag;
@@ -183,6 +187,7 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 mbar_init(&bar->s_full[t], 1); mbar_init(&bar->p_ready[t], kBlockM); mbar_init(&bar->o_done[t], 1);
             }
             for (int s = 0; s < kStages; ++s) { mbar_init(&bar->kv_full[s], 1); mbar_init(&bar->kv_empty[s], 1); }
+            mbar_init(&bar->turn[0], kBlockM); mbar_init(&bar->turn[1], kBlockM);
             mbar_init(&bar->mma_done, 1);
             bar->abort_flag = 0;
             mbar_fence_init();
@@ -254,23 +259,28 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 const uint32_t q_addr = smem_u32(q_smem), kv_addr = smem_u32(kv_smem);
                 auto tmem_s = [&](int t) { return tmem_base + static_cast<uint32_t>(t * 128); };
                 auto tmem_o = [&](int t) { return tmem_base + static_cast<uint32_t>(256 + t * 128); };
+                // Descriptors differ between k-steps only in the 14-bit start-address field, so each
+                // product builds one base descriptor per operand and adds a compile-time constant per
+                // step (the issuing thread is on the critical path: 16 MMAs per tile and iteration).
+                auto desc_add = [](uint64_t d, uint32_t byte_off) { return d + static_cast<uint64_t>(byte_off >> 4); };
                 auto issue_qk = [&](int t, int qbuf, int slot) {
+                    const uint64_t a0 = make_smem_desc_sw128(q_addr + qbuf * C::kTileBytes, 16, 1024);
+                    const uint64_t b0 = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes, 16, 1024);
+                    const uint32_t d = tmem_s(t);
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
-                        uint32_t off = (kk >> 2) * C::kHalfBytes + (kk & 3) * 32;
-                        uint64_t a = make_smem_desc_sw128(q_addr + qbuf * C::kTileBytes + off, 16, 1024);
-                        uint64_t bd = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes + off, 16, 1024);
-                        umma_ss(tmem_s(t), a, bd, idesc_qk, kk > 0 ? 1u : 0u);
+                        const uint32_t off = (kk >> 2) * C::kHalfBytes + (kk & 3) * 32;
+                        umma_ss(d, desc_add(a0, off), desc_add(b0, off), idesc_qk, kk > 0 ? 1u : 0u);
                     }
                 };
                 auto issue_pv = [&](int t, int slot, bool accumulate) {
+                    // V tile is MN-major for this product: 16 keys = 2048 bytes per step,
+                    // second 64-column box one half-tile further (leading offset)
+                    const uint64_t b0 = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes, C::kHalfBytes, 1024);
+                    const uint32_t d = tmem_o(t), a = tmem_s(t);
 #pragma unroll
-                    for (int kk = 0; kk < kBlockN / 16; ++kk) {
-                        // V tile is MN-major for this product: 16 keys = 2048 bytes per step,
-                        // second 64-column box one half-tile further (leading offset)
-                        uint64_t bd = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes + kk * 2048, C::kHalfBytes, 1024);
-                        umma_ts(tmem_o(t), tmem_s(t) + kk * 8, bd, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
-                    }
+                    for (int kk = 0; kk < kBlockN / 16; ++kk)
+                        umma_ts(d, a + kk * 8, desc_add(b0, kk * 2048), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
                 };
                 int kv_item = 0, q_seq = 0;
                 int blk0 = 0, blk1 = 0;          // running count of score tiles per query tile (barrier phases)
@@ -444,14 +454,21 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
         int g = 0;                                   // running count of score tiles of this query tile
         bool ok = true;
         int item_no = -1;
+        // Both warpgroups share each SM sub-partition's special-function unit (16 ex2 per clock and SM).
+        // Left alone they drift into phase: both do their exponentials at once (each at half speed) and
+        // then both wait for the tensor pipe.  A token makes them alternate, so one tile's exponentials
+        // overlap the other tile's MMAs.  Warpgroup 0 holds the token first.
+        int turns = 0;
+        if (VB_PINGPONG && t == 1) mbar_arrive(&bar->turn[0]);
 
         for (int round = 0; round < n_rounds && ok; ++round) {
             const int idx = item_of_round(round, n_items);
             if (idx < 0) continue;
             ++item_no;
             const Item w = get_item(p, idx, n_bh, n_pairs);
-            long long t_wait = 0, t_comp = 0, t_epi = 0;
+            long long t_wait = 0, t_comp = 0, t_epi = 0, t_ld = 0, t_max = 0, t_exp = 0;
             const int n = t ? w.nblk[1] : w.nblk[0];
+            const int n_shared = min(w.nblk[0], w.nblk[1]);   // blocks both tiles have: those alternate
             if (n == 0) continue;
             const int tile_r0 = t ? w.r0[1] : w.r0[0];
             const int row = tile_r0 + r;             // query row in [0, T)
@@ -506,6 +523,9 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
                 tmem_ld_wait();
+#ifdef VB_TIMING
+                const long long tp1 = clock64();
+#endif
 #pragma unroll
                 for (int c = 0; c < 4; ++c) { mask_chunk(s[c], c); max_chunk(s[c]); }
 #endif
@@ -534,6 +554,16 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                     l_sum *= alpha;
                     m_ref = m_new;
                 }
+#if defined(VB_TIMING) && !VB_TWO_PASS
+                const long long tp2 = clock64();
+                t_ld += tp1 - tb_; t_max += tp2 - tp1;
+#endif
+#if VB_PINGPONG
+                if (j < n_shared) {
+                    ok = mbar_wait_warp(&bar->turn[t], turns & 1, abort_flag, 0xB00 + t);
+                    if (!ok) break;
+                }
+#endif
                 // p = 2^(s*scale*log2e - m_ref); packed to 16 bit two per column
                 float2 rs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
                 const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_ref, -m_ref);
@@ -570,7 +600,13 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                     }
                     tmem_st32(s_addr + half * 32, pk);
                 }
+#if VB_PINGPONG
+                if (j < n_shared) { mbar_arrive(&bar->turn[t ^ 1]); ++turns; }      // exponentials issued: pass the token
+#endif
                 l_sum += ((rs[0].x + rs[0].y) + (rs[1].x + rs[1].y)) + ((rs[2].x + rs[2].y) + (rs[3].x + rs[3].y));
+#if defined(VB_TIMING) && !VB_TWO_PASS
+                t_exp += clock64() - tp2;
+#endif
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(&bar->p_ready[t]);
@@ -613,9 +649,9 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 p.lse[(static_cast<long long>(w.b) * p.Hq + w.hq) * p.T + row] = (m_ref + fast_log2(l_sum)) * kLn2;
 #ifdef VB_TIMING
             t_epi = clock64() - te0;
-            if ((tid & 127) == 0) { VB_T(14 - 4 * t, t_wait); VB_T(15 - 4 * t, t_comp); if (t == 1) VB_T(9, t_epi); }
+            if ((tid & 127) == 0) { VB_T(14 - 4 * t, t_wait); VB_T(15 - 4 * t, t_comp); if (t == 1) VB_T(9, t_epi); if (t == 0) { VB_T(6, t_ld); VB_T(7, t_max); VB_T(8, t_exp); } }
 #endif
-            (void)t_wait; (void)t_comp; (void)t_epi;
+            (void)t_wait; (void)t_comp; (void)t_epi; (void)t_ld; (void)t_max; (void)t_exp;
         }
     }
 
