@@ -98,3 +98,31 @@ def test_wrong_size_partial_is_a_host_error():
     ret = mp.Manager().dict()
     mp.spawn(_bad_worker, args=(2, 29733, ret), nprocs=2, join=True)
     assert dict(ret) == {0: "ValueError", 1: "ValueError"}
+
+
+def _absent_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    import time
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    from vesper_b200.sharded import ShardedDecodeStep, ShardExchangeError
+    if rank == 1:
+        time.sleep(6)                         # the failing rank: joined the group, never contributes its partial
+        ret[rank] = "absent"
+        os._exit(0)
+    try:
+        ShardedDecodeStep(world, rank, 16, timeout_s=2.0).run(lambda b, e, p: torch.zeros(4, 6), lambda g: g, dist)
+        ret[rank] = "no error"
+    except ShardExchangeError:
+        ret[rank] = "ShardExchangeError"
+    os._exit(0)                               # the group is unusable after the failure: leave without a collective
+
+
+def test_rank_that_never_contributes_is_a_host_timeout():
+    """Failure made on the host: one rank never issues its all-gather; the other must get an
+    error within the host-side limit instead of hanging."""
+    ret = mp.Manager().dict()
+    mp.spawn(_absent_worker, args=(2, 29761, ret), nprocs=2, join=True)
+    assert ret.get(0) == "ShardExchangeError", dict(ret)

@@ -188,6 +188,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(Dec
         // length this step used, for the combine kernel (stable even when seq_lens advances)
         reinterpret_cast<int*>(p.workspace)[b] = len;
     }
+    // let the combine kernel's blocks be scheduled as soon as every CTA of this grid has started
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (k_begin >= total) return;                                   // nothing for this split
     const int k_end = min(len, k_begin + p.chunk);                  // cached keys [k_begin, k_end)
     const bool owns_new = p.append && (len / p.chunk == split);
@@ -359,6 +361,9 @@ __global__ void __launch_bounds__(128 * kCombineGroups) decode_combine_kernel(De
     __shared__ float s_l[kCombineGroups];
     const int hq = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, d = tid & 127, grp = tid >> 7;
     const int nrep = p.Hq / p.Hkv, kvh = hq / nrep, h = hq % nrep;
+    // Launched with programmatic stream serialization: the blocks may become resident while the
+    // split kernel drains; nothing of its output is touched before this wait returns.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int len = reinterpret_cast<const int*>(p.workspace)[b];
     const int total = len + (p.append ? 1 : 0);
     const int nsp = (total + p.chunk - 1) / p.chunk;
@@ -454,7 +459,19 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
     profile_mark_end(s);
     note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());
-    decode_combine_kernel<T><<<dim3(p.Hq, p.B), 128 * kCombineGroups, 0, s>>>(p);
+    {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(p.Hq, p.B);
+        cfg.blockDim = dim3(128 * kCombineGroups);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_combine_kernel<T>, p));
+    }
     note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());
     return VB200_OK;

@@ -43,6 +43,28 @@ def owner_of_row(total: int, world: int, row: int) -> int:
     return world - 1
 
 
+class ShardExchangeError(RuntimeError):
+    """The all-gather of the partials did not complete (a rank is missing, slow or failed)."""
+
+
+def guarded_all_gather(dist, out, inp, timeout_s=None):
+    """all_gather_into_tensor supervised from the host: with a timeout the collective is issued
+    asynchronously and waited for at most ``timeout_s`` seconds; a rank that never contributes its
+    partial turns into a ShardExchangeError on the others instead of a hang.  No GPU state is
+    touched by the failure path (the process group is left for the caller to abort or rebuild)."""
+    if timeout_s is None:
+        dist.all_gather_into_tensor(out, inp)
+        return
+    import datetime
+    work = dist.all_gather_into_tensor(out, inp, async_op=True)
+    try:
+        done = work.wait(timeout=datetime.timedelta(seconds=timeout_s))
+    except RuntimeError as e:                      # gloo / NCCL report an expired wait as an exception
+        raise ShardExchangeError(f"partial all-gather failed or timed out after {timeout_s} s: {e}") from e
+    if done is False:
+        raise ShardExchangeError(f"partial all-gather timed out after {timeout_s} s")
+
+
 @dataclass
 class ShardedDecodeStep:
     """One rank's view of a sequence-sharded decode step.
@@ -56,6 +78,7 @@ class ShardedDecodeStep:
     rank: int
     context_len: int
     validate: bool = False   # exchange the partial's shape first and fail on the host if ranks disagree
+    timeout_s: float | None = None   # host-side limit on the all-gather (None: wait without limit)
 
     def run(self, local_partial, combine, dist=None):
         import torch
@@ -72,7 +95,7 @@ class ShardedDecodeStep:
                 if not all(torch.equal(shapes[4 * r:4 * r + 4], mine) for r in range(self.world)):
                     raise ValueError(f"rank {self.rank}: partial shapes differ across ranks: {shapes.view(self.world, 4).tolist()}")
             flat = torch.empty((self.world * part.shape[0],) + tuple(part.shape[1:]), dtype=part.dtype, device=part.device)
-            dist.all_gather_into_tensor(flat, part)       # rank-major concatenation along dim 0
+            guarded_all_gather(dist, flat, part, self.timeout_s)       # rank-major concatenation along dim 0
             gathered = flat.view((self.world,) + tuple(part.shape))
         return combine(gathered)
 
@@ -92,6 +115,6 @@ def cuda_step(step: ShardedDecodeStep, q, k_shard, v_shard, *, scale, theta, par
         g = partial_buf.view(1, B * Hq, D + 2)
     else:
         g = gathered if gathered is not None else torch.empty(step.world, B * Hq, D + 2, dtype=torch.float32, device=q.device)
-        dist.all_gather_into_tensor(g.view(step.world * B * Hq, D + 2), partial_buf.view(B * Hq, D + 2))
+        guarded_all_gather(dist, g.view(step.world * B * Hq, D + 2), partial_buf.view(B * Hq, D + 2), step.timeout_s)
     capi.lse_combine(g, out, lse, stream=stream)
     return out
