@@ -57,18 +57,6 @@ constexpr float kRescaleThreshold = 8.0f;
 #ifndef VB_MAX3
 #define VB_MAX3 0              // 3-input max in the row maximum
 #endif
-#ifndef VB_PINGPONG
-#define VB_PINGPONG 1          // the two softmax warpgroups take turns in the exp2 (special-function) phase
-#endif
-#ifndef VB_TWO_PASS
-#define VB_TWO_PASS 0          // read the score tile from TMEM twice (max, then exp) instead of holding it
-#endif
-#ifndef VB_POLY_NUM
-#define VB_POLY_NUM 0          // of every VB_POLY_DEN column pairs, this many take exp2 on the FMA pipe
-#endif
-#ifndef VB_POLY_DEN
-#define VB_POLY_DEN 1
-#endif
 static_assert(VB_REG_SOFTMAX * 256 + VB_REG_OTHER * 128 <= 168 * 384, "register budget");
 
 #ifdef VB_TIMING
@@ -84,7 +72,6 @@ struct __align__(8) Barriers {
     uint64_t q_full[kQBufs], q_rot[kQBufs], q_free[kQBufs];
     uint64_t kv_full[kStages], kv_empty[kStages];
     uint64_t s_full[2], p_ready[2], o_done[2];
-    uint64_t turn[2];           // exp-phase token passed between the two softmax warpgroups
     uint64_t mma_done;
     uint32_t tmem_base;
     int abort_flag;
@@ -137,29 +124,14 @@ __device__ __forceinline__ int item_of_round(int round, int n_items) {
     return idx < n_items ? idx : -1;
 }
 
-// 2^x for a pair of values on the FMA pipe instead of the special-function unit, which the
-// softmax otherwise saturates (128 ex2 per row against 16 results per clock and SM).
-// x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3 polynomial (max relative
-// error 7.5e-5, far below the 16-bit rounding of P); 2^n by adding n to the exponent field.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-    x.x = fmaxf(x.x, -126.0f);
-    x.y = fmaxf(x.y, -126.0f);
-    const float magic = 12582912.0f;                       // 1.5 * 2^23: the sum keeps round(x) in its low mantissa bits
-    const float2 r = __fadd2_rn(x, make_float2(magic, magic));
-    const float2 n = __fadd2_rn(r, make_float2(-magic, -magic));
-    const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
-    float2 p = __ffma2_rn(f, make_float2(0.055171650f, 0.055171650f), make_float2(0.24261113f, 0.24261113f));
-    p = __ffma2_rn(p, f, make_float2(0.69326097f, 0.69326097f));
-    p = __ffma2_rn(p, f, make_float2(0.99992806f, 0.99992806f));
-    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(r.x) << 23));
-    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23));
-    return p;
-}
-
 template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
-template <typename T, int D>
+// kExactRope selects how the RoPE warps get a query row's angles: false = table seed every kRopeSeed
+// steps + angle-addition recurrence (prompts whose last position is <= 16384), true = every row from
+// the table.  A template parameter, not a run-time branch: the extra loop in one kernel body changed
+// the register allocation of the whole kernel and cost the common case 5-8 %.
+template <typename T, int D, bool kExactRope>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
     using C = Cfg<D>;
@@ -187,7 +159,6 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 mbar_init(&bar->s_full[t], 1); mbar_init(&bar->p_ready[t], kBlockM); mbar_init(&bar->o_done[t], 1);
             }
             for (int s = 0; s < kStages; ++s) { mbar_init(&bar->kv_full[s], 1); mbar_init(&bar->kv_empty[s], 1); }
-            mbar_init(&bar->turn[0], kBlockM); mbar_init(&bar->turn[1], kBlockM);
             mbar_init(&bar->mma_done, 1);
             bar->abort_flag = 0;
             mbar_fence_init();
@@ -259,28 +230,23 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 const uint32_t q_addr = smem_u32(q_smem), kv_addr = smem_u32(kv_smem);
                 auto tmem_s = [&](int t) { return tmem_base + static_cast<uint32_t>(t * 128); };
                 auto tmem_o = [&](int t) { return tmem_base + static_cast<uint32_t>(256 + t * 128); };
-                // Descriptors differ between k-steps only in the 14-bit start-address field, so each
-                // product builds one base descriptor per operand and adds a compile-time constant per
-                // step (the issuing thread is on the critical path: 16 MMAs per tile and iteration).
-                auto desc_add = [](uint64_t d, uint32_t byte_off) { return d + static_cast<uint64_t>(byte_off >> 4); };
                 auto issue_qk = [&](int t, int qbuf, int slot) {
-                    const uint64_t a0 = make_smem_desc_sw128(q_addr + qbuf * C::kTileBytes, 16, 1024);
-                    const uint64_t b0 = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes, 16, 1024);
-                    const uint32_t d = tmem_s(t);
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
-                        const uint32_t off = (kk >> 2) * C::kHalfBytes + (kk & 3) * 32;
-                        umma_ss(d, desc_add(a0, off), desc_add(b0, off), idesc_qk, kk > 0 ? 1u : 0u);
+                        uint32_t off = (kk >> 2) * C::kHalfBytes + (kk & 3) * 32;
+                        uint64_t a = make_smem_desc_sw128(q_addr + qbuf * C::kTileBytes + off, 16, 1024);
+                        uint64_t bd = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes + off, 16, 1024);
+                        umma_ss(tmem_s(t), a, bd, idesc_qk, kk > 0 ? 1u : 0u);
                     }
                 };
                 auto issue_pv = [&](int t, int slot, bool accumulate) {
-                    // V tile is MN-major for this product: 16 keys = 2048 bytes per step,
-                    // second 64-column box one half-tile further (leading offset)
-                    const uint64_t b0 = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes, C::kHalfBytes, 1024);
-                    const uint32_t d = tmem_o(t), a = tmem_s(t);
 #pragma unroll
-                    for (int kk = 0; kk < kBlockN / 16; ++kk)
-                        umma_ts(d, a + kk * 8, desc_add(b0, kk * 2048), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < kBlockN / 16; ++kk) {
+                        // V tile is MN-major for this product: 16 keys = 2048 bytes per step,
+                        // second 64-column box one half-tile further (leading offset)
+                        uint64_t bd = make_smem_desc_sw128(kv_addr + slot * C::kTileBytes + kk * 2048, C::kHalfBytes, 1024);
+                        umma_ts(tmem_o(t), tmem_s(t) + kk * 8, bd, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+                    }
                 };
                 int kv_item = 0, q_seq = 0;
                 int blk0 = 0, blk1 = 0;          // running count of score tiles per query tile (barrier phases)
@@ -363,7 +329,6 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
             const int rw = warp - kRopeWarp0;
             const int c = lane & 15;                          // 16-byte chunk of the row (D = 128: 16 chunks)
             constexpr int kRopeSeed = 8;                      // steps (of two rows) between exact table reads
-            const bool exact_rope = p.start_pos + p.T > 16384; // beyond this, every row's angle comes from the table
             float step_c[4], step_s[4];                       // rotation by two positions for this lane's 4 pairs
 #pragma unroll
             for (int e = 0; e < 4; ++e) sincosf(2.0f * p.inv_freq.v[(c * 4 + e) & (kMaxHalfDim - 1)], &step_s[e], &step_c[e]);
@@ -397,6 +362,29 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                             const float4* tab = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(row) * (D / 2)) + c * 2;
                             seed0 = __ldg(tab); seed1 = __ldg(tab + 1);
                         }
+                        if constexpr (kExactRope) {
+                            // far positions: the reference's fp32 angle pos*f is itself rounded to ~6e-8*pos,
+                            // which the recurrence does not reproduce -- every row reads the table there
+#pragma unroll 2
+                            for (int st = 0; st < 32; ++st) {
+                                const int r = r_first + 2 * st;
+                                const int rowx = min(w.r0[t] + r, p.T - 1);
+                                const float4* tabx = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(rowx) * (D / 2)) + c * 2;
+                                const float4 a0 = __ldg(tabx), a1 = __ldg(tabx + 1);
+                                const float csx[4] = {a0.x, a0.z, a1.x, a1.z}, snx[4] = {a0.y, a0.w, a1.y, a1.w};
+                                uint4* ptr = reinterpret_cast<uint4*>(qtile + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+                                uint4 raw = *ptr;
+                                uint32_t* u = &raw.x;
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    float2 x = Elem<T>::unpack2(u[e]);
+                                    float t1 = __fmul_rn(x.x, csx[e]), t2 = __fmul_rn(x.y, snx[e]);
+                                    float t3 = __fmul_rn(x.x, snx[e]), t4 = __fmul_rn(x.y, csx[e]);
+                                    u[e] = Elem<T>::pack2(__fsub_rn(t1, t2), __fadd_rn(t3, t4));
+                                }
+                                *ptr = raw;
+                            }
+                        } else
 #pragma unroll 1
                         for (int s0 = 0; s0 < 32; s0 += kRopeSeed) {
                             float cs[4] = {seed0.x, seed0.z, seed1.x, seed1.z};
@@ -424,15 +412,6 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                                     cs[e] = cn;
                                 }
                                 *ptr = raw;                     // rows past T are zero: rotating them is harmless
-                                if (exact_rope && i + 1 < kRopeSeed) {
-                                    // far positions: the reference's fp32 angle pos*f is itself rounded to ~6e-8*pos,
-                                    // which the recurrence does not reproduce -- read every row from the table there
-                                    const int rown = min(w.r0[t] + r + 2, p.T - 1);
-                                    const float4* tabn = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(rown) * (D / 2)) + c * 2;
-                                    const float4 a0 = __ldg(tabn), a1 = __ldg(tabn + 1);
-                                    cs[0] = a0.x; cs[1] = a0.z; cs[2] = a1.x; cs[3] = a1.z;
-                                    sn[0] = a0.y; sn[1] = a0.w; sn[2] = a1.y; sn[3] = a1.w;
-                                }
                             }
                         }
                     }
@@ -454,21 +433,14 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
         int g = 0;                                   // running count of score tiles of this query tile
         bool ok = true;
         int item_no = -1;
-        // Both warpgroups share each SM sub-partition's special-function unit (16 ex2 per clock and SM).
-        // Left alone they drift into phase: both do their exponentials at once (each at half speed) and
-        // then both wait for the tensor pipe.  A token makes them alternate, so one tile's exponentials
-        // overlap the other tile's MMAs.  Warpgroup 0 holds the token first.
-        int turns = 0;
-        if (VB_PINGPONG && t == 1) mbar_arrive(&bar->turn[0]);
 
         for (int round = 0; round < n_rounds && ok; ++round) {
             const int idx = item_of_round(round, n_items);
             if (idx < 0) continue;
             ++item_no;
             const Item w = get_item(p, idx, n_bh, n_pairs);
-            long long t_wait = 0, t_comp = 0, t_epi = 0, t_ld = 0, t_max = 0, t_exp = 0;
+            long long t_wait = 0, t_comp = 0, t_epi = 0;
             const int n = t ? w.nblk[1] : w.nblk[0];
-            const int n_shared = min(w.nblk[0], w.nblk[1]);   // blocks both tiles have: those alternate
             if (n == 0) continue;
             const int tile_r0 = t ? w.r0[1] : w.r0[0];
             const int row = tile_r0 + r;             // query row in [0, T)
@@ -485,50 +457,35 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 t_wait += tb_ - ta;
 #endif
                 tc_fence_after();
-                const int k0 = j * kBlockN;
-                const bool need_mask = (k0 + kBlockN > p.Skv) || (p.causal && (k0 + kBlockN - 1 > p.start_pos + tile_r0));
-                const int limit = p.causal ? min(p.Skv - 1, p.start_pos + row) : p.Skv - 1;   // last visible key
-                auto mask_chunk = [&](uint32_t (&v)[32], int c) {
-                    if (need_mask) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (k0 + c * 32 + i > limit) v[i] = 0xFF800000u;   // -inf
-                    }
-                };
-                // row max: 8 independent chains (one thread owns the whole row)
-                float mx8[8];
-#pragma unroll
-                for (int a = 0; a < 8; ++a) mx8[a] = -INFINITY;
-                auto max_chunk = [&](const uint32_t (&v)[32]) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2)
-                        mx8[(i >> 1) & 7] = fmaxf(mx8[(i >> 1) & 7], fmaxf(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
-                };
-#if VB_TWO_PASS
-                // Pass 1 reads the score tile from TMEM chunk by chunk for the maximum only; pass 2
-                // reads it again for the exponentials.  Only two 32-column chunks are live at a time,
-                // so the row never has to sit in 128 registers.
-                uint32_t s[2][32];
-                tmem_ld32(s_addr, s[0]);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    tmem_ld_wait();
-                    if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, s[(c + 1) & 1]);
-                    else tmem_ld32(s_addr, s[0]);                  // first chunk of pass 2
-                    mask_chunk(s[c & 1], c);
-                    max_chunk(s[c & 1]);
-                }
-#else
                 uint32_t s[4][32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
                 tmem_ld_wait();
-#ifdef VB_TIMING
-                const long long tp1 = clock64();
-#endif
+
+                const int k0 = j * kBlockN;
+                const bool need_mask = (k0 + kBlockN > p.Skv) || (p.causal && (k0 + kBlockN - 1 > p.start_pos + tile_r0));
+                if (need_mask) {
+                    const int limit = p.causal ? min(p.Skv - 1, p.start_pos + row) : p.Skv - 1;   // last visible key
 #pragma unroll
-                for (int c = 0; c < 4; ++c) { mask_chunk(s[c], c); max_chunk(s[c]); }
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (k0 + c * 32 + i > limit) s[c][i] = 0xFF800000u;   // -inf
+                }
+                // row max: 8 independent chains of 3-input max (one thread owns the whole row)
+                float mx8[8];
+#pragma unroll
+                for (int a = 0; a < 8; ++a) mx8[a] = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+#if VB_MAX3
+                        mx8[(i >> 1) & 7] = fmax3(mx8[(i >> 1) & 7], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+#else
+                        mx8[(i >> 1) & 7] = fmaxf(mx8[(i >> 1) & 7], fmaxf(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
 #endif
+                    }
                 const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
                 const float m_cand = mx * scale_log2;
                 const bool grow = m_cand > m_ref + kRescaleThreshold;      // true on the first block of an item
@@ -554,16 +511,6 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                     l_sum *= alpha;
                     m_ref = m_new;
                 }
-#if defined(VB_TIMING) && !VB_TWO_PASS
-                const long long tp2 = clock64();
-                t_ld += tp1 - tb_; t_max += tp2 - tp1;
-#endif
-#if VB_PINGPONG
-                if (j < n_shared) {
-                    ok = mbar_wait_warp(&bar->turn[t], turns & 1, abort_flag, 0xB00 + t);
-                    if (!ok) break;
-                }
-#endif
                 // p = 2^(s*scale*log2e - m_ref); packed to 16 bit two per column
                 float2 rs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
                 const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_ref, -m_ref);
@@ -573,25 +520,16 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
 #pragma unroll
                     for (int cc = 0; cc < 2; ++cc) {
                         const int c = 2 * half + cc;
-#if VB_TWO_PASS
-                        tmem_ld_wait();                            // chunk c (issued one step earlier)
-                        if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, s[(c + 1) & 1]);
-                        mask_chunk(s[c & 1], c);
-                        const uint32_t (&sv)[32] = s[c & 1];
-#else
-                        const uint32_t (&sv)[32] = s[c];
-#endif
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
 #if VB_PACKED_MATH
                             // packed fp32x2: one FMA and one add per pair of columns
-                            const float2 e = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sc2, nm2);
-                            const float2 pp = (((i >> 1) % VB_POLY_DEN) < VB_POLY_NUM) ? exp2_poly2(e)
-                                                                                       : make_float2(fast_exp2(e.x), fast_exp2(e.y));
+                            const float2 e = __ffma2_rn(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nm2);
+                            const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
                             rs[(i >> 1) & 3] = __fadd2_rn(rs[(i >> 1) & 3], pp);
 #else
-                            const float2 pp = make_float2(fast_exp2(fmaf(__uint_as_float(sv[i]), sc2.x, nm2.x)),
-                                                          fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sc2.x, nm2.x)));
+                            const float2 pp = make_float2(fast_exp2(fmaf(__uint_as_float(s[c][i]), sc2.x, nm2.x)),
+                                                          fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), sc2.x, nm2.x)));
                             rs[(i >> 1) & 3].x += pp.x;
                             rs[(i >> 1) & 3].y += pp.y;
 #endif
@@ -600,13 +538,7 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                     }
                     tmem_st32(s_addr + half * 32, pk);
                 }
-#if VB_PINGPONG
-                if (j < n_shared) { mbar_arrive(&bar->turn[t ^ 1]); ++turns; }      // exponentials issued: pass the token
-#endif
                 l_sum += ((rs[0].x + rs[0].y) + (rs[1].x + rs[1].y)) + ((rs[2].x + rs[2].y) + (rs[3].x + rs[3].y));
-#if defined(VB_TIMING) && !VB_TWO_PASS
-                t_exp += clock64() - tp2;
-#endif
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(&bar->p_ready[t]);
@@ -649,9 +581,9 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 p.lse[(static_cast<long long>(w.b) * p.Hq + w.hq) * p.T + row] = (m_ref + fast_log2(l_sum)) * kLn2;
 #ifdef VB_TIMING
             t_epi = clock64() - te0;
-            if ((tid & 127) == 0) { VB_T(14 - 4 * t, t_wait); VB_T(15 - 4 * t, t_comp); if (t == 1) VB_T(9, t_epi); if (t == 0) { VB_T(6, t_ld); VB_T(7, t_max); VB_T(8, t_exp); } }
+            if ((tid & 127) == 0) { VB_T(14 - 4 * t, t_wait); VB_T(15 - 4 * t, t_comp); if (t == 1) VB_T(9, t_epi); }
 #endif
-            (void)t_wait; (void)t_comp; (void)t_epi; (void)t_ld; (void)t_max; (void)t_exp;
+            (void)t_wait; (void)t_comp; (void)t_epi;
         }
     }
 
@@ -701,7 +633,7 @@ int make_map(CUtensorMap* m, int dtype, const View4& v, int rows, int H, int B, 
     return VB200_OK;
 }
 
-template <typename T, int D>
+template <typename T, int D, bool kExactRope>
 int launch_t(cudaStream_t s, const PrefillParams& p) {
     TmaMaps maps;
     if (int rc = make_map(&maps.q, p.dtype, p.q, p.T, p.Hq, p.B, D)) return rc;
@@ -711,7 +643,7 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
     int dev = 0;
     VB200_CUDA_TRY(cudaGetDevice(&dev));
     if (configured_dev != dev) {
-        VB200_CUDA_TRY(cudaFuncSetAttribute(prefill_sm100_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
+        VB200_CUDA_TRY(cudaFuncSetAttribute(prefill_sm100_kernel<T, D, kExactRope>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
         configured_dev = dev;
     }
     const int n_pairs = (p.T + 2 * kBlockM - 1) / (2 * kBlockM);
@@ -721,7 +653,7 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
     // persistent: one CTA per SM walks the work items (heaviest first, round-robin)
     dim3 grid(static_cast<unsigned>(n_items < sms ? n_items : sms));
     profile_mark_begin(s);
-    prefill_sm100_kernel<T, D><<<grid, kThreads, Cfg<D>::kSmemBytes, s>>>(maps, p);
+    prefill_sm100_kernel<T, D, kExactRope><<<grid, kThreads, Cfg<D>::kSmemBytes, s>>>(maps, p);
     profile_mark_end(s);
     note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());
@@ -739,8 +671,17 @@ extern "C" int vb200_debug_set_timing_buffer(void* buf) {
 
 int launch_prefill_sm100(cudaStream_t s, const PrefillParams& p) {
     if (p.D != 128 && p.D != 64) return set_detail(VB200_ERR_UNSUPPORTED, "bf16/fp16 attention supports head_dim 64 and 128");
-    if (p.dtype == VB200_BF16) return p.D == 128 ? launch_t<__nv_bfloat16, 128>(s, p) : launch_t<__nv_bfloat16, 64>(s, p);
-    if (p.dtype == VB200_F16) return p.D == 128 ? launch_t<__half, 128>(s, p) : launch_t<__half, 64>(s, p);
+    // past position 16384 the fp32 angle pos*f of the reference is itself coarse (~6e-8*pos) and only a
+    // per-row table read reproduces it
+    const bool exact = p.q_rope_table != nullptr && p.start_pos + p.T > 16384;
+    if (p.dtype == VB200_BF16) {
+        if (p.D == 128) return exact ? launch_t<__nv_bfloat16, 128, true>(s, p) : launch_t<__nv_bfloat16, 128, false>(s, p);
+        return exact ? launch_t<__nv_bfloat16, 64, true>(s, p) : launch_t<__nv_bfloat16, 64, false>(s, p);
+    }
+    if (p.dtype == VB200_F16) {
+        if (p.D == 128) return exact ? launch_t<__half, 128, true>(s, p) : launch_t<__half, 128, false>(s, p);
+        return exact ? launch_t<__half, 64, true>(s, p) : launch_t<__half, 64, false>(s, p);
+    }
     return VB200_ERR_UNSUPPORTED;
 }
 
