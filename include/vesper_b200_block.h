@@ -1,0 +1,106 @@
+/*
+ * vesper_b200 -- C ABI of the decoder-block operators that surround the
+ * attention hot path (projections, normalisation, gated MLP, embedding, greedy
+ * sampling).  Same conventions as vesper_b200.h: every pointer is borrowed
+ * device memory, nothing is allocated or freed, launches are asynchronous on
+ * the caller's stream, the return value is VB200_OK or a negative vb200_status.
+ * "file:line" citations name the reference interface each entry point stands
+ * behind, relative to the reference project root.
+ *
+ * Number formats: weights and activations bf16, the residual stream and the
+ * logits fp32, all accumulation fp32.
+ */
+#ifndef VESPER_B200_BLOCK_H
+#define VESPER_B200_BLOCK_H
+
+#include "vesper_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* What vb200_linear does with each accumulated output element acc[m, n]. */
+typedef enum vb200_epilogue {
+    VB200_EPI_BF16 = 0,     /* out_bf16[m, n]  = acc                                            */
+    VB200_EPI_F32 = 1,      /* out_f32[m, n]   = acc            (logits)                        */
+    VB200_EPI_ADD_F32 = 2,  /* out_f32[m, n]  += acc            (residual: h = h + proj(x))     */
+    VB200_EPI_SWIGLU = 3    /* out_bf16[m, n/2] = silu(acc[m, n]) * acc[m, n+1], n even:
+                               W holds gate and up rows interleaved (row 2j = gate_j,
+                               row 2j+1 = up_j), see vb200_interleave_rows                      */
+} vb200_epilogue;
+
+/* y = x W^T.  x [M, K] bf16 with row stride ldx, W [N, K] bf16 with row stride
+ * ldw (the layout of nn::Linear::weight), out [M, N] (or [M, N/2]) with row
+ * stride ldo; strides in elements.  K % 8 == 0, bases and strides 16-byte
+ * aligned.  M <= 64 runs the weight-streaming kernel (K split over a cluster,
+ * `splits` = 0 lets the library choose), larger M the tiled tensor-core kernel.
+ * Replaces gemm_cuda_dispatch(a, b, c, false, true) as nn::Linear::forward and
+ * FusedQKVLinear::forward_split use it (src/ops/gemm.cpp:13,183;
+ * src/nn/linear.cpp:41-48, 86-104), the residual ops::add of
+ * ModelTransformerBlock::forward (src/models/transformer_block.cpp:183-205)
+ * and silu_mul_cuda_dispatch (include/vesper/ops/elementwise.h:105) when the
+ * epilogue asks for them. */
+int vb200_linear(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                 void* out, int64_t ldo, int32_t M, int32_t N, int32_t K, int32_t epilogue, int32_t splits);
+
+/* out[2j] = a[j], out[2j+1] = b[j] for j < rows, rows of `cols` bf16 elements:
+ * builds the interleaved (gate, up) weight VB200_EPI_SWIGLU expects from
+ * SwiGLUMLP's gate_proj / up_proj weights (src/nn/swiglu.cpp:20-34). */
+int vb200_interleave_rows(int device, void* stream, const void* a, const void* b, void* out,
+                          int64_t rows, int64_t cols);
+
+/* RMSNorm over the last dimension: out_bf16[m, :] = x[m, :] * rsqrt(mean(x^2) + eps) * weight,
+ * x fp32 [M, dim] (the residual stream), weight fp32 [dim].  Replaces
+ * rms_norm_cuda_dispatch (src/ops/normalization.cpp:446-450; CPU form :451-481). */
+int vb200_rms_norm(int device, void* stream, const float* x, const float* weight, void* out_bf16,
+                   int32_t M, int32_t dim, float eps);
+
+/* out_bf16 = silu(gate) * up elementwise over n bf16 elements.  Replaces
+ * silu_mul_cuda_dispatch (src/ops/elementwise.cpp:1297-1328) for callers that
+ * keep separate gate / up projections. */
+int vb200_silu_mul(int device, void* stream, const void* gate, const void* up, void* out, int64_t n);
+
+/* out_f32[m, :] = table_bf16[ids[m], :], ids int32 (ids64 == 0) or int64.
+ * Replaces embedding_cuda_dispatch (include/vesper/ops/embedding.h:19).  An id
+ * outside [0, vocab) writes zeros and sets the kernel status word. */
+int vb200_embedding(int device, void* stream, const void* ids, int32_t ids64, const void* table,
+                    float* out, int32_t M, int32_t dim, int32_t vocab);
+
+/* Greedy step: out_ids[b] = argmax_v logits[b, v] (first maximum wins, as
+ * argmax_cpu_dispatch, src/ops/sampling_ops.cpp:18-38; replaces
+ * argmax_cuda_dispatch, include/vesper/ops/sampling_ops.h:62).  Optional, all
+ * on the device so a generation loop needs no host round trip
+ * (src/generation/generator.cpp:75-131):
+ *   history + history_ld + step : also stores the id at history[b*history_ld + step]
+ *   pos_dev[B] + pos_base       : when pos_dev is given the column is pos_dev[b] instead
+ *                                 of `step` (e.g. the per-sequence cache lengths the decode
+ *                                 kernel advances, so a replayed CUDA graph needs no new
+ *                                 arguments) and the number generated so far is
+ *                                 pos_dev[b] - pos_base + 1, else step + 1
+ *   stop_ids[n_stop], done[B]   : done[b] |= id in stop_ids (check_stop_tokens,
+ *                                 src/ops/sampling_ops.cpp:263-288), applied
+ *                                 when the number generated >= min_new_tokens */
+typedef struct vb200_greedy_args {
+    size_t struct_size;
+    int32_t device;
+    void* stream;
+    const float* logits;   /* [B, vocab], row stride ld_logits */
+    int64_t ld_logits;
+    int32_t B, vocab;
+    int32_t* out_ids;      /* [B] */
+    int32_t* history;      /* nullable */
+    int64_t history_ld;
+    int32_t step;
+    const int32_t* stop_ids;  /* nullable, device */
+    int32_t n_stop;
+    int32_t min_new_tokens;
+    int32_t* done;         /* nullable, [B] */
+    const int32_t* pos_dev;   /* nullable, device [B] */
+    int32_t pos_base;
+} vb200_greedy_args;
+int vb200_greedy_step(const vb200_greedy_args* a);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VESPER_B200_BLOCK_H */

@@ -64,6 +64,14 @@ class Oracle:
         L.vo_decode_ragged.argtypes = [_f32p] * 3 + [C.POINTER(C.c_int32)] + [_f32p] * 2 + [_i64] * 5
         L.vo_lse_combine.argtypes = [_f32p] * 5 + [_i64] * 3
         L.vo_bf16_round_array.argtypes = [_f32p, _f32p, _i64]
+        _i32p = C.POINTER(C.c_int32)
+        L.vo_linear.argtypes = [_f32p] * 3 + [_i64] * 3
+        L.vo_rms_norm.argtypes = [_f32p] * 3 + [_i64] * 2 + [C.c_float]
+        L.vo_silu_mul.argtypes = [_f32p] * 3 + [_i64]
+        L.vo_embedding.argtypes = [_i32p, _f32p, _f32p] + [_i64] * 3
+        L.vo_embedding.restype = C.c_int
+        L.vo_argmax.argtypes = [_f32p, _i32p, _i64, _i64]
+        L.vo_check_stop_tokens.argtypes = [_i32p, _i32p, _i64, C.POINTER(_i64), _i64, _i64, _i64]
 
     def flash_attention(self, q, k, v, scale, causal=True):
         q, k, v = _f32(q), _f32(k), _f32(v)
@@ -157,6 +165,51 @@ class Oracle:
         self.lib.vo_bf16_round_array(_fp(x), _fp(out), x.size)
         return out
 
+    # ---- decoder-block operators (vesper_block_oracle.c) ----
+    def linear(self, x, w):
+        x, w = _f32(x), _f32(w)
+        M, K = x.shape
+        N = w.shape[0]
+        y = np.empty((M, N), np.float32)
+        self.lib.vo_linear(_fp(x), _fp(w), _fp(y), M, N, K)
+        return y
+
+    def rms_norm(self, x, w, eps):
+        x, w = _f32(x), _f32(w)
+        y = np.empty_like(x)
+        self.lib.vo_rms_norm(_fp(x), _fp(w), _fp(y), x.size // x.shape[-1], x.shape[-1], eps)
+        return y
+
+    def silu_mul(self, gate, up):
+        gate, up = _f32(gate), _f32(up)
+        y = np.empty_like(gate)
+        self.lib.vo_silu_mul(_fp(gate), _fp(up), _fp(y), gate.size)
+        return y
+
+    def embedding(self, ids, table):
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        table = _f32(table)
+        y = np.empty(ids.shape + (table.shape[1],), np.float32)
+        rc = self.lib.vo_embedding(ids.ctypes.data_as(C.POINTER(C.c_int32)), _fp(table), _fp(y), ids.size, table.shape[0], table.shape[1])
+        if rc != 0:
+            raise IndexError("embedding index out of bounds")
+        return y
+
+    def argmax(self, logits):
+        logits = _f32(logits)
+        out = np.empty(logits.shape[0], np.int32)
+        self.lib.vo_argmax(_fp(logits), out.ctypes.data_as(C.POINTER(C.c_int32)), logits.shape[0], logits.shape[1])
+        return out
+
+    def check_stop_tokens(self, tokens, stop_ids, min_generated, generated_count):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        stop = np.ascontiguousarray(stop_ids, dtype=np.int64)
+        out = np.empty(tokens.shape, np.int32)
+        self.lib.vo_check_stop_tokens(tokens.ctypes.data_as(C.POINTER(C.c_int32)), out.ctypes.data_as(C.POINTER(C.c_int32)),
+                                      tokens.size, stop.ctypes.data_as(C.POINTER(_i64)), stop.size, min_generated, generated_count)
+        return out
+
+
 
 class Ref:
     """The unmodified reference CPU implementation (only where it was built)."""
@@ -187,6 +240,23 @@ class Ref:
         L.ref_gqa_free.argtypes = [C.c_void_p]
         L.ref_gqa_forward.argtypes = [C.c_void_p, _f32p, _f32p] + [_i64] * 3 + [C.c_int]
         L.ref_gqa_forward_cached.argtypes = [C.c_void_p, C.c_void_p, _f32p, _f32p] + [_i64] * 4
+        _i32p = C.POINTER(C.c_int32)
+        L.ref_linear.argtypes = [_f32p] * 3 + [_i64] * 3
+        L.ref_rms_norm.argtypes = [_f32p] * 3 + [_i64] * 2 + [C.c_float]
+        L.ref_silu_mul.argtypes = [_f32p] * 3 + [_i64]
+        L.ref_embedding.argtypes = [_i32p, _f32p, _f32p] + [_i64] * 3
+        L.ref_argmax.argtypes = [_f32p, _i32p, _i64, _i64]
+        L.ref_model_new.argtypes = [_i64] * 7 + [C.c_float, C.c_float]
+        L.ref_model_new.restype = C.c_void_p
+        L.ref_model_free.argtypes = [C.c_void_p]
+        L.ref_model_param_names.argtypes = [C.c_void_p, C.c_char_p, _i64]
+        L.ref_model_param_names.restype = _i64
+        L.ref_model_set_param.argtypes = [C.c_void_p, C.c_char_p, _f32p, _i64]
+        L.ref_model_forward.argtypes = [C.c_void_p, _i32p, _i64, _i64, _f32p]
+        L.ref_model_init_cache.argtypes = [C.c_void_p, _i64]
+        L.ref_model_forward_with_cache.argtypes = [C.c_void_p, _i32p, _i64, _i64, _i64, _f32p]
+        L.ref_generate_greedy.argtypes = [C.c_void_p, _i32p, _i64, _i64, _i64, C.POINTER(_i64), _i64, _i64, _i32p]
+        L.ref_generate_greedy.restype = _i64
 
     def _chk(self, rc):
         if rc != 0:
@@ -307,3 +377,96 @@ class Ref:
 
     def gqa(self, C_, Hq, Hkv, max_seq, theta, wqkv, wo):
         return Ref.GQA(self, C_, Hq, Hkv, max_seq, theta, wqkv, wo)
+
+    # ---- decoder-block operators and the model, through the reference's own classes ----
+    def linear(self, x, w):
+        x, w = _f32(x), _f32(w)
+        y = np.empty((x.shape[0], w.shape[0]), np.float32)
+        self._chk(self.lib.ref_linear(_fp(x), _fp(w), _fp(y), x.shape[0], w.shape[0], x.shape[1]))
+        return y
+
+    def rms_norm(self, x, w, eps):
+        x, w = _f32(x), _f32(w)
+        y = np.empty_like(x)
+        self._chk(self.lib.ref_rms_norm(_fp(x), _fp(w), _fp(y), x.size // x.shape[-1], x.shape[-1], eps))
+        return y
+
+    def silu_mul(self, gate, up):
+        gate, up = _f32(gate), _f32(up)
+        y = np.empty_like(gate)
+        self._chk(self.lib.ref_silu_mul(_fp(gate), _fp(up), _fp(y), gate.size))
+        return y
+
+    def embedding(self, ids, table):
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        table = _f32(table)
+        y = np.empty(ids.shape + (table.shape[1],), np.float32)
+        self._chk(self.lib.ref_embedding(ids.ctypes.data_as(C.POINTER(C.c_int32)), _fp(table), _fp(y), ids.size, table.shape[0], table.shape[1]))
+        return y
+
+    def argmax(self, logits):
+        logits = _f32(logits)
+        out = np.empty(logits.shape[0], np.int32)
+        self._chk(self.lib.ref_argmax(_fp(logits), out.ctypes.data_as(C.POINTER(C.c_int32)), logits.shape[0], logits.shape[1]))
+        return out
+
+    class Model:
+        """models::TransformerLM (Llama style: RMSNorm, RoPE, SwiGLU, no bias, untied head)."""
+
+        def __init__(self, ref, vocab, dim, n_layers, n_heads, n_kv_heads, ffn_hidden, max_seq_len, norm_eps=1e-6, rope_base=10000.0):
+            self.ref = ref
+            self.vocab = vocab
+            self.h = ref.lib.ref_model_new(vocab, dim, n_layers, n_heads, n_kv_heads, ffn_hidden, max_seq_len, norm_eps, rope_base)
+            if not self.h:
+                raise RuntimeError(ref.lib.ref_last_error().decode())
+
+        def param_shapes(self):
+            n = self.ref.lib.ref_model_param_names(self.h, None, 0)
+            buf = C.create_string_buffer(int(n))
+            self.ref.lib.ref_model_param_names(self.h, buf, n)
+            out = {}
+            for line in buf.value.decode().splitlines():
+                parts = line.split()
+                out[parts[0]] = tuple(int(p) for p in parts[1:])
+            return out
+
+        def set_param(self, name, value):
+            value = _f32(value)
+            self.ref._chk(self.ref.lib.ref_model_set_param(self.h, name.encode(), _fp(value), value.size))
+
+        def forward(self, ids):
+            ids = np.ascontiguousarray(ids, dtype=np.int32)
+            B, T = ids.shape
+            y = np.empty((B, T, self.vocab), np.float32)
+            self.ref._chk(self.ref.lib.ref_model_forward(self.h, ids.ctypes.data_as(C.POINTER(C.c_int32)), B, T, _fp(y)))
+            return y
+
+        def init_cache(self, B):
+            self.ref._chk(self.ref.lib.ref_model_init_cache(self.h, B))
+
+        def forward_with_cache(self, ids, start_pos):
+            ids = np.ascontiguousarray(ids, dtype=np.int32)
+            B, T = ids.shape
+            y = np.empty((B, T, self.vocab), np.float32)
+            self.ref._chk(self.ref.lib.ref_model_forward_with_cache(self.h, ids.ctypes.data_as(C.POINTER(C.c_int32)), B, T, start_pos, _fp(y)))
+            return y
+
+        def generate_greedy(self, prompt, max_new, stop_ids=(), min_new=0):
+            prompt = np.ascontiguousarray(prompt, dtype=np.int32)
+            B, P = prompt.shape
+            out = np.zeros((B, P + max_new), np.int32)
+            stop = np.ascontiguousarray(list(stop_ids), dtype=np.int64)
+            cols = self.ref.lib.ref_generate_greedy(self.h, prompt.ctypes.data_as(C.POINTER(C.c_int32)), B, P, max_new,
+                                                    stop.ctypes.data_as(C.POINTER(_i64)), stop.size, min_new,
+                                                    out.ctypes.data_as(C.POINTER(C.c_int32)))
+            if cols < 0:
+                raise RuntimeError(self.ref.lib.ref_last_error().decode())
+            return out.reshape(-1)[: B * cols].reshape(B, cols)
+
+        def __del__(self):
+            if getattr(self, "h", None):
+                self.ref.lib.ref_model_free(self.h)
+                self.h = None
+
+    def model(self, *args, **kw):
+        return Ref.Model(self, *args, **kw)

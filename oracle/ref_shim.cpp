@@ -23,7 +23,15 @@
 #include <vesper/nn/transformer.h>
 #include <vesper/nn/gqa_attention.h>
 #include <vesper/autograd/guard.h>
+#include <vesper/ops/gemm.h>
+#include <vesper/ops/normalization.h>
+#include <vesper/ops/elementwise.h>
+#include <vesper/ops/embedding.h>
+#include <vesper/ops/sampling_ops.h>
+#include <vesper/models/transformer.h>
+#include <vesper/generation/generator.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <cstring>
 #include <string>
@@ -240,6 +248,142 @@ int ref_gqa_forward_cached(void* m, void* cache, const float* x, float* y,
         Tensor ty = g->forward(tx, static_cast<vesper::nn::KVCache*>(cache), start_pos);
         to_host(ty, y);
         return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+
+// ---- decoder-block operators --------------------------------------------------------------
+// y[M,N] = x[M,K] w[N,K]^T exactly as nn::Linear::forward does it: matmul(x, weight.transpose(0,1))
+// (src/nn/linear.cpp:41-48).
+int ref_linear(const float* x, const float* w, float* y, int64_t M, int64_t N, int64_t K) {
+    try {
+        vesper::autograd::NoGradGuard ng;
+        Tensor tx = from_host(x, {M, K}), tw = from_host(w, {N, K});
+        Tensor ty = vesper::ops::matmul(tx, tw.transpose(0, 1));
+        to_host(ty, y);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+int ref_rms_norm(const float* x, const float* w, float* y, int64_t M, int64_t dim, float eps) {
+    try {
+        vesper::autograd::NoGradGuard ng;
+        Tensor ty = vesper::ops::rms_norm(from_host(x, {M, dim}), {dim}, from_host(w, {dim}), eps);
+        to_host(ty, y);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+int ref_silu_mul(const float* gate, const float* up, float* y, int64_t n) {
+    try {
+        vesper::autograd::NoGradGuard ng;
+        Tensor ty = vesper::ops::silu_mul(from_host(gate, {n}), from_host(up, {n}));
+        to_host(ty, y);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+int ref_embedding(const int32_t* ids, const float* table, float* y, int64_t M, int64_t vocab, int64_t dim) {
+    try {
+        vesper::autograd::NoGradGuard ng;
+        Tensor ti = vesper::empty({M}, DType::Int32, Device::CPU);
+        std::memcpy(ti.data_ptr<int32_t>(), ids, sizeof(int32_t) * M);
+        Tensor ty = vesper::ops::embedding(ti, from_host(table, {vocab, dim}));
+        to_host(ty, y);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+int ref_argmax(const float* logits, int32_t* out, int64_t B, int64_t vocab) {
+    try {
+        vesper::autograd::NoGradGuard ng;
+        Tensor t = vesper::ops::argmax(from_host(logits, {B, vocab}), -1);
+        std::memcpy(out, t.data_ptr<int32_t>(), sizeof(int32_t) * B);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+
+// ---- model level: models::TransformerLM with caller-supplied weights ----------------------
+void* ref_model_new(int64_t vocab, int64_t dim, int64_t n_layers, int64_t n_heads, int64_t n_kv_heads,
+                    int64_t ffn_hidden, int64_t max_seq_len, float norm_eps, float rope_base) {
+    try {
+        vesper::models::TransformerConfig c;
+        c.vocab_size = vocab; c.dim = dim; c.n_layers = n_layers; c.n_heads = n_heads; c.n_kv_heads = n_kv_heads;
+        c.ffn_hidden_dim = ffn_hidden; c.max_seq_len = max_seq_len; c.norm_eps = norm_eps; c.use_rms_norm = true;
+        c.rope_base = rope_base; c.use_bias = false; c.tie_word_embeddings = false; c.dropout = 0.0f;
+        auto* m = new vesper::models::TransformerLM(c);
+        m->eval();
+        return m;
+    } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
+}
+void ref_model_free(void* m) { delete static_cast<vesper::models::TransformerLM*>(m); }
+// Parameter names, one per line as "name d0 d1 ...", into buf; returns the length needed.
+int64_t ref_model_param_names(void* m, char* buf, int64_t buflen) {
+    std::string out;
+    for (auto& kv : static_cast<vesper::models::TransformerLM*>(m)->named_parameters_ptrs()) {
+        out += kv.first;
+        for (auto d : kv.second->shape()) out += " " + std::to_string(d);
+        out += "\n";
+    }
+    if (buf && buflen > 0) {
+        const int64_t n = std::min<int64_t>(buflen - 1, static_cast<int64_t>(out.size()));
+        std::memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    return static_cast<int64_t>(out.size()) + 1;
+}
+int ref_model_set_param(void* m, const char* name, const float* data, int64_t numel) {
+    try {
+        auto params = static_cast<vesper::models::TransformerLM*>(m)->named_parameters_ptrs();
+        auto it = params.find(name);
+        if (it == params.end()) { g_err = std::string("no parameter ") + name; return -1; }
+        if (it->second->numel() != numel) { g_err = std::string("size mismatch for ") + name; return -1; }
+        it->second->copy_from_host(data);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+static Tensor ids_tensor(const int32_t* ids, int64_t B, int64_t T) {
+    Tensor t = vesper::empty({B, T}, DType::Int32, Device::CPU);
+    std::memcpy(t.data_ptr<int32_t>(), ids, sizeof(int32_t) * B * T);
+    return t;
+}
+// TransformerLM::forward (uncached, causal): logits [B,T,vocab]  (src/models/transformer.cpp:97-150)
+int ref_model_forward(void* m, const int32_t* ids, int64_t B, int64_t T, float* logits) {
+    try {
+        vesper::autograd::NoGradGuard ng;
+        Tensor y = static_cast<vesper::models::TransformerLM*>(m)->forward(ids_tensor(ids, B, T));
+        to_host(y, logits);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+int ref_model_init_cache(void* m, int64_t B) {
+    try { static_cast<vesper::models::TransformerLM*>(m)->init_cache(B, Device::CPU); return 0; }
+    catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+// TransformerLM::forward_with_cache (src/models/transformer.cpp:152-188): logits [B,T,vocab]
+int ref_model_forward_with_cache(void* m, const int32_t* ids, int64_t B, int64_t T, int64_t start_pos, float* logits) {
+    try {
+        vesper::autograd::NoGradGuard ng;
+        Tensor y = static_cast<vesper::models::TransformerLM*>(m)->forward_with_cache(ids_tensor(ids, B, T), start_pos);
+        to_host(y, logits);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+// generation::Generator::generate with greedy sampling (src/generation/generator.cpp:36-142):
+// out [B, P + max_new] int32; returns the number of columns written or -1.
+int64_t ref_generate_greedy(void* m, const int32_t* prompt, int64_t B, int64_t P, int64_t max_new,
+                            const int64_t* stop_ids, int64_t n_stop, int64_t min_new, int32_t* out) {
+    try {
+        vesper::autograd::NoGradGuard ng;
+        vesper::generation::Generator gen(static_cast<vesper::models::TransformerLM*>(m));
+        vesper::generation::SamplingParams sp;
+        sp.do_sample = false; sp.max_new_tokens = max_new; sp.min_new_tokens = min_new;
+        for (int64_t i = 0; i < n_stop; ++i) sp.stop_token_ids.push_back(stop_ids[i]);
+        Tensor r = gen.generate(ids_tensor(prompt, B, P), sp);
+        Tensor rc = r.is_contiguous() ? r : r.contiguous();
+        const int64_t cols = rc.shape()[1];
+        if (rc.dtype() == DType::Int32) {
+            std::memcpy(out, rc.data_ptr<int32_t>(), sizeof(int32_t) * B * cols);
+        } else if (rc.dtype() == DType::Int64) {
+            const int64_t* p = rc.data_ptr<int64_t>();
+            for (int64_t i = 0; i < B * cols; ++i) out[i] = static_cast<int32_t>(p[i]);
+        } else { g_err = "generate returned an unexpected dtype"; return -1; }
+        return cols;
     } catch (const std::exception& e) { g_err = e.what(); return -1; }
 }
 

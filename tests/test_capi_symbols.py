@@ -9,8 +9,8 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "vesper_b200.h")).read()
+def declared_symbols(header="vesper_b200.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(vb200_[a-z0-9_]+)\s*\(", text)))
 
@@ -22,6 +22,10 @@ def test_header_symbols_are_exported(lib):
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/vesper_b200.h but not exported"
     assert sorted(capi.EXPORTS) == names
+    block = declared_symbols("vesper_b200_block.h")
+    for n in block:
+        assert hasattr(lib, n), f"{n} declared in include/vesper_b200_block.h but not exported"
+    assert sorted(capi.BLOCK_EXPORTS) == block
 
 
 def test_struct_layout_and_host_helpers(lib):

@@ -56,6 +56,22 @@ EXPORTS = [
     "vb200_strerror", "vb200_last_error_detail", "vb200_abi_version", "vb200_launch_count",
     "vb200_reset_launch_count", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
 ]
+BLOCK_EXPORTS = [
+    "vb200_linear", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
+]
+
+
+class GreedyArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_size_t), ("device", C.c_int32), ("stream", C.c_void_p),
+        ("logits", C.c_void_p), ("ld_logits", C.c_int64), ("B", C.c_int32), ("vocab", C.c_int32),
+        ("out_ids", C.c_void_p), ("history", C.c_void_p), ("history_ld", C.c_int64), ("step", C.c_int32),
+        ("stop_ids", C.c_void_p), ("n_stop", C.c_int32), ("min_new_tokens", C.c_int32), ("done", C.c_void_p),
+        ("pos_dev", C.c_void_p), ("pos_base", C.c_int32),
+    ]
+
+
+EPI_BF16, EPI_F32, EPI_ADD_F32, EPI_SWIGLU = 0, 1, 2, 3
 
 _lib = None
 
@@ -96,6 +112,13 @@ def load():
     L.vb200_check_kernel_status.argtypes = [C.c_int, C.c_void_p]
     L.vb200_profile_enable.argtypes = [C.c_int]
     L.vb200_profile_read.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
+    # decoder-block operators (include/vesper_b200_block.h)
+    L.vb200_linear.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64] + [C.c_int32] * 5
+    L.vb200_interleave_rows.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]
+    L.vb200_rms_norm.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_float]
+    L.vb200_silu_mul.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]
+    L.vb200_embedding.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32]
+    L.vb200_greedy_step.argtypes = [C.POINTER(GreedyArgs)]
     _lib = L
     return L
 
@@ -241,3 +264,64 @@ def profile_read():
     ms, n = C.c_double(0.0), C.c_uint64(0)
     check(load().vb200_profile_read(C.byref(ms), C.byref(n)))
     return ms.value, n.value
+
+
+# ---- decoder-block operators ---------------------------------------------------------------
+def linear(x, w, out, epilogue=EPI_BF16, splits=0, stream=None):
+    """out = epilogue(x @ w.T): x [M,K] bf16, w [N,K] bf16 (row strides honoured)."""
+    M, K = x.shape
+    N = w.shape[0]
+    check(load().vb200_linear(x.device.index or 0, _stream_ptr(stream), _ptr(x), x.stride(0), _ptr(w), w.stride(0),
+                              _ptr(out), out.stride(0), M, N, K, epilogue, splits))
+    return out
+
+
+def interleave_rows(a, b, out, stream=None):
+    check(load().vb200_interleave_rows(a.device.index or 0, _stream_ptr(stream), _ptr(a), _ptr(b), _ptr(out), a.shape[0], a.shape[1]))
+    return out
+
+
+def rms_norm(x, weight, out, eps, stream=None):
+    M, dim = x.shape
+    check(load().vb200_rms_norm(x.device.index or 0, _stream_ptr(stream), _ptr(x), _ptr(weight), _ptr(out), M, dim, eps))
+    return out
+
+
+def silu_mul(gate, up, out, stream=None):
+    check(load().vb200_silu_mul(gate.device.index or 0, _stream_ptr(stream), _ptr(gate), _ptr(up), _ptr(out), gate.numel()))
+    return out
+
+
+def embedding(ids, table, out, stream=None):
+    import torch
+    ids64 = 1 if ids.dtype == torch.int64 else 0
+    check(load().vb200_embedding(table.device.index or 0, _stream_ptr(stream), _ptr(ids), ids64, _ptr(table), _ptr(out),
+                                 ids.numel(), table.shape[1], table.shape[0]))
+    return out
+
+
+def greedy_step(logits, out_ids, *, history=None, step=0, stop_ids=None, min_new_tokens=0, done=None, pos_dev=None,
+                pos_base=0, stream=None):
+    a = GreedyArgs()
+    a.struct_size = C.sizeof(GreedyArgs)
+    a.device = logits.device.index or 0
+    a.stream = _stream_ptr(stream)
+    a.logits = _ptr(logits)
+    a.ld_logits = logits.stride(0)
+    a.B, a.vocab = logits.shape
+    a.out_ids = _ptr(out_ids)
+    if history is not None:
+        a.history = _ptr(history)
+        a.history_ld = history.stride(0)
+    a.step = step
+    if stop_ids is not None and stop_ids.numel() > 0:
+        a.stop_ids = _ptr(stop_ids)
+        a.n_stop = stop_ids.numel()
+    a.min_new_tokens = min_new_tokens
+    if done is not None:
+        a.done = _ptr(done)
+    if pos_dev is not None:
+        a.pos_dev = _ptr(pos_dev)
+        a.pos_base = pos_base
+    check(load().vb200_greedy_step(C.byref(a)))
+    return out_ids

@@ -424,4 +424,75 @@ int vb200_repeat_kv(int device, void* stream, int32_t dtype, const vb200_tensor4
     return launch_repeat_kv(static_cast<cudaStream_t>(stream), dtype, to_view(*in), out, B, Hkv, S, D, n_rep);
 }
 
+// ---- decoder-block operators (vesper_b200_block.h) ---------------------------------------------
+
+static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+int vb200_linear(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                 void* out, int64_t ldo, int32_t M, int32_t N, int32_t K, int32_t epilogue, int32_t splits) {
+    if (!x || !w || !out || M <= 0 || N <= 0 || K <= 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear: null pointer or non-positive size");
+    if (epilogue < VB200_EPI_BF16 || epilogue > VB200_EPI_SWIGLU) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear: unknown epilogue");
+    if (ldx < K || ldw < K) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear: ldx and ldw must be >= K");
+    const int64_t out_cols = epilogue == VB200_EPI_SWIGLU ? N / 2 : N;
+    if (ldo < out_cols) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear: ldo smaller than the output row");
+    if (epilogue == VB200_EPI_SWIGLU && N % 2 != 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear: the SwiGLU epilogue needs an even N");
+    const int out_elem = (epilogue == VB200_EPI_F32 || epilogue == VB200_EPI_ADD_F32) ? 4 : 2;
+    if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || (ldo * out_elem) % 16 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(out))
+        return set_detail(VB200_ERR_ALIGNMENT, "vb200_linear: K % 8, and 16-byte aligned bases and row strides, are required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    LinearParams p{};
+    p.x = x; p.ldx = ldx; p.w = w; p.ldw = ldw; p.out = out; p.ldo = ldo;
+    p.M = M; p.N = N; p.K = K; p.epilogue = epilogue; p.splits = splits;
+    p.status = kernel_status_word();
+    if (!p.status) return VB200_ERR_CUDA;
+    return launch_linear(static_cast<cudaStream_t>(stream), p);
+}
+
+int vb200_interleave_rows(int device, void* stream, const void* a, const void* b, void* out, int64_t rows, int64_t cols) {
+    if (!a || !b || !out || rows <= 0 || cols <= 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_interleave_rows: bad arguments");
+    if (!aligned16(a) || !aligned16(b) || !aligned16(out)) return set_detail(VB200_ERR_ALIGNMENT, "vb200_interleave_rows: 16-byte alignment required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    return launch_interleave_rows(static_cast<cudaStream_t>(stream), a, b, out, rows, cols);
+}
+
+int vb200_rms_norm(int device, void* stream, const float* x, const float* weight, void* out_bf16,
+                   int32_t M, int32_t dim, float eps) {
+    if (!x || !weight || !out_bf16 || M <= 0 || dim <= 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_rms_norm: bad arguments");
+    if (!aligned16(x) || !aligned16(weight) || !aligned16(out_bf16)) return set_detail(VB200_ERR_ALIGNMENT, "vb200_rms_norm: 16-byte alignment required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    return launch_rms_norm(static_cast<cudaStream_t>(stream), x, weight, out_bf16, M, dim, eps);
+}
+
+int vb200_silu_mul(int device, void* stream, const void* gate, const void* up, void* out, int64_t n) {
+    if (!gate || !up || !out || n <= 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_silu_mul: bad arguments");
+    if (!aligned16(gate) || !aligned16(up) || !aligned16(out)) return set_detail(VB200_ERR_ALIGNMENT, "vb200_silu_mul: 16-byte alignment required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    return launch_silu_mul(static_cast<cudaStream_t>(stream), gate, up, out, n);
+}
+
+int vb200_embedding(int device, void* stream, const void* ids, int32_t ids64, const void* table,
+                    float* out, int32_t M, int32_t dim, int32_t vocab) {
+    if (!ids || !table || !out || M <= 0 || dim <= 0 || vocab <= 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_embedding: bad arguments");
+    if (!aligned16(table) || !aligned16(out)) return set_detail(VB200_ERR_ALIGNMENT, "vb200_embedding: 16-byte alignment required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    int* status = kernel_status_word();
+    if (!status) return VB200_ERR_CUDA;
+    return launch_embedding(static_cast<cudaStream_t>(stream), ids, ids64, table, out, M, dim, vocab, status);
+}
+
+int vb200_greedy_step(const vb200_greedy_args* a) {
+    if (!a || a->struct_size != sizeof(vb200_greedy_args)) return set_detail(VB200_ERR_INVALID_ARG, "vb200_greedy_args: null or struct_size mismatch");
+    if (!a->logits || !a->out_ids || a->B <= 0 || a->vocab <= 0 || a->ld_logits < a->vocab)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_greedy_step: bad arguments");
+    if (a->n_stop > 0 && !a->stop_ids) return set_detail(VB200_ERR_INVALID_ARG, "vb200_greedy_step: n_stop > 0 without stop_ids");
+    DeviceGuard g;
+    if (int rc = g.init(a->device)) return rc;
+    return launch_greedy_step(static_cast<cudaStream_t>(a->stream), *a);
+}
+
 }  // extern "C"

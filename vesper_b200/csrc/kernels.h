@@ -2,6 +2,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "../../include/vesper_b200_block.h"
 
 namespace vb200 {
 
@@ -76,5 +77,25 @@ int decode_tile_keys();
 int launch_decode(cudaStream_t s, const DecodeParams& p);
 int launch_lse_combine(cudaStream_t s, const float* partials, int R, long long rows, int D,
                        int dtype, void* out, float* lse);
+
+// ---- linear_sm100.cu ----
+struct LinearParams {
+    const void* x;  long long ldx;   // [M, K] bf16
+    const void* w;  long long ldw;   // [N, K] bf16
+    void* out;      long long ldo;   // [M, N] bf16 / fp32, or [M, N/2] bf16 for the SwiGLU epilogue
+    int M, N, K;
+    int epilogue;                    // vb200_epilogue
+    int splits;                      // K slices per cluster of the skinny kernel, 0 = choose
+    int* status;                     // device status word (bounded waits)
+};
+int launch_linear(cudaStream_t s, const LinearParams& p);
+
+// ---- block_ops.cu ----
+int launch_interleave_rows(cudaStream_t s, const void* a, const void* b, void* out, long long rows, long long cols);
+int launch_rms_norm(cudaStream_t s, const float* x, const float* weight, void* out_bf16, int M, int dim, float eps);
+int launch_silu_mul(cudaStream_t s, const void* gate, const void* up, void* out, long long n);
+int launch_embedding(cudaStream_t s, const void* ids, int ids64, const void* table, float* out, int M, int dim,
+                     int vocab, int* status);
+int launch_greedy_step(cudaStream_t s, const vb200_greedy_args& a);
 
 }  // namespace vb200
