@@ -120,6 +120,54 @@ def main():
     save("gqa_module_forward", wqkv=wqkv, wo=wo, x=x, y=g.forward(x, True),
          dims=np.array([Cdim, Hq, Hkv, T], np.int32))
 
+    block_and_model_fixtures(r)
+
+
+MODEL_CASES = {
+    # name: (vocab, dim, n_layers, n_heads, n_kv_heads, ffn_hidden, max_seq_len, weight seed, B, T)
+    "model_gqa_d128": (384, 256, 2, 2, 1, 320, 48, 21, 2, 20),     # grouped-query, head_dim 128
+    "model_gqa_d64": (384, 256, 1, 4, 2, 320, 48, 22, 2, 20),      # grouped-query, head_dim 64
+    "model_mha_d128": (384, 256, 2, 2, 2, 320, 48, 23, 2, 12),     # Hkv == Hq: the reference's cached path and Generator are usable
+}
+
+
+def block_and_model_fixtures(r):
+    """Decoder-block operators and models::TransformerLM through the reference's own classes."""
+    sys.path.insert(0, os.path.join(HERE, ".."))
+    from helpers import bf16_round, model_weights
+    from vesper_b200.model import param_shapes
+    rng = np.random.default_rng(4321)
+    # -- nn::Linear::forward = matmul(x, W^T) (src/nn/linear.cpp:41-48; src/ops/cpu/gemm_cpu.cpp:12-48)
+    x = bf16_round(rng.standard_normal((9, 200)).astype(np.float32))
+    w = bf16_round((rng.standard_normal((70, 200)) / 14.0).astype(np.float32))
+    g = (1.0 + 0.1 * rng.standard_normal(200)).astype(np.float32)
+    gate = rng.standard_normal((9, 70)).astype(np.float32) * 3.0
+    up = rng.standard_normal((9, 70)).astype(np.float32)
+    ids = rng.integers(0, 70, size=(11,)).astype(np.int32)
+    logits = rng.standard_normal((5, 333)).astype(np.float32)
+    logits[2, 10] = logits[2, 300] = 8.0            # a tie: the first index wins (src/ops/sampling_ops.cpp:28-33)
+    save("block_ops", x=x, w=w, y_linear=r.linear(x, w), g=g, y_rms=r.rms_norm(x, g, 1e-6), eps=np.float32(1e-6),
+         gate=gate, up=up, y_silu_mul=r.silu_mul(gate, up), ids=ids, y_embedding=r.embedding(ids, w),
+         logits=logits, y_argmax=r.argmax(logits))
+    # -- models::TransformerLM::forward (uncached, causal; src/models/transformer.cpp:97-150) on seeded weights
+    #    (tests/helpers.py: model_weights(param_shapes, seed, std=0.06)); for the MHA case also
+    #    forward_with_cache (:152-188) and generation::Generator::generate greedy (src/generation/generator.cpp:36-142).
+    for name, (vocab, dim, n_layers, Hq, Hkv, ffn, max_seq, seed, B, T) in MODEL_CASES.items():
+        shapes = param_shapes(vocab, dim, n_layers, Hq, Hkv, ffn)
+        wts = model_weights(shapes, seed, std=0.06)
+        m = r.model(vocab, dim, n_layers, Hq, Hkv, ffn, max_seq)
+        assert {k: tuple(v) for k, v in m.param_shapes().items()} == shapes
+        for k, v in wts.items():
+            m.set_param(k, v)
+        tok = np.random.default_rng(seed + 100).integers(0, vocab, size=(B, T)).astype(np.int32)
+        out = dict(cfg=np.array([vocab, dim, n_layers, Hq, Hkv, ffn, max_seq, seed], np.int64), ids=tok, logits=m.forward(tok))
+        if Hkv == Hq:
+            m.init_cache(B)
+            out["logits_cached_prefill"] = m.forward_with_cache(tok, 0)
+            out["logits_cached_step"] = m.forward_with_cache(tok[:, :1], T)
+            out["greedy"] = m.generate_greedy(tok, 10)
+        save(name, **out)
+
 
 if __name__ == "__main__":
     main()

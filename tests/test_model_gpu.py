@@ -1,0 +1,109 @@
+"""models::TransformerLM and generation::Generator of the host layer on the GPU (through the C facade of
+libvesper_b200_host.so) against the CPU oracle composition and the reference fixtures.
+
+Tolerance: weights are bf16 on both sides (same values); the GPU also keeps activations between
+operators in bf16 (2^-9 relative rounding each) while the oracle is fp32 throughout, so logits are
+compared at 2e-2 of the largest logit magnitude of the case."""
+import numpy as np
+import pytest
+
+from helpers import OracleDecoder, golden, model_weights
+from vesper_b200.model import param_shapes
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_TOL = 2e-2
+
+
+def _build(name, oracle):
+    from vesper_b200.model import TransformerLM
+    g = golden(name)
+    vocab, dim, n_layers, Hq, Hkv, ffn, max_seq, seed = [int(v) for v in g["cfg"]]
+    w = model_weights(param_shapes(vocab, dim, n_layers, Hq, Hkv, ffn), seed, std=0.06)
+    m = TransformerLM(vocab, dim, n_layers, Hq, Hkv, ffn, max_seq)
+    for k, v in w.items():
+        m.set_param(k, v)
+    d = OracleDecoder(oracle, w, n_layers=n_layers, n_heads=Hq, n_kv_heads=Hkv, max_seq_len=max_seq)
+    return g, m, d
+
+
+@pytest.mark.parametrize("name", ["model_gqa_d128", "model_gqa_d64", "model_mha_d128"])
+def test_prompt_pass_and_decode_steps_match_reference_logits(cuda, oracle, name):
+    from vesper_b200 import capi
+    g, m, d = _build(name, oracle)
+    ids, want = g["ids"], g["logits"]
+    B, T = ids.shape
+    scale = np.abs(want).max()
+    m.init_cache(B)
+    got = m.forward_with_cache(ids[:, : T - 4], 0)                       # prompt pass, all positions
+    assert np.abs(got - want[:, : T - 4]).max() <= LOGIT_TOL * scale
+    for t in range(T - 4, T):                                           # then one token at a time through the cache
+        step = m.forward_with_cache(ids[:, t:t + 1], t)[:, 0]
+        assert np.abs(step - want[:, t]).max() <= LOGIT_TOL * scale, t
+    last = m.forward_with_cache(ids[:, :1], T, last_only=True)          # last_only returns [B, 1, vocab]
+    assert last.shape == (B, 1, want.shape[2])
+    capi.check_kernel_status(0)
+
+
+def test_last_only_prompt_pass(cuda, oracle):
+    g, m, d = _build("model_gqa_d128", oracle)
+    ids, want = g["ids"], g["logits"]
+    m.init_cache(ids.shape[0])
+    got = m.forward_with_cache(ids, 0, last_only=True)[:, 0]
+    assert np.abs(got - want[:, -1]).max() <= LOGIT_TOL * np.abs(want).max()
+
+
+@pytest.mark.parametrize("name,use_graph", [("model_mha_d128", True), ("model_mha_d128", False), ("model_gqa_d128", True), ("model_gqa_d64", True)])
+def test_greedy_generation(cuda, oracle, name, use_graph):
+    """Every generated token must be an arg-max of the oracle's logits for the same history, up to the
+    logit tolerance (bf16 activations can flip a near-tie); where the oracle's own margin is wider
+    than the tolerance the token must be identical.  For the MHA case the oracle's tokens are the
+    reference Generator's (fixture)."""
+    g, m, d = _build(name, oracle)
+    prompt = g["ids"]
+    B, P = prompt.shape
+    max_new = 10
+    toks, t = m.generate_greedy(prompt, max_new, use_graph=use_graph)
+    assert toks.shape == (B, P + max_new) and np.array_equal(toks[:, :P], prompt)
+    assert t["decode_steps"] == max_new - 1 and t["graph_replay"] == (use_graph and "d128" in name)
+    # teacher-forced check: oracle logits along the GPU's own token history
+    d.init_cache(B)
+    logits = d.forward_with_cache(prompt, 0)[:, -1]
+    agree = 0
+    for i in range(max_new):
+        tol = LOGIT_TOL * np.abs(logits).max()
+        for b in range(B):
+            best = logits[b].max()
+            assert logits[b, toks[b, P + i]] >= best - 2 * tol, (i, b)
+            agree += int(toks[b, P + i] == int(np.argmax(logits[b])))
+        if i + 1 < max_new:
+            logits = d.forward_with_cache(toks[:, P + i:P + i + 1], P + i)[:, -1]
+    assert agree >= int(0.8 * B * max_new)
+    if "greedy" in g.files and agree == B * max_new:
+        assert np.array_equal(toks, g["greedy"])
+
+
+def test_stop_tokens_end_generation_early(cuda, oracle):
+    g, m, d = _build("model_gqa_d128", oracle)
+    prompt = g["ids"]
+    B, P = prompt.shape
+    free, _ = m.generate_greedy(prompt, 12)
+    # stop on whatever every sequence emits: each sequence's 3rd token; min_new_tokens = 3 keeps earlier hits from counting
+    stop = sorted({int(free[b, P + 2]) for b in range(B)})
+    toks, t = m.generate_greedy(prompt, 12, stop_ids=stop, min_new=3)
+    assert toks.shape[1] < P + 12                      # ended before max_new_tokens (polled every 16 steps or at the end of a step batch)
+    assert np.array_equal(toks, free[:, : toks.shape[1]])
+
+
+def test_model_argument_errors(cuda):
+    from vesper_b200.model import TransformerLM
+    m = TransformerLM(64, 256, 1, 2, 1, 320, 16)
+    with pytest.raises(RuntimeError, match="KV cache not initialized"):
+        m.forward_with_cache(np.zeros((1, 4), np.int32), 0)
+    m.init_cache(1)
+    with pytest.raises(RuntimeError, match="exceeds maximum"):
+        m.forward_with_cache(np.zeros((1, 17), np.int32), 0)
+    with pytest.raises(RuntimeError, match="no parameter named"):
+        m.set_param("layers.0.bogus", np.zeros(4, np.float32))
+    with pytest.raises(RuntimeError, match="max_seq_len"):
+        m.generate_greedy(np.zeros((1, 10), np.int32), 10)

@@ -497,9 +497,7 @@ int launch_wide(cudaStream_t s, const LinearParams& p) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    profile_mark_begin(s);
     VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, p));
-    profile_mark_end(s);
     note_launch();
     return VB200_OK;
 }
@@ -546,9 +544,7 @@ int launch_skinny(cudaStream_t s, const LinearParams& p) {
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    profile_mark_begin(s);
     VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, p, splits));
-    profile_mark_end(s);
     note_launch();
     return VB200_OK;
 }
