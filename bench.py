@@ -10,7 +10,9 @@ One "step" is one pass of the hot path over one synthetic batch:
     FLOPs = 4*B*Hq*D*S*(S+1)/2 (QK^T and PV over the causal triangle only).
   * also reported in the same line: batched GQA decode (B=32, Hq=32, Hkv=8, D=128, ragged
     contexts U[1024,8192], 256 consecutive steps) as KV-read GB/s, and -- at N>1 -- the
-    sequence-sharded long-context decode (131072 keys split over the GPUs, one all-gather).
+    sequence-sharded long-context decode (131072 keys split over the GPUs, one all-gather);
+    "model": the 24-layer Llama-style decoder around the path (8 prompts x 512 ids, prefill +
+    128 greedy tokens through the host layer's Generator) as tokens/s with the attention time share.
   * N>1: prefill and batched decode partition by (batch x kv_head) with no collective, so
     every rank runs the same per-GPU workload on its own units (weak scaling).
 
@@ -38,6 +40,7 @@ sys.path.insert(0, ROOT)
 C2 = dict(B=4, Hq=32, Hkv=8, S=2048, D=128, cap=4096, theta=10000.0)
 C3 = dict(B=32, Hq=32, Hkv=8, D=128, lo=1024, hi=8192, steps=256)
 C4 = dict(B=1, Hq=64, Hkv=8, D=128, L=131072)
+C5 = dict(vocab=32000, dim=2048, layers=24, Hq=16, Hkv=4, ffn=5632, B=8, P=512, new=128)
 
 
 def prefill_flops(c):
@@ -427,6 +430,69 @@ def bench_sharded(cx, nsteps=50):
     }
 
 
+def bench_model(cx, reps=3):
+    """C5: random-init Llama-style decoder (24 layers, d_model 2048, 16 query / 4 KV heads of 128, SwiGLU 5632,
+    RMSNorm, RoPE 1e4, vocab 32000, bf16 weights ~ N(0, 0.02)); 8 prompts of 512 uniform-random ids, prefill then
+    128 greedy tokens through generation::Generator of the host layer (device-resident loop, CUDA-graph replay).
+    Every rank runs the whole workload (units = sequences, no collective): weak scaling."""
+    import time
+
+    import numpy as np
+    from vesper_b200.model import TransformerLM, param_shapes
+    capi = cx.capi
+    c = C5
+    shapes = param_shapes(c["vocab"], c["dim"], c["layers"], c["Hq"], c["Hkv"], c["ffn"])
+    m = TransformerLM(c["vocab"], c["dim"], c["layers"], c["Hq"], c["Hkv"], c["ffn"], c["P"] + c["new"], norm_eps=1e-6, rope_base=10000.0)
+    rng = np.random.default_rng(7)
+    n_params = 0
+    for name in sorted(shapes):
+        shape = shapes[name]
+        w = np.ones(shape, np.float32) if len(shape) == 1 else (0.02 * rng.standard_normal(shape, dtype=np.float32))
+        m.set_param(name, w)
+        n_params += w.size
+    prompt = np.random.default_rng(8).integers(0, c["vocab"], size=(c["B"], c["P"])).astype(np.int32)
+    m.generate_greedy(prompt, 8)                                   # warm-up: kernels configured, buffers allocated
+    cx.sync_all()
+    pre_ms, dec_ms, wall_ms, steps = [], [], [], 0
+    for _ in range(reps):
+        cx.flush_l2()
+        cx.sync_all()
+        capi.load().vb200_reset_launch_count()
+        t0 = time.perf_counter()
+        toks, t = m.generate_greedy(prompt, c["new"])
+        wall_ms.append((time.perf_counter() - t0) * 1e3)
+        launches = int(capi.load().vb200_launch_count())
+        pre_ms.append(t["prefill_ms"]); dec_ms.append(t["decode_ms"]); steps = t["decode_steps"]
+    # attention share: the same generation, eager, with the attention kernels bracketed by events
+    capi.profile_enable(True)
+    _, tp = m.generate_greedy(prompt, c["new"], use_graph=False)
+    attn_ms, attn_launches = capi.profile_read()
+    capi.profile_enable(False)
+    capi.check_kernel_status(cx.local)
+    pre = cx.max_over_ranks(float(np.median(pre_ms)))
+    dec = cx.max_over_ranks(float(np.median(dec_ms)))
+    wall = cx.max_over_ranks(float(np.median(wall_ms)))
+    new_tokens = c["B"] * c["new"] * cx.world
+    weight_bytes = 2.0 * (n_params - c["vocab"] * c["dim"])          # bf16; the embedding table is gathered, not streamed
+    m.close()
+    return {
+        "metric": "generated tokens/s (prefill + greedy decode)", "value": new_tokens / ((pre + dec) * 1e-3), "unit": "tokens/s",
+        "prefill_ms": pre, "decode_ms": dec, "decode_steps": steps, "ms_per_decode_step": dec / max(1, steps),
+        "prefill_tokens_per_s": c["B"] * c["P"] * cx.world / (pre * 1e-3),
+        "attention_time_share": attn_ms / (tp["prefill_ms"] + tp["decode_ms"]),
+        "attention_kernel_ms": attn_ms, "attention_kernel_launches": int(attn_launches),
+        "graph_replay": True, "launches_recorded_outside_graph": launches, "scaling": "weak",
+        "e2e": {"value": new_tokens / (wall * 1e-3), "unit": "tokens/s", "ms": wall,
+                "h2d_bytes_per_step": int(prompt.nbytes), "d2h_bytes_per_step": int(toks.nbytes)},
+        "roofline": {"bound": "hbm", "what": "decode step: bf16 weights streamed once per step",
+                     "achieved": weight_bytes / (dec / max(1, steps) * 1e-3) / 1e9, "peak": cx.peaks["hbm"], "unit": "GB/s",
+                     "frac": weight_bytes / (dec / max(1, steps) * 1e-3) / 1e9 / cx.peaks["hbm"], "peak_source": cx.peaks["source"]},
+        "config": {"workload": f"Llama-style decoder {c['layers']} layers d_model {c['dim']} Hq={c['Hq']} Hkv={c['Hkv']} D=128 SwiGLU {c['ffn']} "
+                               f"vocab {c['vocab']} bf16 weights N(0,0.02); {c['B']} prompts x {c['P']} random ids, prefill + {c['new']} greedy tokens; "
+                               "per GPU (sequences are the units, no collective)", "parameters": int(n_params)},
+    }
+
+
 def run_ours(args):
     cx = Ctx()
     K, W = max(1, args.steps), max(3, args.warmup)
@@ -434,6 +500,7 @@ def run_ours(args):
     pre = bench_prefill(cx, K, W, quick=args.no_cpu_baseline) if only in ("all", "prefill") else None
     dec = bench_decode(cx, args.decode_steps, W) if only in ("all", "decode") else None
     shd = bench_sharded(cx) if only in ("all", "sharded") else None
+    mdl = bench_model(cx) if only in ("all", "model") else None
     cpu_baseline = None
     if cx.rank == 0 and cx.world == 1 and not args.no_cpu_baseline and only == "all":
         cpu_baseline, _ = cpu_prefill_sample(target_seconds=12.0)
@@ -453,6 +520,7 @@ def run_ours(args):
             "clocks": pre["clocks"] if pre else None,
             "decode": dec,
             "decode_sharded": shd,
+            "model": mdl,
         }
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
@@ -483,7 +551,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU sample (profiling runs)")
     ap.add_argument("--decode-steps", type=int, default=C3["steps"], help="consecutive decode steps (default: the workload's 256)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "sharded"], help="run one section (profiling runs)")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "sharded", "model"], help="run one section (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
