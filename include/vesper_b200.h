@@ -183,6 +183,37 @@ int vb200_decode_fwd_static(const vb200_decode_args* a);
 int vb200_lse_combine(int device, void* stream, const float* partials, int32_t R,
                       int64_t rows, int32_t D, int32_t dtype, void* out, float* lse);
 
+/* ---- fused exchange + merge for sequence-sharded decode (no reference counterpart) ----------
+ * Replaces "all-gather the partial_out records of all ranks, then vb200_lse_combine" by one kernel
+ * over NVLink peer memory: every rank stores its records into every rank's exchange buffer (plain
+ * peer stores), publishes a flag, waits for all ranks' flags in its own buffer and merges.
+ * peer_buffers[r] is rank r's exchange buffer as THIS process addresses it (peer-mapped device
+ * memory: CUDA IPC, VMM or a symmetric-memory allocator; entry [rank] is the local buffer); each is
+ * vb200_exchange_buffer_bytes(...) long and zero-filled once before the first call.  All ranks
+ * must make the same sequence of calls with the same rows / D.  step: 0 = number the calls with
+ * a counter kept in the buffer (works under CUDA-graph replay), else a caller-chosen number that
+ * grows by one per call.  A rank that never arrives ends the wait after timeout_cycles GPU clock
+ * cycles (0 = about one second): the output is left unwritten and vb200_check_kernel_status
+ * reports VB200_ERR_KERNEL_TIMEOUT -- the context stays usable. */
+#define VB200_EXCHANGE_MAX_WORLD 16
+typedef struct vb200_exchange_args {
+    size_t struct_size;
+    int32_t device;
+    void* stream;
+    int32_t world, rank;
+    void* const* peer_buffers;   /* host array of `world` device pointers */
+    const float* partial;        /* local [rows, D+2] records (O/l, m, l) */
+    int64_t rows;
+    int32_t D;
+    int32_t dtype;               /* of out: VB200_BF16 or VB200_F16 */
+    void* out;                   /* [rows, D] */
+    float* lse;                  /* [rows], nullable */
+    uint32_t step;
+    int64_t timeout_cycles;
+} vb200_exchange_args;
+size_t vb200_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t D);
+int vb200_exchange_combine(const vb200_exchange_args* a);
+
 /* ---- cache append without attention ---------------------------------------
  * Rotates K (if rope.enabled) and writes K, V rows [start_pos, start_pos+T)
  * of the cache.  Replaces the copy_strided_cuda_dispatch calls behind

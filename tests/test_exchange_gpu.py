@@ -1,0 +1,132 @@
+"""vb200_exchange_combine (the fused peer-memory exchange + LSE merge of sequence-sharded decode) on ONE
+GPU: the other ranks are emulated by writing what they would have pushed (records + flags) into this
+rank's buffer before the launch, so no launch ever waits for another one.  The real multi-GPU run is
+tests/test_exchange_multi_gpu.py."""
+import numpy as np
+import pytest
+
+from helpers import from_torch
+
+pytestmark = pytest.mark.gpu
+
+FLAG_BASE, SLOT_BASE, MAX_WORLD, MAX_CTAS, ROWS_PER_CTA = 4096, 4096 + 2 * 16 * 64 * 4, 16, 64, 4
+
+
+def _ctas(rows):
+    """CTAs the launcher uses: 4 rows each, at most 64 (then more rows per CTA)."""
+    n = (rows + ROWS_PER_CTA - 1) // ROWS_PER_CTA
+    if n > MAX_CTAS:
+        per = (rows + MAX_CTAS - 1) // MAX_CTAS
+        n = (rows + per - 1) // per
+    return n
+
+
+def _partials(rng, world, rows, D):
+    """Records (O/l, m, l) as a split of one softmax over `world` shards."""
+    p = np.empty((world, rows, D + 2), np.float32)
+    p[:, :, :D] = rng.standard_normal((world, rows, D))
+    p[:, :, D] = 3.0 * rng.standard_normal((world, rows))
+    p[:, :, D + 1] = rng.uniform(0.5, 20.0, size=(world, rows))
+    return p
+
+
+def _want(oracle, p):
+    world, rows, D2 = p.shape
+    D = D2 - 2
+    o, lse = oracle.lse_combine(p[:, :, D].copy(), p[:, :, D + 1].copy(), p[:, :, :D].copy())
+    return o, lse
+
+
+def _seed_peer(buf, world, rows, D, src, step, record):
+    """What rank `src` would have pushed into this buffer for call number `step`."""
+    import torch
+    parity = step & 1
+    n = rows * (D + 2)
+    off = SLOT_BASE + (parity * world + src) * n * 4
+    buf[off:off + n * 4].view(torch.float32).copy_(torch.from_numpy(record.reshape(-1)).to(buf.device))
+    ctas = _ctas(rows)
+    f0 = FLAG_BASE + ((parity * MAX_WORLD + src) * MAX_CTAS) * 4
+    buf[f0:f0 + ctas * 4].view(torch.int32).fill_(step)
+
+
+def test_buffer_size_and_argument_checks(lib):
+    from vesper_b200 import capi
+    assert capi.exchange_buffer_bytes(8, 64, 128) == SLOT_BASE + 2 * 8 * 64 * 130 * 4
+    assert capi.exchange_buffer_bytes(17, 64, 128) == 0 and capi.exchange_buffer_bytes(0, 64, 128) == 0
+    a = capi.ExchangeArgs()
+    assert lib.vb200_exchange_combine(None) == -1
+    a.struct_size = 8
+    assert lib.vb200_exchange_combine(a) == -1
+
+
+def test_single_rank_equals_lse_combine(cuda, oracle):
+    import torch
+    from vesper_b200 import capi
+    rng = np.random.default_rng(0)
+    rows, D = 64, 128
+    p = _partials(rng, 1, rows, D)
+    buf = torch.zeros(capi.exchange_buffer_bytes(1, rows, D), dtype=torch.uint8, device=cuda)
+    out = torch.empty(rows, D, dtype=torch.bfloat16, device=cuda)
+    lse = torch.empty(rows, dtype=torch.float32, device=cuda)
+    for _ in range(3):                                   # call numbers 1, 2, 3 from the buffer's own counter
+        capi.exchange_combine(torch.from_numpy(p[0]).to(cuda), [buf.data_ptr()], 0, out, lse)
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)
+    o, l = _want(oracle, p)
+    assert np.abs(from_torch(out) - o).max() <= 2.0 ** -8 * np.abs(o).max() and np.abs(from_torch(lse) - l).max() <= 1e-5
+
+
+@pytest.mark.parametrize("world,rows,D", [(2, 64, 128), (4, 7, 64), (8, 64, 128), (3, 300, 128)])
+def test_emulated_peers_receive_side_and_push_side(cuda, oracle, world, rows, D):
+    import torch
+    from vesper_b200 import capi
+    rng = np.random.default_rng(world * 1000 + rows)
+    rank = 1 % world
+    nbytes = capi.exchange_buffer_bytes(world, rows, D)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=cuda) for _ in range(world)]     # bufs[rank] is "ours", the rest stand in for the peers' memory
+    out = torch.empty(rows, D, dtype=torch.bfloat16, device=cuda)
+    lse = torch.empty(rows, dtype=torch.float32, device=cuda)
+    for step in (1, 2, 3):
+        p = _partials(rng, world, rows, D)
+        for src in range(world):
+            if src != rank:
+                _seed_peer(bufs[rank], world, rows, D, src, step, p[src])
+        capi.exchange_combine(torch.from_numpy(p[rank]).to(cuda), [b.data_ptr() for b in bufs], rank, out, lse)
+        torch.cuda.synchronize()
+        capi.check_kernel_status(0)
+        o, l = _want(oracle, p)
+        assert np.abs(from_torch(out) - o).max() <= 2.0 ** -8 * max(1.0, np.abs(o).max()), step
+        assert np.abs(from_torch(lse) - l).max() <= 1e-4, step
+        # push side: every stand-in peer buffer now holds our records in slot[parity][rank] and our flags
+        n = rows * (D + 2)
+        for dst in range(world):
+            off = SLOT_BASE + ((step & 1) * world + rank) * n * 4
+            got = bufs[dst][off:off + n * 4].view(torch.float32).cpu().numpy()
+            assert np.array_equal(got, p[rank].reshape(-1))
+            f0 = FLAG_BASE + (((step & 1) * MAX_WORLD + rank) * MAX_CTAS) * 4
+            assert bool((bufs[dst][f0:f0 + _ctas(rows) * 4].view(torch.int32) == step).all())
+
+
+def test_absent_peer_times_out_with_a_status_not_a_hang(cuda, oracle):
+    """A flag that nothing sets: the bounded wait (here 2e6 cycles, about a millisecond) gives up, the
+    output stays untouched, the status word reports it, and the next call works."""
+    import torch
+    from vesper_b200 import capi
+    rng = np.random.default_rng(5)
+    world, rows, D = 2, 16, 128
+    p = _partials(rng, world, rows, D)
+    nbytes = capi.exchange_buffer_bytes(world, rows, D)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=cuda) for _ in range(world)]
+    out = torch.full((rows, D), 7.0, dtype=torch.bfloat16, device=cuda)
+    capi.exchange_combine(torch.from_numpy(p[0]).to(cuda), [b.data_ptr() for b in bufs], 0, out, timeout_cycles=2_000_000)
+    torch.cuda.synchronize()
+    with pytest.raises(capi.Vb200Error, match="bounded in-kernel wait"):
+        capi.check_kernel_status(0)
+    assert bool((out == 7.0).all())
+    # the peer "arrives" for the next call number (2): the same buffers keep working
+    _seed_peer(bufs[0], world, rows, D, 1, 2, p[1])
+    capi.exchange_combine(torch.from_numpy(p[0]).to(cuda), [b.data_ptr() for b in bufs], 0, out, timeout_cycles=2_000_000)
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)
+    o, _ = _want(oracle, p)
+    assert np.abs(from_torch(out) - o).max() <= 2.0 ** -8 * max(1.0, np.abs(o).max())

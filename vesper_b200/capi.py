@@ -51,7 +51,7 @@ class DecodeArgs(C.Structure):
 
 EXPORTS = [
     "vb200_prefill_workspace_bytes", "vb200_prefill_fwd", "vb200_decode_workspace_bytes", "vb200_decode_fwd",
-    "vb200_decode_fwd_static",
+    "vb200_decode_fwd_static", "vb200_exchange_buffer_bytes", "vb200_exchange_combine",
     "vb200_lse_combine", "vb200_kv_append", "vb200_apply_rope", "vb200_repeat_kv", "vb200_rope_inv_freq",
     "vb200_strerror", "vb200_last_error_detail", "vb200_abi_version", "vb200_launch_count",
     "vb200_reset_launch_count", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
@@ -59,6 +59,14 @@ EXPORTS = [
 BLOCK_EXPORTS = [
     "vb200_linear", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
 ]
+
+
+class ExchangeArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_size_t), ("device", C.c_int32), ("stream", C.c_void_p), ("world", C.c_int32), ("rank", C.c_int32),
+        ("peer_buffers", C.POINTER(C.c_void_p)), ("partial", C.c_void_p), ("rows", C.c_int64), ("D", C.c_int32), ("dtype", C.c_int32),
+        ("out", C.c_void_p), ("lse", C.c_void_p), ("step", C.c_uint32), ("timeout_cycles", C.c_int64),
+    ]
 
 
 class GreedyArgs(C.Structure):
@@ -112,6 +120,9 @@ def load():
     L.vb200_check_kernel_status.argtypes = [C.c_int, C.c_void_p]
     L.vb200_profile_enable.argtypes = [C.c_int]
     L.vb200_profile_read.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
+    L.vb200_exchange_buffer_bytes.argtypes = [C.c_int32, C.c_int64, C.c_int32]
+    L.vb200_exchange_buffer_bytes.restype = C.c_size_t
+    L.vb200_exchange_combine.argtypes = [C.POINTER(ExchangeArgs)]
     # decoder-block operators (include/vesper_b200_block.h)
     L.vb200_linear.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64] + [C.c_int32] * 5
     L.vb200_interleave_rows.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]
@@ -264,6 +275,30 @@ def profile_read():
     ms, n = C.c_double(0.0), C.c_uint64(0)
     check(load().vb200_profile_read(C.byref(ms), C.byref(n)))
     return ms.value, n.value
+
+
+def exchange_buffer_bytes(world, rows, D):
+    return int(load().vb200_exchange_buffer_bytes(world, rows, D))
+
+
+def exchange_combine(partial, peer_ptrs, rank, out, lse=None, *, step=0, timeout_cycles=0, stream=None):
+    """partial [rows, D+2] fp32 (local), peer_ptrs: device address of every rank's exchange buffer."""
+    a = ExchangeArgs()
+    a.struct_size = C.sizeof(ExchangeArgs)
+    a.device = partial.device.index or 0
+    a.stream = _stream_ptr(stream)
+    a.world, a.rank = len(peer_ptrs), rank
+    arr = (C.c_void_p * len(peer_ptrs))(*[C.c_void_p(int(p)) for p in peer_ptrs])
+    a.peer_buffers = arr
+    a.partial = _ptr(partial)
+    a.rows, a.D = partial.shape[0], partial.shape[1] - 2
+    a.dtype = dtype_code(out)
+    a.out = _ptr(out)
+    a.lse = _ptr(lse)
+    a.step = step
+    a.timeout_cycles = timeout_cycles
+    check(load().vb200_exchange_combine(C.byref(a)))
+    return out
 
 
 # ---- decoder-block operators ---------------------------------------------------------------

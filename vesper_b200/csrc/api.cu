@@ -424,6 +424,35 @@ int vb200_repeat_kv(int device, void* stream, int32_t dtype, const vb200_tensor4
     return launch_repeat_kv(static_cast<cudaStream_t>(stream), dtype, to_view(*in), out, B, Hkv, S, D, n_rep);
 }
 
+size_t vb200_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t D) {
+    if (world <= 0 || world > VB200_EXCHANGE_MAX_WORLD || rows <= 0 || D <= 0) return 0;
+    return exchange_buffer_bytes(world, rows, D);
+}
+
+int vb200_exchange_combine(const vb200_exchange_args* a) {
+    if (!a || a->struct_size != sizeof(vb200_exchange_args)) return set_detail(VB200_ERR_INVALID_ARG, "vb200_exchange_args: null or struct_size mismatch");
+    if (a->world <= 0 || a->world > VB200_EXCHANGE_MAX_WORLD || a->rank < 0 || a->rank >= a->world)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_exchange_combine: world must be in [1, 16] and rank in [0, world)");
+    if (!a->peer_buffers || !a->partial || !a->out || a->rows <= 0 || a->D <= 0 || a->D % 2 != 0)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_exchange_combine: null pointer, rows <= 0 or odd D");
+    if (a->dtype != VB200_BF16 && a->dtype != VB200_F16) return set_detail(VB200_ERR_UNSUPPORTED, "vb200_exchange_combine: out must be bf16 or fp16");
+    ExchangeParams p{};
+    p.world = a->world; p.rank = a->rank;
+    for (int r = 0; r < a->world; ++r) {
+        if (!a->peer_buffers[r] || reinterpret_cast<uintptr_t>(a->peer_buffers[r]) % 128 != 0)
+            return set_detail(VB200_ERR_ALIGNMENT, "vb200_exchange_combine: every exchange buffer must be non-null and 128-byte aligned");
+        p.peers[r] = a->peer_buffers[r];
+    }
+    if (reinterpret_cast<uintptr_t>(a->partial) % 8 != 0) return set_detail(VB200_ERR_ALIGNMENT, "vb200_exchange_combine: partial must be 8-byte aligned");
+    p.partial = a->partial; p.rows = a->rows; p.D = a->D; p.dtype = a->dtype; p.out = a->out; p.lse = a->lse;
+    p.step = a->step; p.timeout_cycles = a->timeout_cycles;
+    DeviceGuard g;
+    if (int rc = g.init(a->device)) return rc;
+    p.status = kernel_status_word();
+    if (!p.status) return VB200_ERR_CUDA;
+    return launch_exchange_combine(static_cast<cudaStream_t>(a->stream), p);
+}
+
 // ---- decoder-block operators (vesper_b200_block.h) ---------------------------------------------
 
 static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }

@@ -78,6 +78,23 @@ int launch_decode(cudaStream_t s, const DecodeParams& p);
 int launch_lse_combine(cudaStream_t s, const float* partials, int R, long long rows, int D,
                        int dtype, void* out, float* lse);
 
+// ---- decode_exchange.cu ----
+struct ExchangeParams {
+    int world, rank;
+    void* peers[VB200_EXCHANGE_MAX_WORLD];   // exchange buffer of every rank as this GPU addresses it; [rank] = own
+    const float* partial;                    // local [rows, D+2]
+    long long rows;
+    long long rows_per_cta;                  // filled in by the launcher
+    int D, dtype;
+    void* out;                               // [rows, D]
+    float* lse;                              // [rows] or null
+    unsigned step;                           // 0 = take the next step number from the buffer's own counter
+    long long timeout_cycles;
+    int* status;
+};
+size_t exchange_buffer_bytes(int world, long long rows, int D);
+int launch_exchange_combine(cudaStream_t s, ExchangeParams p);
+
 // ---- linear_sm100.cu ----
 struct LinearParams {
     const void* x;  long long ldx;   // [M, K] bf16

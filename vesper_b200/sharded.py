@@ -100,17 +100,51 @@ class ShardedDecodeStep:
         return combine(gathered)
 
 
+class PeerExchange:
+    """Exchange buffers of all ranks mapped into every process (torch symmetric memory supplies the
+    allocation and the address exchange: plumbing only) for ``vb200_exchange_combine``, which pushes
+    this rank's partial records into every peer's buffer over NVLink, waits for the peers' flags and
+    merges -- one kernel instead of all-gather + combine.  Collective: every rank constructs it with
+    the same (rows, D) at the same point."""
+
+    def __init__(self, dist, world, rank, rows, D, device, group=None):
+        import torch
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import capi
+        self.world, self.rank, self.rows, self.D = world, rank, rows, D
+        nbytes = capi.exchange_buffer_bytes(world, rows, D)
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        handle = symm_mem.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+        self.ptrs = [int(p) for p in handle.buffer_ptrs]
+        if len(self.ptrs) != world or self.ptrs[rank] != self.buf.data_ptr():
+            raise ShardExchangeError("symmetric memory rendezvous returned an unexpected set of buffers")
+        self._handle = handle
+        torch.cuda.synchronize(device)          # every rank's flags are zero before anybody publishes one
+        dist.barrier()
+
+    def combine(self, partial, out, lse=None, *, timeout_cycles=0, stream=None):
+        from . import capi
+        return capi.exchange_combine(partial, self.ptrs, self.rank, out, lse, timeout_cycles=timeout_cycles, stream=stream)
+
+
 def cuda_step(step: ShardedDecodeStep, q, k_shard, v_shard, *, scale, theta, partial_buf, out, lse=None,
-              gathered=None, workspace=None, dist=None, stream=None):
+              gathered=None, workspace=None, dist=None, stream=None, exchange: PeerExchange | None = None, qpos=None):
     """GPU implementation of one step on this rank.  ``k_shard``/``v_shard`` hold rows
-    [begin, end) of the sequence; ``q`` is the unrotated query [B,Hq,1,D] (replicated)."""
+    [begin, end) of the sequence; ``q`` is the unrotated query [B,Hq,1,D] (replicated).
+    With ``exchange`` the partial records travel and merge in one peer-memory kernel; without it
+    they go through a host-supervised all-gather followed by ``vb200_lse_combine``."""
     import torch
     from . import capi
     begin, end = shard_range(step.context_len, step.world, step.rank)
     B, Hq, _, D = q.shape
-    qpos = torch.full((B,), step.context_len, dtype=torch.int32, device=q.device)
+    if qpos is None:
+        qpos = torch.full((B,), step.context_len, dtype=torch.int32, device=q.device)
     capi.decode(q, None, k_shard, v_shard, scale=scale, theta=theta, uniform_len=end - begin, max_len=end - begin,
                 pos_offset=begin, q_positions=qpos, partial_out=partial_buf, workspace=workspace, stream=stream)
+    if exchange is not None:
+        exchange.combine(partial_buf.view(B * Hq, D + 2), out, lse, stream=stream)
+        return out
     if step.world == 1:
         g = partial_buf.view(1, B * Hq, D + 2)
     else:
