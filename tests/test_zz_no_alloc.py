@@ -66,6 +66,7 @@ def test_static_scratch_rejects_plans_beyond_the_array(lib, cuda):
     q = torch.zeros(B, Hq, 1, D, dtype=torch.bfloat16, device=cuda)
     kc = torch.zeros(B, Hkv, cap, D, dtype=torch.bfloat16, device=cuda)
     a = capi.decode_args(q, torch.empty_like(q), kc, kc, scale=1.0, uniform_len=10, max_len=16384 + 512)
+    a.num_splits = 33                 # asked for explicitly: with one common length the planner would pick far fewer
     need = lib.vb200_decode_workspace_bytes(C.byref(a))
     assert need > 16 * 1024 * 1024
     assert lib.vb200_decode_fwd_static(C.byref(a)) == -4

@@ -146,12 +146,13 @@ DecodePlan plan_decode(const vb200_decode_args* a) {
     if (a->num_splits > 0) {
         chunk = (max_total + a->num_splits - 1) / a->num_splits;
     } else {
-        // enough CTAs for about two waves of 2 CTAs/SM on 148 SMs, but never
-        // more than 512 keys per CTA so ragged batches balance
+        // enough CTAs for about two waves of 2 CTAs/SM on 148 SMs; with per-sequence lengths never
+        // more than 512 keys per CTA so ragged batches balance (one common length needs no such cap:
+        // longer chunks spend less of a CTA's life in its prologue and merge)
         long long units = static_cast<long long>(a->B) * a->Hkv;
         int want = static_cast<int>((592 + units - 1) / units);
         chunk = (max_total + want - 1) / want;
-        if (chunk > 512) chunk = 512;
+        if (chunk > 512 && a->seq_lens) chunk = 512;
     }
     chunk = (chunk + tile - 1) / tile * tile;
     if (chunk < tile) chunk = tile;

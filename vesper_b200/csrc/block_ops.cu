@@ -21,6 +21,7 @@ constexpr int kNormMaxVec = 8;        // float4 per thread: dim <= 256 * 4 * 8 =
 
 __global__ void __launch_bounds__(kNormThreads)
 rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int dim, float eps) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long row = blockIdx.x;
     const float4* xr = reinterpret_cast<const float4*>(x + row * dim);
@@ -60,6 +61,7 @@ rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, __nv_b
 
 // silu(g) * u with silu(g) = g * sigmoid(g) -- ops::silu_mul, src/ops/elementwise.cpp:1297-1328.
 __global__ void silu_mul_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ out, long long nvec) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -78,6 +80,7 @@ __global__ void silu_mul_kernel(const uint4* __restrict__ gate, const uint4* __r
 // out[m,:] = float(table[ids[m],:]) -- ops::embedding, src/ops/embedding.cpp:10-17.
 __global__ void embedding_kernel(const void* __restrict__ ids, int ids64, const __nv_bfloat16* __restrict__ table,
                                  float* __restrict__ out, int dim, int vocab, int* status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long m = blockIdx.x;
     const long long id = ids64 ? static_cast<const long long*>(ids)[m] : static_cast<const int*>(ids)[m];
@@ -103,6 +106,7 @@ greedy_step_kernel(const float* __restrict__ logits, long long ld, int vocab, in
                    int* __restrict__ history, long long history_ld, int step,
                    const int* __restrict__ stop_ids, int n_stop, int min_new, int* __restrict__ done,
                    const int* __restrict__ pos_dev, int pos_base) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = blockIdx.x;
     const float* row = logits + b * ld;

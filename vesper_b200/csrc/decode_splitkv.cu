@@ -180,6 +180,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(Dec
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, l16 = lane & 15;
 
+    // launched with the programmatic-dependent-launch attribute: q / k_new / v_new and the length array
+    // may come from the kernel just before this one
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     int len = p.seq_lens ? p.seq_lens[b] : p.uniform_len;          // cached keys before this token
     len = max(0, min(len, p.cache_cap));
     const int total = len + (p.append ? 1 : 0);
@@ -444,18 +447,36 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
     constexpr int CW = 4;
     constexpr int kStages = (NREP <= 4) ? 2 : 3;
     constexpr int MINB = (NREP <= 4) ? 3 : 2;
-    size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + D * sizeof(float) + D * sizeof(T) + 2 * CW * 16 * sizeof(float) + sizeof(DecodeSmem<CW, kStages>);
-    static_assert(2 * CW * NREP * 128 * 4 + 2 * 2 * CW * NREP * 4 <= kStages * 2 * kTile * 128 * 2, "merge buffers must fit in the ring");
-    static thread_local int configured_dev = -1;
-    int dev = 0;
-    VB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_dev != dev) {
-        VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        configured_dev = dev;
+    if constexpr (NREP == 8) {
+        // 8-head groups are compute-bound on CUDA cores: their split kernel runs the products as warp MMAs
+        profile_mark_begin(s);
+        if (int rc = launch_decode_gqa8_split<T>(s, p)) return rc;
+    } else {
+        size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + D * sizeof(float) + D * sizeof(T) + 2 * CW * 16 * sizeof(float) + sizeof(DecodeSmem<CW, kStages>);
+        static_assert(2 * CW * NREP * 128 * 4 + 2 * 2 * CW * NREP * 4 <= kStages * 2 * kTile * 128 * 2, "merge buffers must fit in the ring");
+        static thread_local int configured_dev = -1;
+        int dev = 0;
+        VB200_CUDA_TRY(cudaGetDevice(&dev));
+        if (configured_dev != dev) {
+            VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            configured_dev = dev;
+        }
+        dim3 grid(p.num_splits, p.Hkv, p.B);
+        profile_mark_begin(s);
+        {
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = grid;
+            cfg.blockDim = dim3((CW + 1) * 32);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = s;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, p));
+        }
     }
-    dim3 grid(p.num_splits, p.Hkv, p.B);
-    profile_mark_begin(s);
-    decode_splitkv_kernel<T, NREP, CW, kStages, MINB><<<grid, (CW + 1) * 32, smem, s>>>(p);
     profile_mark_end(s);
     note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());

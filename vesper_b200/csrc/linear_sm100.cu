@@ -174,7 +174,9 @@ linear_wide_kernel(const __grid_constant__ LinearMaps maps, LinearParams p) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // the activations may come from the kernel launched just before this one
+    // the next kernel in the stream may be scheduled now (it waits for this grid to finish before it reads
+    // anything); the activations may come from the kernel launched just before this one
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
@@ -317,7 +319,12 @@ linear_skinny_kernel(const __grid_constant__ LinearMaps maps, LinearParams p, in
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Programmatic dependent launch: the next kernel of the stream may be scheduled as soon as every CTA of
+    // this grid is here, and this grid was scheduled while its predecessor was still running.  Weights do
+    // not depend on the predecessor, so their first ring of TMA loads goes out BEFORE griddepcontrol.wait
+    // and streams while the predecessor finishes; only the activation loads and the epilogue's global
+    // accesses wait for it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     float acc[MT];
 #pragma unroll
@@ -325,13 +332,21 @@ linear_skinny_kernel(const __grid_constant__ LinearMaps maps, LinearParams p, in
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb; ++i) {
+            const int pre = min(nkb, C::kStages);
+            for (int i = 0; i < pre; ++i) {
+                mbar_arrive_expect_tx(&full[i], C::kStageBytes);
+                tma_load_2d(smem + i * C::kStageBytes, &maps.a, &full[i], (kb0 + i) * kBK, nt * kTileA);     // 128 W rows
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(smem + i * C::kStageBytes + kABytes, &maps.b, &full[i], (kb0 + i) * kBK, 0);      // the token rows (zero filled past M)
+            for (int i = pre; i < nkb; ++i) {
                 const int s = i % C::kStages;
-                if (i >= C::kStages && !mbar_wait(&empty[s], ((i / C::kStages) - 1) & 1, ctx, 0x51)) break;
+                if (!mbar_wait(&empty[s], ((i / C::kStages) - 1) & 1, ctx, 0x51)) break;
                 uint8_t* st = smem + s * C::kStageBytes;
                 mbar_arrive_expect_tx(&full[s], C::kStageBytes);
-                tma_load_2d(st, &maps.a, &full[s], (kb0 + i) * kBK, nt * kTileA);     // 128 W rows
-                tma_load_2d(st + kABytes, &maps.b, &full[s], (kb0 + i) * kBK, 0);      // the token rows (zero filled past M)
+                tma_load_2d(st, &maps.a, &full[s], (kb0 + i) * kBK, nt * kTileA);
+                tma_load_2d(st + kABytes, &maps.b, &full[s], (kb0 + i) * kBK, 0);
             }
         }
     } else if (warp == 1) {
@@ -353,6 +368,7 @@ linear_skinny_kernel(const __grid_constant__ LinearMaps maps, LinearParams p, in
         }
     } else {
         const int quarter = warp & 3;
+        asm volatile("griddepcontrol.wait;" ::: "memory");      // before any global access of the epilogue
         // wait even when this slice is empty: the commit above always arrives
         if (mbar_wait_warp(acc_full, 0, ctx, 0x53) && nkb > 0) {
             tc_fence_after();
