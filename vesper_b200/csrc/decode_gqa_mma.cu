@@ -73,10 +73,11 @@ struct FragState {
 };
 
 // CW consumer warps (16 keys of every 64-key tile each) + 1 producer warp.
-template <typename T, int CW, int kStages, int MINB>
-__global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa8_mma_kernel(const __grid_constant__ KvMaps maps, DecodeParams p) {
+template <typename T, int NREP, int CW, int kStages, int MINB>
+__global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa_mma_kernel(const __grid_constant__ KvMaps maps, DecodeParams p) {
     static_assert(CW * 16 == kTileM, "one 16-key slice per consumer warp");
-    constexpr int D = 128, NREP = 8;
+    constexpr int D = 128;
+    static_assert(NREP >= 1 && NREP <= 8, "the heads of a group are rows 0..NREP-1 of the 16-row MMA tile");
     constexpr int kRowBytes = D * 2;
     constexpr int kMatBytes = 2 * kBoxBytes;                 // one K or V tile = two boxes (dims 0-63, 64-127)
     constexpr int kStageBytes = 2 * kMatBytes;
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa8_mma_kernel(co
 
     // rotated query in A-fragment layout: step ks covers dims [16 ks, 16 ks + 16); this thread holds the
     // pairs (16 ks + 2 cq, +1) and (16 ks + 8 + 2 cq, +1) of head hh -- a register is one RoPE pair
-    uint32_t qa[8][2];
+    uint32_t qa[8][2], qlo[8][2];      // q = hi + lo in the 16-bit type: the scores keep fp32-class accuracy in q
     const float pos = __int2float_rn(p.q_positions ? p.q_positions[b] : static_cast<int>(p.pos_offset) + len);
     {
         // The 16 angles a thread needs depend on cq only: the 8 threads that share cq compute two each
@@ -147,7 +148,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa8_mma_kernel(co
 #pragma unroll
             for (int half = 0; half < 2; ++half) sincosf(pos * p.inv_freq.v[hh * 8 + half * 4 + cq], &my_sn[half], &my_cs[half]);
         }
-        const T* qp = static_cast<const T*>(p.q.ptr) + b * p.q.sb + (kvh * NREP + hh) * p.q.sh;
+        const bool live = hh < NREP;                          // rows NREP..7 of the tile are padding as well
+        const T* qp = static_cast<const T*>(p.q.ptr) + b * p.q.sb + (kvh * NREP + (live ? hh : 0)) * p.q.sh;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
 #pragma unroll
@@ -157,7 +159,11 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa8_mma_kernel(co
                 const float sn = __shfl_sync(0xFFFFFFFFu, my_sn[half], ks * 4 + cq);
                 float2 t = Elem<T>::unpack2(*reinterpret_cast<const uint32_t*>(qp + d0));
                 const float t1 = __fmul_rn(t.x, cs), t2 = __fmul_rn(t.y, sn), t3 = __fmul_rn(t.x, sn), t4 = __fmul_rn(t.y, cs);
-                qa[ks][half] = Elem<T>::pack2(__fsub_rn(t1, t2), __fadd_rn(t3, t4));
+                const float rx = __fsub_rn(t1, t2), ry = __fadd_rn(t3, t4);
+                const uint32_t hi = Elem<T>::pack2(rx, ry);
+                const float2 hf = Elem<T>::unpack2(hi);
+                qa[ks][half] = live ? hi : 0u;
+                qlo[ks][half] = live ? Elem<T>::pack2(rx - hf.x, ry - hf.y) : 0u;
             }
         }
     }
@@ -228,8 +234,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa8_mma_kernel(co
                     uint32_t kb[4];
                     // matrices: (keys nt*8.., dims 32kp + 8 lm_mat ..)
                     ldmatrix_x4(kb, ks_addr + (kp >> 1) * kBoxBytes + (nt * 8 + lm_row) * 128 + ((((kp & 1) * 4 + lm_mat) ^ lm_row) << 4));
-                    const uint32_t a_lo[4] = {qa[2 * kp][0], 0u, qa[2 * kp][1], 0u};
-                    const uint32_t a_hi[4] = {qa[2 * kp + 1][0], 0u, qa[2 * kp + 1][1], 0u};
+                    // rows 0-7 of the A tile carry the high halves of q, rows 8-15 (otherwise padding) the low
+                    // halves: one MMA yields both partial scores, added below
+                    const uint32_t a_lo[4] = {qa[2 * kp][0], qlo[2 * kp][0], qa[2 * kp][1], qlo[2 * kp][1]};
+                    const uint32_t a_hi[4] = {qa[2 * kp + 1][0], qlo[2 * kp + 1][0], qa[2 * kp + 1][1], qlo[2 * kp + 1][1]};
                     MmaOp<T>::mma(sc[nt], a_lo, kb[0], kb[1]);
                     MmaOp<T>::mma(sc[nt], a_hi, kb[2], kb[3]);
                 }
@@ -241,7 +249,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa8_mma_kernel(co
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     const int key = key0 + nt * 8 + cq * 2 + j;
-                    sv[nt * 2 + j] = key < nk ? sc[nt][j] * qscale : -INFINITY;
+                    sv[nt * 2 + j] = key < nk ? (sc[nt][j] + sc[nt][j + 2]) * qscale : -INFINITY;
                 }
             float bm = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
             bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 1));
@@ -280,7 +288,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa8_mma_kernel(co
     if (owns_new && warp == 0) {
         __syncwarp();
         // dot of head hh: this thread covers dims cq*32 .. cq*32+31 of q (re-read, rotated again in fp32)
-        const T* qp = static_cast<const T*>(p.q.ptr) + b * p.q.sb + (kvh * NREP + hh) * p.q.sh + cq * 32;
+        const T* qp = static_cast<const T*>(p.q.ptr) + b * p.q.sb + (kvh * NREP + (hh < NREP ? hh : 0)) * p.q.sh + cq * 32;
         float dot = 0.f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -323,10 +331,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa8_mma_kernel(co
     float* go = reinterpret_cast<float*>(smem_raw);           // [CW][NREP][128]
     float* gm = go + CW * NREP * 128;                         // [CW][NREP]
     float* gl = gm + CW * NREP;                               // [CW][NREP]
-    if (cq == 0) { gm[warp * NREP + hh] = st.m; gl[warp * NREP + hh] = l; }
+    if (hh < NREP) {
+        if (cq == 0) { gm[warp * NREP + hh] = st.m; gl[warp * NREP + hh] = l; }
 #pragma unroll
-    for (int n = 0; n < 16; ++n)
-        *reinterpret_cast<float2*>(go + (warp * NREP + hh) * 128 + n * 8 + cq * 2) = make_float2(st.o[n][0], st.o[n][1]);
+        for (int n = 0; n < 16; ++n)
+            *reinterpret_cast<float2*>(go + (warp * NREP + hh) * 128 + n * 8 + cq * 2) = make_float2(st.o[n][0], st.o[n][1]);
+    }
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
     if (tid < 128) {
         const int d = tid;
@@ -388,16 +398,16 @@ int make_kv_map(CUtensorMap* m, int dtype, const View4& v, int rows, int H, int 
 
 }  // namespace
 
-// Launches the split kernel for 8-head groups; the caller follows with the common combine kernel.
-template <typename T>
-int launch_decode_gqa8_split(cudaStream_t s, const DecodeParams& p) {
+// Launches the split kernel; the caller follows with the common combine kernel.
+template <typename T, int NREP>
+int launch_decode_gqa_mma_split(cudaStream_t s, const DecodeParams& p) {
     constexpr int CW = 4, kStages = 3, MINB = 2;
     constexpr size_t smem = static_cast<size_t>(kStages) * 4 * kBoxBytes + 128 * 4 + 128 * 2 + sizeof(MmaSmem<CW, kStages>) + 1024;
-    static_assert(CW * 8 * 128 * 4 + 2 * CW * 8 * 4 <= kStages * 4 * kBoxBytes, "merge buffers must fit in the ring");
+    static_assert(CW * NREP * 128 * 4 + 2 * CW * NREP * 4 <= kStages * 4 * kBoxBytes, "merge buffers must fit in the ring");
     KvMaps maps;
     if (int rc = make_kv_map(&maps.k, p.dtype, p.k_cache, p.cache_cap, p.Hkv, p.B)) return rc;
     if (int rc = make_kv_map(&maps.v, p.dtype, p.v_cache, p.cache_cap, p.Hkv, p.B)) return rc;
-    auto kernel = decode_gqa8_mma_kernel<T, CW, kStages, MINB>;
+    auto kernel = decode_gqa_mma_kernel<T, NREP, CW, kStages, MINB>;
     static thread_local int configured_dev = -1;
     int dev = 0;
     VB200_CUDA_TRY(cudaGetDevice(&dev));
@@ -418,7 +428,9 @@ int launch_decode_gqa8_split(cudaStream_t s, const DecodeParams& p) {
     VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, p));
     return VB200_OK;
 }
-template int launch_decode_gqa8_split<__nv_bfloat16>(cudaStream_t, const DecodeParams&);
-template int launch_decode_gqa8_split<__half>(cudaStream_t, const DecodeParams&);
+template int launch_decode_gqa_mma_split<__nv_bfloat16, 8>(cudaStream_t, const DecodeParams&);
+template int launch_decode_gqa_mma_split<__half, 8>(cudaStream_t, const DecodeParams&);
+template int launch_decode_gqa_mma_split<__nv_bfloat16, 4>(cudaStream_t, const DecodeParams&);
+template int launch_decode_gqa_mma_split<__half, 4>(cudaStream_t, const DecodeParams&);
 
 }  // namespace vb200

@@ -75,8 +75,8 @@ struct DecodeParams {
 };
 int decode_tile_keys();
 int launch_decode(cudaStream_t s, const DecodeParams& p);
-// decode_gqa_mma.cu: split kernel for Hq / Hkv == 8 (warp-MMA products); same workspace layout
-template <typename T> int launch_decode_gqa8_split(cudaStream_t s, const DecodeParams& p);
+// decode_gqa_mma.cu: split kernel with warp-MMA products (instantiated for Hq / Hkv of 4 and 8); same workspace layout
+template <typename T, int NREP> int launch_decode_gqa_mma_split(cudaStream_t s, const DecodeParams& p);
 int launch_lse_combine(cudaStream_t s, const float* partials, int R, long long rows, int D,
                        int dtype, void* out, float* lse);
 
