@@ -472,7 +472,7 @@ def bench_sharded(cx, nsteps=50):
     }
 
 
-def bench_model(cx, reps=3):
+def bench_model(cx, reps=3, layers=None, new=None):
     """C5: random-init Llama-style decoder (24 layers, d_model 2048, 16 query / 4 KV heads of 128, SwiGLU 5632,
     RMSNorm, RoPE 1e4, vocab 32000, bf16 weights ~ N(0, 0.02)); 8 prompts of 512 uniform-random ids, prefill then
     128 greedy tokens through generation::Generator of the host layer (device-resident loop, CUDA-graph replay).
@@ -482,7 +482,11 @@ def bench_model(cx, reps=3):
     import numpy as np
     from vesper_b200.model import TransformerLM, param_shapes
     capi = cx.capi
-    c = C5
+    c = dict(C5)
+    if layers:
+        c["layers"] = layers         # profiling runs only: a shallower stack launches the same kernels
+    if new:
+        c["new"] = new
     shapes = param_shapes(c["vocab"], c["dim"], c["layers"], c["Hq"], c["Hkv"], c["ffn"])
     m = TransformerLM(c["vocab"], c["dim"], c["layers"], c["Hq"], c["Hkv"], c["ffn"], c["P"] + c["new"], norm_eps=1e-6, rope_base=10000.0)
     rng = np.random.default_rng(7)
@@ -493,7 +497,7 @@ def bench_model(cx, reps=3):
         m.set_param(name, w)
         n_params += w.size
     prompt = np.random.default_rng(8).integers(0, c["vocab"], size=(c["B"], c["P"])).astype(np.int32)
-    m.generate_greedy(prompt, 8)                                   # warm-up: kernels configured, buffers allocated
+    m.generate_greedy(prompt, min(8, c["new"]))                    # warm-up: kernels configured, buffers allocated
     cx.sync_all()
     pre_ms, dec_ms, wall_ms, steps = [], [], [], 0
     for _ in range(reps):
@@ -542,7 +546,7 @@ def run_ours(args):
     pre = bench_prefill(cx, K, W, quick=args.no_cpu_baseline) if only in ("all", "prefill") else None
     dec = bench_decode(cx, args.decode_steps, W) if only in ("all", "decode") else None
     shd = bench_sharded(cx) if only in ("all", "sharded") else None
-    mdl = bench_model(cx) if only in ("all", "model") else None
+    mdl = bench_model(cx, layers=args.model_layers, new=args.model_new) if only in ("all", "model") else None
     cpu_baseline = None
     if cx.rank == 0 and cx.world == 1 and not args.no_cpu_baseline and only == "all":
         cpu_baseline, _ = cpu_prefill_sample(target_seconds=12.0)
@@ -593,6 +597,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU sample (profiling runs)")
     ap.add_argument("--decode-steps", type=int, default=C3["steps"], help="consecutive decode steps (default: the workload's 256)")
+    ap.add_argument("--model-layers", type=int, default=0, help="profiling runs: depth of the model section's decoder (default: the workload's 24)")
+    ap.add_argument("--model-new", type=int, default=0, help="profiling runs: tokens to generate in the model section (default: 128)")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "sharded", "model"], help="run one section (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
