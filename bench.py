@@ -58,8 +58,8 @@ def load_peaks():
 def load_traffic():
     """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels,
     copied from the ncu captures summarised in profiles/prefill_sm100_c2.md and
-    profiles/decode_splitkv_c3.md (captured on exactly these workloads, so no scaling applies)."""
-    return {"prefill_sm100_bytes_per_launch": 129.7e6, "decode_splitkv_bytes_per_launch": 704.4e6}
+    profiles/decode_gqa_mma_c3.md (captured on exactly these workloads, so no scaling applies)."""
+    return {"prefill_sm100_bytes_per_launch": 129.7e6, "decode_splitkv_bytes_per_launch": 709.2e6}
 
 
 class ClockSampler:
@@ -379,7 +379,7 @@ def bench_decode(cx, nsteps, W):
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": kgbs, "peak": pk["hbm"], "unit": "GB/s", "frac": (kgbs / pk["hbm"]) if kgbs else None,
                      "peak_source": pk["source"], "frac_of_nominal_8TBs": (kgbs / 8000.0) if kgbs else None,
-                     "kernel": "decode_splitkv_kernel", "kernel_ms": kern_ms / max(1, nprof),
+                     "kernel": "decode_gqa_mma_kernel", "kernel_ms": kern_ms / max(1, nprof),
                      "traffic": cx.traffic.get("decode_splitkv_bytes_per_launch")},
     }
 
