@@ -214,6 +214,31 @@ typedef struct vb200_exchange_args {
 size_t vb200_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t D);
 int vb200_exchange_combine(const vb200_exchange_args* a);
 
+/* ---- attention backward (training; fp32, the reference's training dtype) --------------------
+ * dQ, dK, dV of O = softmax(scale Q K^T [causal]) V from the saved O and LSE of the forward, P
+ * recomputed tile by tile.  All tensors contiguous [B,H,N,D] fp32 with Hq == Hkv (the reference op
+ * takes q, k, v of one shape), lse [B,H,N]; dq, dk, dv are overwritten.  Deterministic (no atomics).
+ * workspace: B*H*N floats (vb200_attention_bwd_workspace_bytes).  Replaces
+ * flash_attention_backward_cuda_dispatch (src/ops/flash_attention.cpp:34-39,
+ * src/ops/cuda/flash_attention.cu:546-576; CPU form src/ops/flash_attention.cpp:366-482); like the
+ * reference's CUDA path it has no dropout. */
+typedef struct vb200_attention_bwd_args {
+    size_t struct_size;
+    int32_t device;
+    void* stream;
+    int32_t dtype;               /* VB200_F32 */
+    int32_t B, H, N, D;
+    int32_t causal;
+    float scale;
+    const void *d_out, *q, *k, *v, *out;
+    const float* lse;
+    void *dq, *dk, *dv;
+    void* workspace;
+    size_t workspace_bytes;
+} vb200_attention_bwd_args;
+size_t vb200_attention_bwd_workspace_bytes(const vb200_attention_bwd_args* a);
+int vb200_attention_bwd(const vb200_attention_bwd_args* a);
+
 /* ---- cache append without attention ---------------------------------------
  * Rotates K (if rope.enabled) and writes K, V rows [start_pos, start_pos+T)
  * of the cache.  Replaces the copy_strided_cuda_dispatch calls behind

@@ -64,6 +64,7 @@ class Oracle:
         L.vo_decode_ragged.argtypes = [_f32p] * 3 + [C.POINTER(C.c_int32)] + [_f32p] * 2 + [_i64] * 5
         L.vo_lse_combine.argtypes = [_f32p] * 5 + [_i64] * 3
         L.vo_bf16_round_array.argtypes = [_f32p, _f32p, _i64]
+        L.vo_flash_attention_bwd.argtypes = [_f32p] * 9 + [_i64] * 4 + [C.c_float, C.c_int]
         _i32p = C.POINTER(C.c_int32)
         L.vo_linear.argtypes = [_f32p] * 3 + [_i64] * 3
         L.vo_rms_norm.argtypes = [_f32p] * 3 + [_i64] * 2 + [C.c_float]
@@ -165,6 +166,13 @@ class Oracle:
         self.lib.vo_bf16_round_array(_fp(x), _fp(out), x.size)
         return out
 
+    def flash_attention_bwd(self, d_out, q, k, v, out, lse, scale, causal=True):
+        d_out, q, k, v, out, lse = _f32(d_out), _f32(q), _f32(k), _f32(v), _f32(out), _f32(lse)
+        B, H, N, D = q.shape
+        dq, dk, dv = np.empty_like(q), np.empty_like(q), np.empty_like(q)
+        self.lib.vo_flash_attention_bwd(_fp(d_out), _fp(q), _fp(k), _fp(v), _fp(out), _fp(lse), _fp(dq), _fp(dk), _fp(dv), B, H, N, D, scale, int(causal))
+        return dq, dk, dv
+
     # ---- decoder-block operators (vesper_block_oracle.c) ----
     def linear(self, x, w):
         x, w = _f32(x), _f32(w)
@@ -241,6 +249,7 @@ class Ref:
         L.ref_gqa_forward.argtypes = [C.c_void_p, _f32p, _f32p] + [_i64] * 3 + [C.c_int]
         L.ref_gqa_forward_cached.argtypes = [C.c_void_p, C.c_void_p, _f32p, _f32p] + [_i64] * 4
         _i32p = C.POINTER(C.c_int32)
+        L.ref_flash_attention_backward.argtypes = [_f32p] * 9 + [_i64] * 4 + [C.c_float, C.c_int]
         L.ref_linear.argtypes = [_f32p] * 3 + [_i64] * 3
         L.ref_rms_norm.argtypes = [_f32p] * 3 + [_i64] * 2 + [C.c_float]
         L.ref_silu_mul.argtypes = [_f32p] * 3 + [_i64]
@@ -377,6 +386,14 @@ class Ref:
 
     def gqa(self, C_, Hq, Hkv, max_seq, theta, wqkv, wo):
         return Ref.GQA(self, C_, Hq, Hkv, max_seq, theta, wqkv, wo)
+
+    def flash_attention_bwd(self, d_out, q, k, v, out, lse, scale, causal=True):
+        d_out, q, k, v, out, lse = _f32(d_out), _f32(q), _f32(k), _f32(v), _f32(out), _f32(lse)
+        B, H, N, D = q.shape
+        dq, dk, dv = np.empty_like(q), np.empty_like(q), np.empty_like(q)
+        self._chk(self.lib.ref_flash_attention_backward(_fp(d_out), _fp(q), _fp(k), _fp(v), _fp(out), _fp(lse), _fp(dq), _fp(dk), _fp(dv),
+                                                        B, H, N, D, scale, int(causal)))
+        return dq, dk, dv
 
     # ---- decoder-block operators and the model, through the reference's own classes ----
     def linear(self, x, w):

@@ -251,6 +251,22 @@ int ref_gqa_forward_cached(void* m, void* cache, const float* x, float* y,
     } catch (const std::exception& e) { g_err = e.what(); return -1; }
 }
 
+// ops::flash_attention_backward (src/ops/flash_attention.cpp:165-215 -> CPU backward :366-482)
+int ref_flash_attention_backward(const float* d_out, const float* q, const float* k, const float* v,
+                                 const float* out, const float* lse, float* dq, float* dk, float* dv,
+                                 int64_t B, int64_t H, int64_t N, int64_t D, float scale, int causal) {
+    try {
+        vesper::autograd::NoGradGuard ng;
+        std::vector<int64_t> sh = {B, H, N, D};
+        auto g = vesper::ops::flash_attention_backward(from_host(d_out, sh), from_host(q, sh), from_host(k, sh), from_host(v, sh),
+                                                       from_host(out, sh), from_host(lse, {B, H, N}), scale, causal != 0, 0.0f, Tensor());
+        to_host(std::get<0>(g), dq);
+        to_host(std::get<1>(g), dk);
+        to_host(std::get<2>(g), dv);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+
 // ---- decoder-block operators --------------------------------------------------------------
 // y[M,N] = x[M,K] w[N,K]^T exactly as nn::Linear::forward does it: matmul(x, weight.transpose(0,1))
 // (src/nn/linear.cpp:41-48).

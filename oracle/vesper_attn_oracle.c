@@ -364,3 +364,41 @@ void vo_bf16_round_array(const float* in, float* out, int64_t n)
 {
     for (int64_t i = 0; i < n; ++i) out[i] = vo_bf16_round(in[i]);
 }
+
+void vo_flash_attention_bwd(const float* d_out, const float* q, const float* k, const float* v,
+                            const float* out, const float* lse, float* dq, float* dk, float* dv,
+                            int64_t B, int64_t H, int64_t N, int64_t D, float scale, int causal) {
+    memset(dq, 0, sizeof(float) * (size_t)(B * H * N * D));
+    memset(dk, 0, sizeof(float) * (size_t)(B * H * N * D));
+    memset(dv, 0, sizeof(float) * (size_t)(B * H * N * D));
+    float* Di = (float*)malloc(sizeof(float) * (size_t)N);
+    for (int64_t bh = 0; bh < B * H; ++bh) {
+        const float* qp = q + bh * N * D; const float* kp = k + bh * N * D; const float* vp = v + bh * N * D;
+        const float* op = out + bh * N * D; const float* dop = d_out + bh * N * D; const float* lp = lse + bh * N;
+        float* dqp = dq + bh * N * D; float* dkp = dk + bh * N * D; float* dvp = dv + bh * N * D;
+        for (int64_t i = 0; i < N; ++i) {
+            float sum = 0.0f;
+            for (int64_t d = 0; d < D; ++d) sum += dop[i * D + d] * op[i * D + d];
+            Di[i] = sum;
+        }
+        for (int64_t qi = 0; qi < N; ++qi) {
+            const float li = lp[qi];
+            const int64_t k_end = causal ? qi + 1 : N;
+            for (int64_t ki = 0; ki < k_end; ++ki) {
+                float score = 0.0f;
+                for (int64_t d = 0; d < D; ++d) score += qp[qi * D + d] * kp[ki * D + d];
+                score *= scale;
+                const float p = expf(score - li);
+                for (int64_t d = 0; d < D; ++d) dvp[ki * D + d] += p * dop[qi * D + d];
+                float dp = 0.0f;
+                for (int64_t d = 0; d < D; ++d) dp += dop[qi * D + d] * vp[ki * D + d];
+                const float ds = p * (dp - Di[qi]);
+                for (int64_t d = 0; d < D; ++d) {
+                    dqp[qi * D + d] += scale * ds * kp[ki * D + d];
+                    dkp[ki * D + d] += scale * ds * qp[qi * D + d];
+                }
+            }
+        }
+    }
+    free(Di);
+}

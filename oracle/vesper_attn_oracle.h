@@ -112,6 +112,15 @@ void vo_lse_combine(const float* m, const float* l, const float* o,
                     int64_t R, int64_t rows, int64_t D);
 
 /* Round-to-nearest-even fp32 -> bf16 -> fp32, include/vesper/core/half.h:162-173. */
+/* flash_attention_backward_cpu_dispatch, src/ops/flash_attention.cpp:366-482 (no dropout):
+ * Di = rowsum(dO * O); for every visible (query i, key j): p = exp(scale q_i.k_j - lse_i),
+ * dV_j += p dO_i, dS = p (dO_i.v_j - Di_i), dQ_i += scale dS k_j, dK_j += scale dS q_i,
+ * accumulated in the reference's loop order.  All tensors [B,H,N,D] fp32, lse [B,H,N];
+ * dq, dk, dv are overwritten. */
+void vo_flash_attention_bwd(const float* d_out, const float* q, const float* k, const float* v,
+                            const float* out, const float* lse, float* dq, float* dk, float* dv,
+                            int64_t B, int64_t H, int64_t N, int64_t D, float scale, int causal);
+
 float vo_bf16_round(float x);
 void vo_bf16_round_array(const float* in, float* out, int64_t n);
 

@@ -5,12 +5,16 @@
 //   cached == uncached forward                      tests/test_kv_cache_chapter33.cpp:66-188
 //   RoPE angle table / 90 degree rotation           tests/test_rope.cpp:11-73
 //   repeat_kv index pattern                         tests/test_gqa_chapter33.cpp:76-118
+//   flash backward: finite, non-zero, vs CPU        tests/test_flash_attention.cpp:292-339
+//   model forward_with_cache / greedy generation    src/models/transformer.cpp:152-206, src/generation/generator.cpp:36-142
 // The CPU side is the oracle (oracle/vesper_attn_oracle.c, pinned to the reference).
 #include <vesper/core/factories.h>
 #include <vesper/nn/functional.h>
 #include <vesper/nn/transformer.h>
 #include <vesper/ops/attention_ops.h>
 #include <vesper/ops/flash_attention.h>
+#include <vesper/generation/generator.h>
+#include <vesper/models/transformer.h>
 
 #include "../../oracle/vesper_attn_oracle.h"
 
@@ -216,6 +220,72 @@ static void test_sdpa_routes() {                // src/nn/functional.cpp:370-422
     }
 }
 
+static void test_flash_backward() {             // tests/test_flash_attention.cpp:292-339: d(sum(out)) exists, finite, non-zero
+    int B = 1, H = 2, N = 16, D = 32;
+    size_t n = static_cast<size_t>(B) * H * N * D;
+    float scale = 1.0f / std::sqrt(static_cast<float>(D));
+    auto q = randn(n, 41), k = randn(n, 42), v = randn(n, 43);
+    std::vector<float> ones(n, 1.0f), o(n), lse(static_cast<size_t>(B) * H * N), dq(n), dk(n), dv(n);
+    vo_flash_attention_fwd(q.data(), k.data(), v.data(), o.data(), lse.data(), B, H, N, D, scale, 1);
+    vo_flash_attention_bwd(ones.data(), q.data(), k.data(), v.data(), o.data(), lse.data(), dq.data(), dk.data(), dv.data(), B, H, N, D, scale, 1);
+    Tensor tq = to_cuda(q, {B, H, N, D}), tk = to_cuda(k, {B, H, N, D}), tv = to_cuda(v, {B, H, N, D});
+    auto fwd = ops::flash_attention_with_lse(tq, tk, tv, scale, true);
+    auto g = ops::flash_attention_backward(to_cuda(ones, {B, H, N, D}), tq, tk, tv, fwd.first, fwd.second, scale, true);
+    auto gq = to_host(std::get<0>(g)), gk = to_host(std::get<1>(g)), gv = to_host(std::get<2>(g));
+    CHECK(std::get<0>(g).shape() == tq.shape());
+    bool nonzero = false;
+    for (float x : gq) { CHECK(std::isfinite(x)); nonzero = nonzero || x != 0.f; }
+    CHECK(nonzero);
+    CHECK(allclose(gq, dq, 1e-3f, 1e-4f) && allclose(gk, dk, 1e-3f, 1e-4f) && allclose(gv, dv, 1e-3f, 1e-4f));
+}
+
+static void test_model_generate() {             // cached decode == full forward; greedy loop shape and determinism
+    models::TransformerConfig c;
+    c.vocab_size = 128; c.dim = 256; c.n_layers = 2; c.n_heads = 2; c.n_kv_heads = 1; c.ffn_hidden_dim = 320; c.max_seq_len = 32;
+    c.norm_eps = 1e-6f;
+    models::TransformerLM m(c);
+    unsigned seed = 100;
+    for (auto& kv : m.parameter_shapes()) {
+        size_t n = 1;
+        for (auto d : kv.second) n *= static_cast<size_t>(d);
+        auto w = kv.second.size() == 1 ? std::vector<float>(n, 1.0f) : randn(n, seed++, 0.06f);
+        m.load_parameter(kv.first, w.data(), static_cast<int64_t>(n));
+    }
+    bool threw = false;
+    Tensor ids = empty({2, 10}, DType::Int32, Device::CPU);
+    for (int i = 0; i < 20; ++i) ids.data_ptr<int32_t>()[i] = (7 * i + 3) % 128;
+    try { m.forward_with_cache(ids, 0); } catch (const std::runtime_error& e) { threw = std::string(e.what()).find("KV cache not initialized") != std::string::npos; }
+    CHECK(threw);
+    m.init_cache(2, Device::CUDA);
+    CHECK(m.has_cache());
+    auto full = to_host(m.forward_with_cache(ids, 0));                       // [2, 10, 128]
+    m.init_cache(2, Device::CUDA);
+    Tensor head = empty({2, 9}, DType::Int32, Device::CPU), last = empty({2, 1}, DType::Int32, Device::CPU);
+    for (int b = 0; b < 2; ++b) {
+        for (int t = 0; t < 9; ++t) head.data_ptr<int32_t>()[b * 9 + t] = ids.data_ptr<int32_t>()[b * 10 + t];
+        last.data_ptr<int32_t>()[b] = ids.data_ptr<int32_t>()[b * 10 + 9];
+    }
+    m.forward_with_cache(head, 0);
+    auto step = to_host(m.forward_with_cache(last, 9));                      // [2, 1, 128]
+    float scale = 0.f;
+    for (float x : full) scale = std::max(scale, std::fabs(x));
+    for (int b = 0; b < 2; ++b)
+        for (int vv = 0; vv < 128; ++vv) CHECK(std::fabs(step[b * 128 + vv] - full[(b * 10 + 9) * 128 + vv]) <= 2e-2f * scale);
+    generation::Generator gen(&m);
+    generation::SamplingParams sp;
+    sp.do_sample = false; sp.max_new_tokens = 8;
+    Tensor a = gen.generate(ids, sp), b2 = gen.generate(ids, sp);
+    CHECK(a.shape()[0] == 2 && a.shape()[1] == 18 && a.dtype() == DType::Int32);
+    CHECK(gen.last_timings().graph_replay && gen.last_timings().decode_steps == 7);
+    for (int i = 0; i < 36; ++i) CHECK(a.data_ptr<int32_t>()[i] == b2.data_ptr<int32_t>()[i]);      // deterministic
+    for (int b = 0; b < 2; ++b) for (int t = 0; t < 10; ++t) CHECK(a.data_ptr<int32_t>()[b * 18 + t] == ids.data_ptr<int32_t>()[b * 10 + t]);
+    sp.do_sample = true;
+    threw = false;
+    try { gen.generate(ids, sp); } catch (const std::runtime_error&) { threw = true; }
+    CHECK(threw);
+    CHECK(!m.has_cache());                                                    // generate() clears the cache (generator.cpp:133)
+}
+
 int main() {
     std::printf("flash attention: GPU vs CPU\n");
     test_flash_vs_cpu(2, 4, 64, 64, false, DType::Float32, 1e-2f, 1e-3f);
@@ -234,6 +304,9 @@ int main() {
     test_rope_table_and_rotation();
     test_repeat_kv_pattern();
     test_sdpa_routes();
+    std::printf("flash backward / model / generator\n");
+    test_flash_backward();
+    test_model_generate();
     std::printf("All B200 host-layer tests passed\n");
     return 0;
 }

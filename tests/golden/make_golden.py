@@ -120,6 +120,18 @@ def main():
     save("gqa_module_forward", wqkv=wqkv, wo=wo, x=x, y=g.forward(x, True),
          dims=np.array([Cdim, Hq, Hkv, T], np.int32))
 
+    # -- ops::flash_attention_backward (src/ops/flash_attention.cpp:165-215, CPU form :366-482), the shapes of
+    #    tests/test_flash_attention.cpp:295,345 plus a ragged one, causal and not
+    bw = {}
+    for tag, (B, H, N, D, causal) in {"a": (1, 2, 16, 32, True), "b": (1, 1, 8, 16, True), "c": (1, 2, 45, 64, False)}.items():
+        rng2 = np.random.default_rng(700 + N)
+        q, k, v, do = [rng2.standard_normal((B, H, N, D)).astype(np.float32) for _ in range(4)]
+        sc = np.float32(1.0 / np.sqrt(D))
+        o, lse = r.flash_attention(q, k, v, float(sc), causal)
+        dq, dk, dv = r.flash_attention_bwd(do, q, k, v, o, lse, float(sc), causal)
+        bw.update({f"{tag}_q": q, f"{tag}_k": k, f"{tag}_v": v, f"{tag}_do": do, f"{tag}_o": o, f"{tag}_lse": lse,
+                   f"{tag}_dq": dq, f"{tag}_dk": dk, f"{tag}_dv": dv, f"{tag}_scale": sc, f"{tag}_causal": np.int32(causal)})
+    save("flash_backward", **bw)
     block_and_model_fixtures(r)
 
 

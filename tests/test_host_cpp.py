@@ -52,6 +52,14 @@ def test_headers_keep_reference_signatures():
     assert "Tensor scaled_dot_product_attention(const Tensor& query, const Tensor& key, const Tensor& value," in fn
     assert "Tensor compute_rope_frequencies(int seq_len, int head_dim, int start_pos = 0, float theta = 10000.0f," in fn
     assert "Tensor apply_rotary_emb(const Tensor& x, const Tensor& freqs);" in fn
+    assert "std::tuple<Tensor, Tensor, Tensor> flash_attention_backward(const Tensor& grad_output, const Tensor& q, const Tensor& k," in fa
+    tm = open(os.path.join(inc, "models", "transformer.h")).read()
+    assert "explicit TransformerLM(const TransformerConfig& config);" in tm
+    assert "Tensor forward_with_cache(const Tensor& tokens, int64_t start_pos" in tm
+    assert "void init_cache(int64_t batch_size, Device device);" in tm and "void clear_cache();" in tm
+    gn = open(os.path.join(inc, "generation", "generator.h")).read()
+    assert "explicit Generator(models::TransformerLM* model)" in gn
+    assert "Tensor generate(const Tensor& prompt_ids, const SamplingParams& params);" in gn
 
 
 @pytest.mark.gpu

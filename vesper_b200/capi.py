@@ -52,6 +52,7 @@ class DecodeArgs(C.Structure):
 EXPORTS = [
     "vb200_prefill_workspace_bytes", "vb200_prefill_fwd", "vb200_decode_workspace_bytes", "vb200_decode_fwd",
     "vb200_decode_fwd_static", "vb200_exchange_buffer_bytes", "vb200_exchange_combine",
+    "vb200_attention_bwd_workspace_bytes", "vb200_attention_bwd",
     "vb200_lse_combine", "vb200_kv_append", "vb200_apply_rope", "vb200_repeat_kv", "vb200_rope_inv_freq",
     "vb200_strerror", "vb200_last_error_detail", "vb200_abi_version", "vb200_launch_count",
     "vb200_reset_launch_count", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
@@ -59,6 +60,15 @@ EXPORTS = [
 BLOCK_EXPORTS = [
     "vb200_linear", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
 ]
+
+
+class AttnBwdArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_size_t), ("device", C.c_int32), ("stream", C.c_void_p), ("dtype", C.c_int32),
+        ("B", C.c_int32), ("H", C.c_int32), ("N", C.c_int32), ("D", C.c_int32), ("causal", C.c_int32), ("scale", C.c_float),
+        ("d_out", C.c_void_p), ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
 
 
 class ExchangeArgs(C.Structure):
@@ -120,6 +130,9 @@ def load():
     L.vb200_check_kernel_status.argtypes = [C.c_int, C.c_void_p]
     L.vb200_profile_enable.argtypes = [C.c_int]
     L.vb200_profile_read.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
+    L.vb200_attention_bwd_workspace_bytes.argtypes = [C.POINTER(AttnBwdArgs)]
+    L.vb200_attention_bwd_workspace_bytes.restype = C.c_size_t
+    L.vb200_attention_bwd.argtypes = [C.POINTER(AttnBwdArgs)]
     L.vb200_exchange_buffer_bytes.argtypes = [C.c_int32, C.c_int64, C.c_int32]
     L.vb200_exchange_buffer_bytes.restype = C.c_size_t
     L.vb200_exchange_combine.argtypes = [C.POINTER(ExchangeArgs)]
@@ -275,6 +288,27 @@ def profile_read():
     ms, n = C.c_double(0.0), C.c_uint64(0)
     check(load().vb200_profile_read(C.byref(ms), C.byref(n)))
     return ms.value, n.value
+
+
+def attention_bwd(d_out, q, k, v, out, lse, *, scale, causal=True, stream=None):
+    """fp32 contiguous [B,H,N,D] tensors; returns (dq, dk, dv)."""
+    import torch
+    B, H, N, D = q.shape
+    a = AttnBwdArgs()
+    a.struct_size = C.sizeof(AttnBwdArgs)
+    a.device = q.device.index or 0
+    a.stream = _stream_ptr(stream)
+    a.dtype = dtype_code(q)
+    a.B, a.H, a.N, a.D, a.causal, a.scale = B, H, N, D, int(causal), scale
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    for name, t in (("d_out", d_out), ("q", q), ("k", k), ("v", v), ("out", out), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
+        assert t.is_contiguous()
+        setattr(a, name, _ptr(t))
+    need = load().vb200_attention_bwd_workspace_bytes(C.byref(a))
+    ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+    a.workspace, a.workspace_bytes = _ptr(ws), need
+    check(load().vb200_attention_bwd(C.byref(a)))
+    return dq, dk, dv
 
 
 def exchange_buffer_bytes(world, rows, D):

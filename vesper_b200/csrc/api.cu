@@ -425,6 +425,31 @@ int vb200_repeat_kv(int device, void* stream, int32_t dtype, const vb200_tensor4
     return launch_repeat_kv(static_cast<cudaStream_t>(stream), dtype, to_view(*in), out, B, Hkv, S, D, n_rep);
 }
 
+size_t vb200_attention_bwd_workspace_bytes(const vb200_attention_bwd_args* a) {
+    if (!a || a->struct_size != sizeof(vb200_attention_bwd_args) || a->B <= 0 || a->H <= 0 || a->N <= 0) return 0;
+    return align_up(sizeof(float) * static_cast<size_t>(a->B) * a->H * a->N, 256);
+}
+
+int vb200_attention_bwd(const vb200_attention_bwd_args* a) {
+    if (!a || a->struct_size != sizeof(vb200_attention_bwd_args)) return set_detail(VB200_ERR_INVALID_ARG, "vb200_attention_bwd_args: null or struct_size mismatch");
+    if (a->dtype != VB200_F32) return set_detail(VB200_ERR_UNSUPPORTED, "vb200_attention_bwd: fp32 only (the reference's training dtype)");
+    if (a->B <= 0 || a->H <= 0 || a->N <= 0 || a->D <= 0) return set_detail(VB200_ERR_INVALID_ARG, "B, H, N, D must be positive");
+    if (a->D > 128) return set_detail(VB200_ERR_UNSUPPORTED, "vb200_attention_bwd: head_dim must be <= 128");
+    if (!a->d_out || !a->q || !a->k || !a->v || !a->out || !a->lse || !a->dq || !a->dk || !a->dv)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_attention_bwd: null tensor");
+    if (!a->workspace || a->workspace_bytes < vb200_attention_bwd_workspace_bytes(a))
+        return set_detail(VB200_ERR_WORKSPACE, "vb200_attention_bwd: workspace missing or too small");
+    DeviceGuard g;
+    if (int rc = g.init(a->device)) return rc;
+    AttnBwdParams p{};
+    p.B = a->B; p.H = a->H; p.N = a->N; p.D = a->D; p.causal = a->causal; p.scale = a->scale;
+    p.d_out = static_cast<const float*>(a->d_out); p.q = static_cast<const float*>(a->q); p.k = static_cast<const float*>(a->k);
+    p.v = static_cast<const float*>(a->v); p.out = static_cast<const float*>(a->out); p.lse = a->lse;
+    p.dq = static_cast<float*>(a->dq); p.dk = static_cast<float*>(a->dk); p.dv = static_cast<float*>(a->dv);
+    p.delta = static_cast<float*>(a->workspace);
+    return launch_attention_bwd_f32(static_cast<cudaStream_t>(a->stream), p);
+}
+
 size_t vb200_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t D) {
     if (world <= 0 || world > VB200_EXCHANGE_MAX_WORLD || rows <= 0 || D <= 0) return 0;
     return exchange_buffer_bytes(world, rows, D);

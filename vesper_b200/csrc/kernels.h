@@ -80,6 +80,16 @@ template <typename T, int NREP> int launch_decode_gqa_mma_split(cudaStream_t s, 
 int launch_lse_combine(cudaStream_t s, const float* partials, int R, long long rows, int D,
                        int dtype, void* out, float* lse);
 
+// ---- flash_bwd_f32.cu ----
+struct AttnBwdParams {
+    int B, H, N, D, causal;
+    float scale;
+    const float *d_out, *q, *k, *v, *out, *lse;   // contiguous [B,H,N,D]; lse [B,H,N]
+    float *dq, *dk, *dv;
+    float* delta;                                 // workspace [B,H,N]
+};
+int launch_attention_bwd_f32(cudaStream_t s, const AttnBwdParams& p);
+
 // ---- decode_exchange.cu ----
 struct ExchangeParams {
     int world, rank;

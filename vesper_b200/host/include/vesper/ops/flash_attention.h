@@ -4,6 +4,7 @@
 // (src/ops/flash_attention.cpp:28-32) and forwards to vb200_prefill_fwd.
 #pragma once
 #include <vesper/core/tensor.h>
+#include <tuple>
 #include <utility>
 
 namespace vesper::ops {
@@ -22,5 +23,17 @@ std::pair<Tensor, Tensor> flash_attention_with_lse(const Tensor& q, const Tensor
 void flash_attention_cuda_dispatch(const Tensor& q, const Tensor& k, const Tensor& v,
                                    Tensor& output, Tensor& lse, float scale, bool is_causal,
                                    float dropout_p, bool training, Tensor* dropout_mask_out);
+
+// Backward for training (include/vesper/ops/flash_attention.h:61-70 of the reference): gradients of
+// q, k, v from the saved output and log-sum-exp.  Float32, contiguous inputs are made as the reference does
+// (src/ops/flash_attention.cpp:373-378); dropout is not part of the CUDA path (dropout_p must be 0).
+std::tuple<Tensor, Tensor, Tensor> flash_attention_backward(const Tensor& grad_output, const Tensor& q, const Tensor& k,
+                                                            const Tensor& v, const Tensor& output, const Tensor& lse,
+                                                            float scale, bool is_causal, float dropout_p = 0.0f,
+                                                            const Tensor& dropout_mask = Tensor());
+void flash_attention_backward_cuda_dispatch(const Tensor& grad_output, const Tensor& q, const Tensor& k, const Tensor& v,
+                                            const Tensor& output, const Tensor& lse, Tensor& grad_q, Tensor& grad_k,
+                                            Tensor& grad_v, float scale, bool is_causal, float dropout_p,
+                                            const Tensor* dropout_mask);
 
 }  // namespace vesper::ops

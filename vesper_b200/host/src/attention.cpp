@@ -96,6 +96,45 @@ Tensor flash_attention(const Tensor& q, const Tensor& k, const Tensor& v, float 
     return flash_attention_with_lse(q, k, v, scale, is_causal).first;
 }
 
+void flash_attention_backward_cuda_dispatch(const Tensor& grad_output, const Tensor& q, const Tensor& k, const Tensor& v,
+                                            const Tensor& output, const Tensor& lse, Tensor& grad_q, Tensor& grad_k,
+                                            Tensor& grad_v, float scale, bool is_causal, float dropout_p,
+                                            const Tensor* /*dropout_mask*/) {
+    if (dropout_p > 0.0f) throw std::runtime_error("flash_attention_backward: dropout is not part of the CUDA path");
+    if (q.dtype() != DType::Float32) throw std::runtime_error("flash_attention_backward: Float32 only");
+    // contiguous copies where needed, as src/ops/flash_attention.cpp:373-378
+    Tensor dO = grad_output.contiguous(), qc = q.contiguous(), kc = k.contiguous(), vc = v.contiguous(), oc = output.contiguous(),
+           lc = lse.contiguous();
+    vb200_attention_bwd_args a{};
+    a.struct_size = sizeof(a);
+    a.device = q.device_index();
+    a.stream = current_stream();
+    a.dtype = VB200_F32;
+    a.B = static_cast<int>(q.shape()[0]); a.H = static_cast<int>(q.shape()[1]); a.N = static_cast<int>(q.shape()[2]); a.D = static_cast<int>(q.shape()[3]);
+    a.causal = is_causal ? 1 : 0;
+    a.scale = scale;
+    a.d_out = dO.data_ptr<char>(); a.q = qc.data_ptr<char>(); a.k = kc.data_ptr<char>(); a.v = vc.data_ptr<char>(); a.out = oc.data_ptr<char>();
+    a.lse = lc.data_ptr<float>();
+    a.dq = grad_q.data_ptr<char>(); a.dk = grad_k.data_ptr<char>(); a.dv = grad_v.data_ptr<char>();
+    Tensor ws = workspace(vb200_attention_bwd_workspace_bytes(&a));
+    a.workspace = ws.data_ptr<char>();
+    a.workspace_bytes = ws.numel() * 4;
+    check(vb200_attention_bwd(&a), "flash_attention_backward");
+}
+
+std::tuple<Tensor, Tensor, Tensor> flash_attention_backward(const Tensor& grad_output, const Tensor& q, const Tensor& k,
+                                                            const Tensor& v, const Tensor& output, const Tensor& lse,
+                                                            float scale, bool is_causal, float dropout_p,
+                                                            const Tensor& dropout_mask) {
+    if (q.ndim() != 4 || q.shape() != k.shape() || k.shape() != v.shape() || grad_output.shape() != q.shape() || output.shape() != q.shape())
+        throw std::runtime_error("flash_attention_backward: grad_output, Q, K, V, output must have the same 4D shape");
+    require_cuda(q, "flash_attention_backward");
+    Tensor gq = empty(q.shape(), q.dtype(), Device::CUDA), gk = empty(q.shape(), q.dtype(), Device::CUDA), gv = empty(q.shape(), q.dtype(), Device::CUDA);
+    flash_attention_backward_cuda_dispatch(grad_output, q, k, v, output, lse, gq, gk, gv, scale, is_causal, dropout_p,
+                                           dropout_mask.defined() ? &dropout_mask : nullptr);
+    return {gq, gk, gv};
+}
+
 void repeat_kv_cuda_dispatch(const Tensor& input, Tensor& output, int64_t n_rep) {
     vb200_tensor4 in = view4(input);
     check(vb200_repeat_kv(input.device_index(), current_stream(), dtype_of(input, "repeat_kv"), &in, output.data_ptr<char>(),
