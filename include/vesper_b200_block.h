@@ -43,6 +43,14 @@ typedef enum vb200_epilogue {
 int vb200_linear(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
                  void* out, int64_t ldo, int32_t M, int32_t N, int32_t K, int32_t epilogue, int32_t splits);
 
+/* h += x W^T followed by the RMSNorm of the finished rows, xn = rmsnorm(h) * norm_weight (bf16) -- the
+ * output projection / down projection of a block, its residual add, and the NEXT norm in the block
+ * sequence (src/models/transformer_block.cpp:183-205) as one call (two launches chained by
+ * programmatic dependent launch).  h [M, N] fp32 and xn [M, N] bf16 are contiguous (row stride N). */
+int vb200_linear_add_rmsnorm(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                             float* h, int32_t M, int32_t N, int32_t K, const float* norm_weight, float eps,
+                             void* xn_out, int32_t splits);
+
 /* out[2j] = a[j], out[2j+1] = b[j] for j < rows, rows of `cols` bf16 elements:
  * builds the interleaved (gate, up) weight VB200_EPI_SWIGLU expects from
  * SwiGLUMLP's gate_proj / up_proj weights (src/nn/swiglu.cpp:20-34). */
@@ -65,6 +73,11 @@ int vb200_silu_mul(int device, void* stream, const void* gate, const void* up, v
  * outside [0, vocab) writes zeros and sets the kernel status word. */
 int vb200_embedding(int device, void* stream, const void* ids, int32_t ids64, const void* table,
                     float* out, int32_t M, int32_t dim, int32_t vocab);
+/* The same gather, plus xn_out[m, :] = rmsnorm(out[m, :]) * norm_weight (bf16): embedding and the first
+ * block's attention norm in one launch. */
+int vb200_embedding_rmsnorm(int device, void* stream, const void* ids, int32_t ids64, const void* table,
+                            float* out, int32_t M, int32_t dim, int32_t vocab, const float* norm_weight,
+                            float eps, void* xn_out);
 
 /* Greedy step: out_ids[b] = argmax_v logits[b, v] (first maximum wins, as
  * argmax_cpu_dispatch, src/ops/sampling_ops.cpp:18-38; replaces

@@ -200,3 +200,44 @@ def test_greedy_step_matches_reference_argmax_and_stop_rule(cuda, oracle):
     torch.cuda.synchronize()
     assert int(done.sum()) == 0
     assert np.array_equal(hist[0::2, 2].cpu().numpy(), want[0::2]) and np.array_equal(hist[1::2, 3].cpu().numpy(), want[1::2])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 512), (8, 2048, 2048), (8, 2048, 5632), (16, 384, 456), (40, 2048, 512), (200, 512, 256)])
+def test_linear_add_rmsnorm(cuda, oracle, M, N, K):
+    """h += x W^T and the next RMSNorm in one call, behind both GEMM kernels."""
+    import torch
+    from vesper_b200 import capi
+    rng = np.random.default_rng(M + N + K)
+    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    w = bf16_round((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32))
+    h0 = rng.standard_normal((M, N)).astype(np.float32)
+    g = (1.0 + 0.1 * rng.standard_normal(N)).astype(np.float32)
+    h = to_torch(h0, torch.float32, cuda)
+    xn = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=cuda)
+    for rep in range(2):
+        capi.linear_add_rmsnorm(to_torch(x, torch.bfloat16, cuda), to_torch(w, torch.bfloat16, cuda), h, to_torch(g, torch.float32, cuda), 1e-6, xn)
+        torch.cuda.synchronize()
+        capi.check_kernel_status(0)
+        want_h = h0 + (rep + 1) * oracle.linear(x, w)
+        got_h = from_torch(h)
+        assert np.all(np.abs(got_h - want_h) <= 1e-3 * (1.0 + np.abs(want_h)))
+        want_n = oracle.rms_norm(got_h, g, 1e-6)            # the norm of the rows the GPU actually holds
+        err = np.abs(from_torch(xn) - want_n)
+        assert np.all(err <= 2.0 ** -8 * np.abs(want_n) + 1e-5), (rep, float(err.max()))
+
+
+def test_embedding_rmsnorm(cuda, oracle):
+    import torch
+    from vesper_b200 import capi
+    rng = np.random.default_rng(12)
+    table = bf16_round(rng.standard_normal((500, 2048)).astype(np.float32))
+    g = (1.0 + 0.1 * rng.standard_normal(2048)).astype(np.float32)
+    ids = rng.integers(0, 500, size=(9,)).astype(np.int32)
+    out = torch.empty(9, 2048, dtype=torch.float32, device=cuda)
+    xn = torch.empty(9, 2048, dtype=torch.bfloat16, device=cuda)
+    capi.embedding_rmsnorm(torch.from_numpy(ids).to(cuda), to_torch(table, torch.bfloat16, cuda), out, to_torch(g, torch.float32, cuda), 1e-6, xn)
+    torch.cuda.synchronize()
+    want = oracle.embedding(ids, table)
+    assert np.array_equal(from_torch(out), want)
+    wn = oracle.rms_norm(want, g, 1e-6)
+    assert np.all(np.abs(from_torch(xn) - wn) <= 2.0 ** -8 * np.abs(wn) + 1e-6)

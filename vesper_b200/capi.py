@@ -58,7 +58,7 @@ EXPORTS = [
     "vb200_reset_launch_count", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
 ]
 BLOCK_EXPORTS = [
-    "vb200_linear", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
+    "vb200_linear", "vb200_linear_add_rmsnorm", "vb200_embedding_rmsnorm", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
 ]
 
 
@@ -138,6 +138,10 @@ def load():
     L.vb200_exchange_combine.argtypes = [C.POINTER(ExchangeArgs)]
     # decoder-block operators (include/vesper_b200_block.h)
     L.vb200_linear.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64] + [C.c_int32] * 5
+    L.vb200_linear_add_rmsnorm.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                           C.c_void_p, C.c_float, C.c_void_p, C.c_int32]
+    L.vb200_embedding_rmsnorm.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                          C.c_void_p, C.c_float, C.c_void_p]
     L.vb200_interleave_rows.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]
     L.vb200_rms_norm.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_float]
     L.vb200_silu_mul.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]
@@ -343,6 +347,23 @@ def linear(x, w, out, epilogue=EPI_BF16, splits=0, stream=None):
     check(load().vb200_linear(x.device.index or 0, _stream_ptr(stream), _ptr(x), x.stride(0), _ptr(w), w.stride(0),
                               _ptr(out), out.stride(0), M, N, K, epilogue, splits))
     return out
+
+
+def linear_add_rmsnorm(x, w, h, norm_weight, eps, xn_out, splits=0, stream=None):
+    """h += x @ w.T; xn_out = rmsnorm(h) * norm_weight (bf16)."""
+    M, K = x.shape
+    N = w.shape[0]
+    check(load().vb200_linear_add_rmsnorm(x.device.index or 0, _stream_ptr(stream), _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(h), M, N, K,
+                                          _ptr(norm_weight), eps, _ptr(xn_out), splits))
+    return h, xn_out
+
+
+def embedding_rmsnorm(ids, table, out, norm_weight, eps, xn_out, stream=None):
+    import torch
+    ids64 = 1 if ids.dtype == torch.int64 else 0
+    check(load().vb200_embedding_rmsnorm(table.device.index or 0, _stream_ptr(stream), _ptr(ids), ids64, _ptr(table), _ptr(out), ids.numel(),
+                                         table.shape[1], table.shape[0], _ptr(norm_weight), eps, _ptr(xn_out)))
+    return out, xn_out
 
 
 def interleave_rows(a, b, out, stream=None):

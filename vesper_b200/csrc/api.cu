@@ -504,6 +504,25 @@ int vb200_linear(int device, void* stream, const void* x, int64_t ldx, const voi
     return launch_linear(static_cast<cudaStream_t>(stream), p);
 }
 
+int vb200_linear_add_rmsnorm(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                             float* h, int32_t M, int32_t N, int32_t K, const float* norm_weight, float eps,
+                             void* xn_out, int32_t splits) {
+    if (!x || !w || !h || !norm_weight || !xn_out || M <= 0 || N <= 0 || K <= 0)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_add_rmsnorm: null pointer or non-positive size");
+    if (ldx < K || ldw < K) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_add_rmsnorm: ldx and ldw must be >= K");
+    if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(h) || !aligned16(norm_weight) || !aligned16(xn_out))
+        return set_detail(VB200_ERR_ALIGNMENT, "vb200_linear_add_rmsnorm: K % 8, N % 8 and 16-byte aligned bases and row strides are required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    LinearParams p{};
+    p.x = x; p.ldx = ldx; p.w = w; p.ldw = ldw; p.out = h; p.ldo = N;
+    p.M = M; p.N = N; p.K = K; p.epilogue = VB200_EPI_ADD_F32; p.splits = splits;
+    p.norm_w = norm_weight; p.norm_out = xn_out; p.norm_ld = N; p.norm_eps = eps;
+    p.status = kernel_status_word();
+    if (!p.status) return VB200_ERR_CUDA;
+    return launch_linear(static_cast<cudaStream_t>(stream), p);
+}
+
 int vb200_interleave_rows(int device, void* stream, const void* a, const void* b, void* out, int64_t rows, int64_t cols) {
     if (!a || !b || !out || rows <= 0 || cols <= 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_interleave_rows: bad arguments");
     if (!aligned16(a) || !aligned16(b) || !aligned16(out)) return set_detail(VB200_ERR_ALIGNMENT, "vb200_interleave_rows: 16-byte alignment required");
@@ -538,6 +557,20 @@ int vb200_embedding(int device, void* stream, const void* ids, int32_t ids64, co
     int* status = kernel_status_word();
     if (!status) return VB200_ERR_CUDA;
     return launch_embedding(static_cast<cudaStream_t>(stream), ids, ids64, table, out, M, dim, vocab, status);
+}
+
+int vb200_embedding_rmsnorm(int device, void* stream, const void* ids, int32_t ids64, const void* table,
+                            float* out, int32_t M, int32_t dim, int32_t vocab, const float* norm_weight,
+                            float eps, void* xn_out) {
+    if (!ids || !table || !out || !norm_weight || !xn_out || M <= 0 || dim <= 0 || vocab <= 0)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_embedding_rmsnorm: bad arguments");
+    if (!aligned16(table) || !aligned16(out) || !aligned16(norm_weight) || !aligned16(xn_out))
+        return set_detail(VB200_ERR_ALIGNMENT, "vb200_embedding_rmsnorm: 16-byte alignment required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    int* status = kernel_status_word();
+    if (!status) return VB200_ERR_CUDA;
+    return launch_embedding(static_cast<cudaStream_t>(stream), ids, ids64, table, out, M, dim, vocab, status, norm_weight, xn_out, eps);
 }
 
 int vb200_greedy_step(const vb200_greedy_args* a) {

@@ -77,9 +77,12 @@ __global__ void silu_mul_kernel(const uint4* __restrict__ gate, const uint4* __r
     }
 }
 
-// out[m,:] = float(table[ids[m],:]) -- ops::embedding, src/ops/embedding.cpp:10-17.
-__global__ void embedding_kernel(const void* __restrict__ ids, int ids64, const __nv_bfloat16* __restrict__ table,
-                                 float* __restrict__ out, int dim, int vocab, int* status) {
+// out[m,:] = float(table[ids[m],:]) -- ops::embedding, src/ops/embedding.cpp:10-17; optionally also the
+// RMSNorm of the row (the first block's attention norm) so a decode step starts with one launch less.
+__global__ void __launch_bounds__(256)
+embedding_kernel(const void* __restrict__ ids, int ids64, const __nv_bfloat16* __restrict__ table,
+                 float* __restrict__ out, int dim, int vocab, int* status, const float* __restrict__ norm_w,
+                 __nv_bfloat16* __restrict__ norm_out, float norm_eps) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long m = blockIdx.x;
@@ -88,12 +91,37 @@ __global__ void embedding_kernel(const void* __restrict__ ids, int ids64, const 
     if (bad && threadIdx.x == 0) atomicCAS(status, 0, (2 << 24) | 0x61);
     const uint4* src = reinterpret_cast<const uint4*>(table + (bad ? 0 : id) * dim);
     float4* dst = reinterpret_cast<float4*>(out + m * dim);
+    float ss = 0.f;
     for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) {
         const uint4 u = bad ? make_uint4(0, 0, 0, 0) : __ldg(src + i);
         const float2 a = Elem<__nv_bfloat16>::unpack2(u.x), b = Elem<__nv_bfloat16>::unpack2(u.y);
         const float2 c = Elem<__nv_bfloat16>::unpack2(u.z), d = Elem<__nv_bfloat16>::unpack2(u.w);
         dst[2 * i] = make_float4(a.x, a.y, b.x, b.y);
         dst[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+        ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+    }
+    if (norm_out == nullptr) return;
+    __shared__ float part[8];
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += part[i];
+    const float inv_rms = 1.0f / sqrtf(tot / static_cast<float>(dim) + norm_eps);
+    uint4* nd = reinterpret_cast<uint4*>(norm_out + m * dim);
+    const float4* g = reinterpret_cast<const float4*>(norm_w);
+    for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) {
+        const uint4 u = bad ? make_uint4(0, 0, 0, 0) : __ldg(src + i);
+        const float2 a = Elem<__nv_bfloat16>::unpack2(u.x), b = Elem<__nv_bfloat16>::unpack2(u.y);
+        const float2 c = Elem<__nv_bfloat16>::unpack2(u.z), d = Elem<__nv_bfloat16>::unpack2(u.w);
+        const float4 g0 = __ldg(g + 2 * i), g1 = __ldg(g + 2 * i + 1);
+        uint4 o;
+        o.x = Elem<__nv_bfloat16>::pack2(a.x * inv_rms * g0.x, a.y * inv_rms * g0.y);
+        o.y = Elem<__nv_bfloat16>::pack2(b.x * inv_rms * g0.z, b.y * inv_rms * g0.w);
+        o.z = Elem<__nv_bfloat16>::pack2(c.x * inv_rms * g1.x, c.y * inv_rms * g1.y);
+        o.w = Elem<__nv_bfloat16>::pack2(d.x * inv_rms * g1.z, d.y * inv_rms * g1.w);
+        nd[i] = o;
     }
 }
 
@@ -198,10 +226,11 @@ int launch_silu_mul(cudaStream_t s, const void* gate, const void* up, void* out,
 }
 
 int launch_embedding(cudaStream_t s, const void* ids, int ids64, const void* table, float* out, int M, int dim,
-                     int vocab, int* status) {
+                     int vocab, int* status, const float* norm_w, void* norm_out, float norm_eps) {
     if (dim % 8 != 0) return set_detail(VB200_ERR_ALIGNMENT, "embedding: dim must be a multiple of 8");
     return launch_pdl(embedding_kernel, dim3(static_cast<unsigned>(M)), dim3(256), s, ids, ids64,
-                      static_cast<const __nv_bfloat16*>(table), out, dim, vocab, status);
+                      static_cast<const __nv_bfloat16*>(table), out, dim, vocab, status, norm_w,
+                      static_cast<__nv_bfloat16*>(norm_out), norm_eps);
 }
 
 int launch_greedy_step(cudaStream_t s, const vb200_greedy_args& a) {

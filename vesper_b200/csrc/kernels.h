@@ -116,6 +116,11 @@ struct LinearParams {
     int epilogue;                    // vb200_epilogue
     int splits;                      // K slices per cluster of the skinny kernel, 0 = choose
     int* status;                     // device status word (bounded waits)
+    // optional, with the += epilogue: RMSNorm of the finished rows, out_norm[m,:] = out[m,:] * inv_rms * norm_w
+    const float* norm_w;             // [N]
+    void* norm_out;                  // [M, N] bf16, row stride norm_ld; null = no fused norm
+    long long norm_ld;
+    float norm_eps;
 };
 int launch_linear(cudaStream_t s, const LinearParams& p);
 
@@ -123,8 +128,9 @@ int launch_linear(cudaStream_t s, const LinearParams& p);
 int launch_interleave_rows(cudaStream_t s, const void* a, const void* b, void* out, long long rows, long long cols);
 int launch_rms_norm(cudaStream_t s, const float* x, const float* weight, void* out_bf16, int M, int dim, float eps);
 int launch_silu_mul(cudaStream_t s, const void* gate, const void* up, void* out, long long n);
+// norm_w / norm_out (nullable): also out_norm[m,:] = rmsnorm(out[m,:]) * norm_w as bf16
 int launch_embedding(cudaStream_t s, const void* ids, int ids64, const void* table, float* out, int M, int dim,
-                     int vocab, int* status);
+                     int vocab, int* status, const float* norm_w = nullptr, void* norm_out = nullptr, float norm_eps = 0.f);
 int launch_greedy_step(cudaStream_t s, const vb200_greedy_args& a);
 
 }  // namespace vb200

@@ -579,7 +579,14 @@ int launch_linear(cudaStream_t s, const LinearParams& p) {
     switch (p.epilogue) {
         case VB200_EPI_BF16: return launch_epi<VB200_EPI_BF16>(s, p);
         case VB200_EPI_F32: return launch_epi<VB200_EPI_F32>(s, p);
-        case VB200_EPI_ADD_F32: return launch_epi<VB200_EPI_ADD_F32>(s, p);
+        case VB200_EPI_ADD_F32: {
+            if (int rc = launch_epi<VB200_EPI_ADD_F32>(s, p)) return rc;
+            // the norm of the finished rows is a second launch, chained by programmatic dependent launch.  (Doing it
+            // inside the weight-streaming kernel, by the CTA that finishes last, was measured: fence + ticket +
+            // a lone CTA re-reading the rows cost 8 us on the decode step's critical path against 3-4 us here.)
+            if (p.norm_out) return launch_rms_norm(s, static_cast<const float*>(p.out), p.norm_w, p.norm_out, p.M, p.N, p.norm_eps);
+            return VB200_OK;
+        }
         case VB200_EPI_SWIGLU: return launch_epi<VB200_EPI_SWIGLU>(s, p);
         default: return set_detail(VB200_ERR_INVALID_ARG, "unknown linear epilogue");
     }

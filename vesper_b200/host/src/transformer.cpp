@@ -218,7 +218,8 @@ void TransformerLM::run_blocks(int64_t B, int64_t T, int64_t start_pos, bool dev
     for (size_t l = 0; l < layers_.size(); ++l) {
         Layer& L = *layers_[l];
         nn::KVCache& cache = *kv_caches_[l];
-        check(vb200_rms_norm(dev, s, b.h.data_ptr<float>(), L.attn_norm.data_ptr<float>(), b.xn.data_ptr<char>(), M, dim, config_.norm_eps), "rms_norm");
+        // on entry b.xn = attention_norm_l(h): written by the embedding call (l = 0) or by the previous
+        // block's down projection call, which ends with the next norm
         check(vb200_linear(dev, s, b.xn.data_ptr<char>(), dim, L.wqkv.data_ptr<char>(), dim, qkv, qkv_n, M, qkv_n, dim, VB200_EPI_BF16, 0), "linear(wqkv)");
         const vb200_tensor4 kc{cache.k().data_ptr<char>(), cache.k().strides()[0], cache.k().strides()[1], cache.k().strides()[2]};
         const vb200_tensor4 vc{cache.v().data_ptr<char>(), cache.v().strides()[0], cache.v().strides()[1], cache.v().strides()[2]};
@@ -259,10 +260,12 @@ void TransformerLM::run_blocks(int64_t B, int64_t T, int64_t start_pos, bool dev
             check(vb200_prefill_fwd(&a), "attention(prefill)");
         }
         if (!device_positions) cache.set_current_len(std::max(cache.current_seq_len(), static_cast<int>(start_pos + T)));
-        check(vb200_linear(dev, s, b.attn.data_ptr<char>(), Hq * D, L.wo.data_ptr<char>(), Hq * D, b.h.data_ptr<float>(), dim, M, dim, Hq * D, VB200_EPI_ADD_F32, 0), "linear(wo)");
-        check(vb200_rms_norm(dev, s, b.h.data_ptr<float>(), L.ffn_norm.data_ptr<float>(), b.xn.data_ptr<char>(), M, dim, config_.norm_eps), "rms_norm");
+        check(vb200_linear_add_rmsnorm(dev, s, b.attn.data_ptr<char>(), Hq * D, L.wo.data_ptr<char>(), Hq * D, b.h.data_ptr<float>(), M, dim, Hq * D,
+                                       L.ffn_norm.data_ptr<float>(), config_.norm_eps, b.xn.data_ptr<char>(), 0), "linear(wo) + ffn_norm");
         check(vb200_linear(dev, s, b.xn.data_ptr<char>(), dim, L.w13.data_ptr<char>(), dim, b.act.data_ptr<char>(), hid, M, 2 * hid, dim, VB200_EPI_SWIGLU, 0), "linear(gate,up)");
-        check(vb200_linear(dev, s, b.act.data_ptr<char>(), hid, L.w2.data_ptr<char>(), hid, b.h.data_ptr<float>(), dim, M, dim, hid, VB200_EPI_ADD_F32, 0), "linear(down)");
+        const float* next_norm = (l + 1 < layers_.size()) ? layers_[l + 1]->attn_norm.data_ptr<float>() : final_norm_.data_ptr<float>();
+        check(vb200_linear_add_rmsnorm(dev, s, b.act.data_ptr<char>(), hid, L.w2.data_ptr<char>(), hid, b.h.data_ptr<float>(), M, dim, hid,
+                                       next_norm, config_.norm_eps, b.xn.data_ptr<char>(), 0), "linear(down) + next norm");
     }
 }
 
@@ -281,11 +284,10 @@ Tensor TransformerLM::forward_with_cache(const Tensor& tokens, int64_t start_pos
     const int dim = static_cast<int>(config_.dim), vocab = static_cast<int>(config_.vocab_size);
     Tensor ids = tokens.is_contiguous() ? tokens : tokens.contiguous();
     if (ids.device() != Device::CUDA) ids = ids.to(Device::CUDA);
-    check(vb200_embedding(dev, s, ids.data_ptr<char>(), ids.dtype() == DType::Int64 ? 1 : 0, tok_emb_.data_ptr<char>(), b.h.data_ptr<float>(),
-                          static_cast<int>(B * T), dim, vocab), "embedding");
-    run_blocks(B, T, start_pos, false, nullptr, 0);
-    const int M = static_cast<int>(B * T);
-    check(vb200_rms_norm(dev, s, b.h.data_ptr<float>(), final_norm_.data_ptr<float>(), b.xn.data_ptr<char>(), M, dim, config_.norm_eps), "rms_norm");
+    const float* first_norm = layers_.empty() ? final_norm_.data_ptr<float>() : layers_[0]->attn_norm.data_ptr<float>();
+    check(vb200_embedding_rmsnorm(dev, s, ids.data_ptr<char>(), ids.dtype() == DType::Int64 ? 1 : 0, tok_emb_.data_ptr<char>(), b.h.data_ptr<float>(),
+                                  static_cast<int>(B * T), dim, vocab, first_norm, config_.norm_eps, b.xn.data_ptr<char>()), "embedding + norm");
+    run_blocks(B, T, start_pos, false, nullptr, 0);          // leaves final_norm(h) in b.xn
     const int64_t out_rows = last_only ? B : B * T;
     if (b.logit_rows < out_rows) {
         b.logits = empty({out_rows, config_.vocab_size}, DType::Float32, Device::CUDA);
@@ -336,9 +338,10 @@ void TransformerLM::decode_step(DecodeState& st) {
     void* s = current_stream();
     const int dev = b.h.device_index();
     const int dim = static_cast<int>(config_.dim), vocab = static_cast<int>(config_.vocab_size);
-    check(vb200_embedding(dev, s, st.ids.data_ptr<char>(), 0, tok_emb_.data_ptr<char>(), b.h.data_ptr<float>(), static_cast<int>(B), dim, vocab), "embedding");
-    run_blocks(B, 1, 0, true, st.lens.data_ptr<int32_t>(), st.max_len);
-    check(vb200_rms_norm(dev, s, b.h.data_ptr<float>(), final_norm_.data_ptr<float>(), b.xn.data_ptr<char>(), static_cast<int>(B), dim, config_.norm_eps), "rms_norm");
+    const float* first_norm = layers_.empty() ? final_norm_.data_ptr<float>() : layers_[0]->attn_norm.data_ptr<float>();
+    check(vb200_embedding_rmsnorm(dev, s, st.ids.data_ptr<char>(), 0, tok_emb_.data_ptr<char>(), b.h.data_ptr<float>(), static_cast<int>(B), dim, vocab,
+                                  first_norm, config_.norm_eps, b.xn.data_ptr<char>()), "embedding + norm");
+    run_blocks(B, 1, 0, true, st.lens.data_ptr<int32_t>(), st.max_len);      // leaves final_norm(h) in b.xn
     check(vb200_linear(dev, s, b.xn.data_ptr<char>(), dim, lm_head_.data_ptr<char>(), dim, b.logits.data_ptr<float>(), vocab, static_cast<int>(B), vocab, dim,
                        VB200_EPI_F32, 0), "linear(output)");
     pick_from_last_logits(st);
