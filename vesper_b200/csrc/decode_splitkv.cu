@@ -447,13 +447,17 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
     constexpr int CW = 4;
     constexpr int kStages = (NREP <= 4) ? 2 : 3;
     constexpr int MINB = (NREP <= 4) ? 3 : 2;
-#ifndef VB_DECODE_MMA_MIN_NREP
-#define VB_DECODE_MMA_MIN_NREP 4       // groups of at least this many heads use the warp-MMA split kernel
-#endif
-    if constexpr (NREP >= VB_DECODE_MMA_MIN_NREP && (NREP == 4 || NREP == 8)) {
-        // large groups are compute-bound on CUDA cores: their split kernel runs the products as warp MMAs
-        profile_mark_begin(s);
-        if (int rc = launch_decode_gqa_mma_split<T, NREP>(s, p)) return rc;
+    // Groups of 8 heads are compute-bound on CUDA cores and always take the warp-MMA split kernel; groups of 4
+    // take it when a CTA streams at least 256 keys (measured: 5.7 vs 5.3 TB/s on 1-8 K contexts) and the
+    // CUDA-core kernel below that, where its lighter prologue wins (3 us per call at 600-key contexts).
+    bool use_mma = false;
+    if constexpr (NREP == 8) use_mma = true;
+    if constexpr (NREP == 4) use_mma = p.chunk >= 256;
+    if (use_mma) {
+        if constexpr (NREP == 4 || NREP == 8) {
+            profile_mark_begin(s);
+            if (int rc = launch_decode_gqa_mma_split<T, NREP>(s, p)) return rc;
+        }
     } else {
         size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + D * sizeof(float) + D * sizeof(T) + 2 * CW * 16 * sizeof(float) + sizeof(DecodeSmem<CW, kStages>);
         static_assert(2 * CW * NREP * 128 * 4 + 2 * 2 * CW * NREP * 4 <= kStages * 2 * kTile * 128 * 2, "merge buffers must fit in the ring");
