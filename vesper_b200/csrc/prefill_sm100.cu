@@ -89,24 +89,49 @@ struct Cfg {
     static constexpr int kSmemBytes = (kQBufs + kStages) * kTileBytes + 1024 /*alignment slack*/ + 256 /*Barriers*/;
 };
 
-// One unit of work: two adjacent 128-row query tiles of one (batch, q_head).
+#ifndef VB_HEAD_PAIRS
+#define VB_HEAD_PAIRS 1        // pair the tiles of two heads of a group (equal work) instead of two row tiles of one head
+#endif
+
+// One unit of work: two 128-row query tiles that read the same K/V blocks.  With an even number of
+// query heads per KV head the two tiles are the SAME rows of two heads of one group: both visit the
+// same number of key blocks, so neither softmax warpgroup idles in the last iteration (adjacent row
+// tiles of one head differ by one block: 8 of 72 iterations per head wasted at S = 2048).  Otherwise
+// (one query head per KV head) they are two adjacent row tiles of one head.
 struct Item {
-    int b, hq, hkv;
+    int b, hq, hq1, hkv;   // hq / hq1: head of tile 0 / tile 1
     int r0[2];      // first query row of each tile
     int nblk[2];    // key blocks each tile visits (0: tile not present)
     int nmax;
 };
 
+__host__ __device__ __forceinline__ bool pair_by_heads(const PrefillParams& p) {
+    return VB_HEAD_PAIRS && ((p.Hq / p.Hkv) % 2 == 0);
+}
+// number of (batch, head or head pair) columns and of row steps of the item grid
+__host__ __device__ __forceinline__ int item_cols(const PrefillParams& p) { return pair_by_heads(p) ? p.B * (p.Hq / 2) : p.B * p.Hq; }
+__host__ __device__ __forceinline__ int item_rows(const PrefillParams& p) {
+    return pair_by_heads(p) ? (p.T + kBlockM - 1) / kBlockM : (p.T + 2 * kBlockM - 1) / (2 * kBlockM);
+}
+
 __device__ __forceinline__ Item get_item(const PrefillParams& p, int it, int n_bh, int n_pairs) {
     Item w;
-    const int pair = n_pairs - 1 - it / n_bh;      // heaviest (last) query pairs first
+    const int pair = n_pairs - 1 - it / n_bh;      // heaviest (last) query rows first
     const int bh = it % n_bh;
-    w.b = bh / p.Hq;
-    w.hq = bh % p.Hq;
+    const bool by_heads = pair_by_heads(p);
+    if (by_heads) {
+        w.b = bh / (p.Hq / 2);
+        w.hq = 2 * (bh % (p.Hq / 2));
+        w.hq1 = w.hq + 1;
+    } else {
+        w.b = bh / p.Hq;
+        w.hq = bh % p.Hq;
+        w.hq1 = w.hq;
+    }
     w.hkv = w.hq / (p.Hq / p.Hkv);
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
-        w.r0[t] = (2 * pair + t) * kBlockM;
+        w.r0[t] = by_heads ? pair * kBlockM : (2 * pair + t) * kBlockM;
         if (w.r0[t] >= p.T) { w.nblk[t] = 0; continue; }
         int kv_end = p.Skv;
         if (p.causal) kv_end = min(p.Skv, p.start_pos + min(w.r0[t] + kBlockM, p.T));
@@ -143,8 +168,8 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
     Barriers* bar = reinterpret_cast<Barriers*>(smem + (kQBufs + kStages) * C::kTileBytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_bh = p.B * p.Hq;
-    const int n_pairs = (p.T + 2 * kBlockM - 1) / (2 * kBlockM);
+    const int n_bh = item_cols(p);
+    const int n_pairs = item_rows(p);
     const int n_items = n_bh * n_pairs;
     const int n_rounds = (n_items + gridDim.x - 1) / gridDim.x;
     const bool rope = p.q_rope_table != nullptr;
@@ -194,7 +219,7 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                     mbar_arrive_expect_tx(&bar->q_full[b], C::kTileBytes);
 #pragma unroll
                     for (int h = 0; h < C::kHalves; ++h)
-                        tma_load_4d(q_smem + b * C::kTileBytes + h * C::kHalfBytes, &maps.q, &bar->q_full[b], h * 64, w.r0[t], w.hq, w.b);
+                        tma_load_4d(q_smem + b * C::kTileBytes + h * C::kHalfBytes, &maps.q, &bar->q_full[b], h * 64, w.r0[t], t ? w.hq1 : w.hq, w.b);
                 };
                 int round = 0;
                 int idx = -1;
@@ -556,7 +581,8 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
             if (!ok) break;
             tc_fence_after();
             const float inv_l = 1.0f / l_sum;
-            T* orow = static_cast<T*>(p.o.ptr) + w.b * p.o.sb + w.hq * p.o.sh + static_cast<long long>(row) * p.o.ss;
+            const int hq_t = t ? w.hq1 : w.hq;
+            T* orow = static_cast<T*>(p.o.ptr) + w.b * p.o.sb + hq_t * p.o.sh + static_cast<long long>(row) * p.o.ss;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t o[32];
@@ -578,7 +604,7 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
             // p_ready arrival) may overwrite it
             tc_fence_before();
             if (p.lse != nullptr && row < p.T)
-                p.lse[(static_cast<long long>(w.b) * p.Hq + w.hq) * p.T + row] = (m_ref + fast_log2(l_sum)) * kLn2;
+                p.lse[(static_cast<long long>(w.b) * p.Hq + hq_t) * p.T + row] = (m_ref + fast_log2(l_sum)) * kLn2;
 #ifdef VB_TIMING
             t_epi = clock64() - te0;
             if ((tid & 127) == 0) { VB_T(14 - 4 * t, t_wait); VB_T(15 - 4 * t, t_comp); if (t == 1) VB_T(9, t_epi); }
@@ -646,8 +672,7 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
         VB200_CUDA_TRY(cudaFuncSetAttribute(prefill_sm100_kernel<T, D, kExactRope>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
         configured_dev = dev;
     }
-    const int n_pairs = (p.T + 2 * kBlockM - 1) / (2 * kBlockM);
-    const int n_items = n_pairs * p.B * p.Hq;
+    const int n_items = item_rows(p) * item_cols(p);
     int sms = 0;
     VB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     // persistent: one CTA per SM walks the work items (heaviest first, round-robin)
