@@ -60,3 +60,17 @@ def test_decode_workspace_plan_is_consistent(lib):
     d.seq_lens = 0x1000
     d.num_splits = 1
     assert lib.vb200_decode_workspace_bytes(C.byref(d)) < n
+
+
+def test_host_layer_facade_exports(lib):
+    """libvesper_b200_host.so (models::TransformerLM / generation::Generator behind a C facade) loads without
+    a GPU and exports what vesper_b200/model.py binds."""
+    from vesper_b200 import model
+    from vesper_b200.build import build_host
+    build_host()
+    L = model.load_host()
+    for n in model.HOST_EXPORTS:
+        assert hasattr(L, n), n
+    shapes = model.param_shapes(32000, 2048, 24, 16, 4, 5632)
+    assert shapes["layers.23.attention.wqkv.weight"] == (3072, 2048) and shapes["output.weight"] == (32000, 2048)
+    assert sum(int(np.prod(s)) for s in shapes.values()) == 1213302784          # the C5 decoder
