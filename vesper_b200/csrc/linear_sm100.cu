@@ -130,7 +130,7 @@ __device__ __forceinline__ void store_row32(const LinearParams& p, int row, int 
 // ------------------------------------------------------------------------------------------------
 template <int BN>
 struct WideCfg {
-    static constexpr int kStages = 4;
+    static constexpr int kStages = 6;
     static constexpr int kBBytes = BN * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarOffset = kStages * kStageBytes;
