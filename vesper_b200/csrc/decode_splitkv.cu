@@ -458,7 +458,7 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
             profile_mark_begin(s);
             if (int rc = launch_decode_gqa_mma_split<T, NREP>(s, p)) return rc;
         }
-    } else {
+    } else if constexpr (NREP != 8) {       // (the CUDA-core kernel is never the choice for 8-head groups)
         size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + D * sizeof(float) + D * sizeof(T) + 2 * CW * 16 * sizeof(float) + sizeof(DecodeSmem<CW, kStages>);
         static_assert(2 * CW * NREP * 128 * 4 + 2 * 2 * CW * NREP * 4 <= kStages * 2 * kTile * 128 * 2, "merge buffers must fit in the ring");
         static thread_local int configured_dev = -1;

@@ -51,7 +51,6 @@ struct TransformerLM::Buffers {
     Tensor attn;       // [rows, Hq * D] bf16, heads merged
     Tensor act;        // [rows, hidden] bf16
     Tensor logits;     // [logit_rows, vocab] fp32
-    Tensor ids;        // [rows] int32 staging for host token ids
     Tensor attn_ws;    // attention workspace (angle table / split-KV partials)
     int64_t logit_rows = 0;
 };
@@ -178,7 +177,6 @@ void TransformerLM::ensure_buffers(int64_t rows, int64_t batch) {
     b.qkv = empty({rows, qkv_n}, DType::BFloat16, Device::CUDA);
     b.attn = empty({rows, config_.n_heads * D}, DType::BFloat16, Device::CUDA);
     b.act = empty({rows, hid}, DType::BFloat16, Device::CUDA);
-    b.ids = empty({rows}, DType::Int32, Device::CUDA);
     // attention workspace: the larger of the prompt pass's angle table and the split-KV partials of a
     // decode step planned for the longest sequence the cache can hold
     vb200_prefill_args pa{};
