@@ -43,6 +43,13 @@ typedef enum vb200_epilogue {
 int vb200_linear(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
                  void* out, int64_t ldo, int32_t M, int32_t N, int32_t K, int32_t epilogue, int32_t splits);
 
+/* y = x W^T + bias: vb200_linear with nn::Linear's optional bias (fp32 [N], src/nn/linear.cpp:26-35,44-46)
+ * added to every output row before the epilogue's own step (for VB200_EPI_SWIGLU the bias has the
+ * interleaved gate / up layout of the weight rows).  bias == NULL is vb200_linear. */
+int vb200_linear_bias(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                      const float* bias, void* out, int64_t ldo, int32_t M, int32_t N, int32_t K,
+                      int32_t epilogue, int32_t splits);
+
 /* h += x W^T followed by the RMSNorm of the finished rows, xn = rmsnorm(h) * norm_weight (bf16) -- the
  * output projection / down projection of a block, its residual add, and the NEXT norm in the block
  * sequence (src/models/transformer_block.cpp:183-205) as one call (two launches chained by

@@ -15,6 +15,8 @@
 #include <vesper/ops/flash_attention.h>
 #include <vesper/generation/generator.h>
 #include <vesper/models/transformer.h>
+#include <vesper/nn/linear.h>
+#include "../../oracle/vesper_block_oracle.h"
 
 #include "../../oracle/vesper_attn_oracle.h"
 
@@ -239,6 +241,46 @@ static void test_flash_backward() {             // tests/test_flash_attention.cp
     CHECK(allclose(gq, dq, 1e-3f, 1e-4f) && allclose(gk, dk, 1e-3f, 1e-4f) && allclose(gv, dv, 1e-3f, 1e-4f));
 }
 
+static void test_modules() {                    // nn::Linear (bias), FusedQKVLinear views, RMSNorm, SwiGLUMLP vs the CPU oracle
+    const int M = 6, in_f = 256, out_f = 384, hid = 320;
+    auto x = round_like(randn(static_cast<size_t>(M) * in_f, 51), DType::BFloat16);
+    auto w = round_like(randn(static_cast<size_t>(out_f) * in_f, 52, 0.06f), DType::BFloat16);
+    auto b = randn(out_f, 53);
+    std::vector<float> y(static_cast<size_t>(M) * out_f);
+    vo_linear(x.data(), w.data(), y.data(), M, out_f, in_f);
+    for (int m = 0; m < M; ++m) for (int n = 0; n < out_f; ++n) y[static_cast<size_t>(m) * out_f + n] += b[n];
+    nn::Linear lin(in_f, out_f, true);
+    lin.load_weight(w.data(), b.data());
+    Tensor tx = to_cuda(x, {2, 3, in_f}, DType::BFloat16);
+    Tensor ty = lin.forward(tx);
+    CHECK(ty.shape() == (std::vector<int64_t>{2, 3, out_f}));
+    CHECK(allclose(to_host(ty), y, 1.0f / 128, 2e-3f));
+    nn::FusedQKVLinear qkv(in_f, 256, 64, false);
+    qkv.load_weight(w.data());                                   // 256 + 2 * 64 = 384 rows
+    auto parts = qkv.forward_split(tx);
+    CHECK(std::get<0>(parts).shape().back() == 256 && std::get<1>(parts).shape().back() == 64 && std::get<2>(parts).shape().back() == 64);
+    CHECK(std::get<1>(parts).strides()[1] == 384);               // views of the fused output, not copies
+    auto h = randn(static_cast<size_t>(M) * in_f, 54, 3.0f);
+    auto g = randn(in_f, 55, 0.1f);
+    for (auto& v : g) v += 1.0f;
+    std::vector<float> hn(h.size());
+    vo_rms_norm(h.data(), g.data(), hn.data(), M, in_f, 1e-6f);
+    nn::RMSNorm norm({in_f}, 1e-6f);
+    norm.load_weight(g.data());
+    CHECK(allclose(to_host(norm.forward(to_cuda(h, {M, in_f}))), hn, 1.0f / 128, 1e-5f));
+    auto wg = round_like(randn(static_cast<size_t>(hid) * in_f, 56, 0.06f), DType::BFloat16), wu = round_like(randn(static_cast<size_t>(hid) * in_f, 57, 0.06f), DType::BFloat16);
+    auto wd = round_like(randn(static_cast<size_t>(in_f) * hid, 58, 0.06f), DType::BFloat16);
+    std::vector<float> a(static_cast<size_t>(M) * hid), u(a.size()), act(a.size()), out(static_cast<size_t>(M) * in_f);
+    vo_linear(x.data(), wg.data(), a.data(), M, hid, in_f);
+    vo_linear(x.data(), wu.data(), u.data(), M, hid, in_f);
+    vo_silu_mul(a.data(), u.data(), act.data(), static_cast<int64_t>(act.size()));
+    vo_linear(act.data(), wd.data(), out.data(), M, in_f, hid);
+    nn::SwiGLUMLP mlp(in_f, hid);
+    mlp.load_weights(wg.data(), wu.data(), wd.data());
+    CHECK(allclose(to_host(mlp.forward(tx)), out, 2.0f / 128, 3e-3f));
+    CHECK(nn::SwiGLUMLP::compute_hidden_dim(2048) == 5632);      // src/nn/swiglu.cpp:50-61
+}
+
 static void test_model_generate() {             // cached decode == full forward; greedy loop shape and determinism
     models::TransformerConfig c;
     c.vocab_size = 128; c.dim = 256; c.n_layers = 2; c.n_heads = 2; c.n_kv_heads = 1; c.ffn_hidden_dim = 320; c.max_seq_len = 32;
@@ -306,6 +348,7 @@ int main() {
     test_sdpa_routes();
     std::printf("flash backward / model / generator\n");
     test_flash_backward();
+    test_modules();
     test_model_generate();
     std::printf("All B200 host-layer tests passed\n");
     return 0;

@@ -241,3 +241,31 @@ def test_embedding_rmsnorm(cuda, oracle):
     assert np.array_equal(from_torch(out), want)
     wn = oracle.rms_norm(want, g, 1e-6)
     assert np.all(np.abs(from_torch(xn) - wn) <= 2.0 ** -8 * np.abs(wn) + 1e-6)
+
+
+@pytest.mark.parametrize("M", [8, 200])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+def test_linear_with_bias(cuda, oracle, M, epilogue):
+    """nn::Linear with bias (src/nn/linear.cpp:44-46): y = x W^T + b before the epilogue's own step."""
+    import torch
+    from vesper_b200 import capi
+    N, K = 384, 256
+    rng = np.random.default_rng(77 + M + epilogue)
+    x = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    w = bf16_round((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32))
+    b = rng.standard_normal(N).astype(np.float32)
+    want = oracle.linear(x, w) + b[None, :]
+    if epilogue == capi.EPI_BF16:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=cuda)
+    elif epilogue == capi.EPI_SWIGLU:
+        out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=cuda)
+        want = oracle.silu_mul(want[:, 0::2].copy(), want[:, 1::2].copy())
+    else:
+        h0 = rng.standard_normal((M, N)).astype(np.float32)
+        out = to_torch(h0, torch.float32, cuda)
+        if epilogue == capi.EPI_ADD_F32:
+            want = h0 + want
+    capi.linear(to_torch(x, torch.bfloat16, cuda), to_torch(w, torch.bfloat16, cuda), out, epilogue=epilogue, bias=to_torch(b, torch.float32, cuda))
+    torch.cuda.synchronize()
+    tol = 2.0 ** -8 * np.abs(want) + 2e-3 if epilogue in (capi.EPI_BF16, capi.EPI_SWIGLU) else 1e-3 * (1.0 + np.abs(want))
+    assert np.all(np.abs(from_torch(out) - want) <= tol)

@@ -58,7 +58,7 @@ EXPORTS = [
     "vb200_reset_launch_count", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
 ]
 BLOCK_EXPORTS = [
-    "vb200_linear", "vb200_linear_add_rmsnorm", "vb200_embedding_rmsnorm", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
+    "vb200_linear", "vb200_linear_bias", "vb200_linear_add_rmsnorm", "vb200_embedding_rmsnorm", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
 ]
 
 
@@ -138,6 +138,7 @@ def load():
     L.vb200_exchange_combine.argtypes = [C.POINTER(ExchangeArgs)]
     # decoder-block operators (include/vesper_b200_block.h)
     L.vb200_linear.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64] + [C.c_int32] * 5
+    L.vb200_linear_bias.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64] + [C.c_int32] * 5
     L.vb200_linear_add_rmsnorm.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                            C.c_void_p, C.c_float, C.c_void_p, C.c_int32]
     L.vb200_embedding_rmsnorm.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
@@ -340,12 +341,12 @@ def exchange_combine(partial, peer_ptrs, rank, out, lse=None, *, step=0, timeout
 
 
 # ---- decoder-block operators ---------------------------------------------------------------
-def linear(x, w, out, epilogue=EPI_BF16, splits=0, stream=None):
-    """out = epilogue(x @ w.T): x [M,K] bf16, w [N,K] bf16 (row strides honoured)."""
+def linear(x, w, out, epilogue=EPI_BF16, splits=0, stream=None, bias=None):
+    """out = epilogue(x @ w.T [+ bias]): x [M,K] bf16, w [N,K] bf16 (row strides honoured), bias fp32 [N]."""
     M, K = x.shape
     N = w.shape[0]
-    check(load().vb200_linear(x.device.index or 0, _stream_ptr(stream), _ptr(x), x.stride(0), _ptr(w), w.stride(0),
-                              _ptr(out), out.stride(0), M, N, K, epilogue, splits))
+    check(load().vb200_linear_bias(x.device.index or 0, _stream_ptr(stream), _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias),
+                                   _ptr(out), out.stride(0), M, N, K, epilogue, splits))
     return out
 
 

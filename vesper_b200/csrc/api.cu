@@ -483,8 +483,9 @@ int vb200_exchange_combine(const vb200_exchange_args* a) {
 
 static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
-int vb200_linear(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
-                 void* out, int64_t ldo, int32_t M, int32_t N, int32_t K, int32_t epilogue, int32_t splits) {
+int vb200_linear_bias(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                      const float* bias, void* out, int64_t ldo, int32_t M, int32_t N, int32_t K,
+                      int32_t epilogue, int32_t splits) {
     if (!x || !w || !out || M <= 0 || N <= 0 || K <= 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear: null pointer or non-positive size");
     if (epilogue < VB200_EPI_BF16 || epilogue > VB200_EPI_SWIGLU) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear: unknown epilogue");
     if (ldx < K || ldw < K) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear: ldx and ldw must be >= K");
@@ -499,9 +500,15 @@ int vb200_linear(int device, void* stream, const void* x, int64_t ldx, const voi
     LinearParams p{};
     p.x = x; p.ldx = ldx; p.w = w; p.ldw = ldw; p.out = out; p.ldo = ldo;
     p.M = M; p.N = N; p.K = K; p.epilogue = epilogue; p.splits = splits;
+    p.bias = bias;
     p.status = kernel_status_word();
     if (!p.status) return VB200_ERR_CUDA;
     return launch_linear(static_cast<cudaStream_t>(stream), p);
+}
+
+int vb200_linear(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                 void* out, int64_t ldo, int32_t M, int32_t N, int32_t K, int32_t epilogue, int32_t splits) {
+    return vb200_linear_bias(device, stream, x, ldx, w, ldw, nullptr, out, ldo, M, N, K, epilogue, splits);
 }
 
 int vb200_linear_add_rmsnorm(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,

@@ -116,6 +116,7 @@ struct LinearParams {
     int epilogue;                    // vb200_epilogue
     int splits;                      // K slices per cluster of the skinny kernel, 0 = choose
     int* status;                     // device status word (bounded waits)
+    const float* bias;               // [N] fp32 added to every output row before the epilogue's own step, or null
     // optional, with the += epilogue: RMSNorm of the finished rows, out_norm[m,:] = out[m,:] * inv_rms * norm_w
     const float* norm_w;             // [N]
     void* norm_out;                  // [M, N] bf16, row stride norm_ld; null = no fused norm

@@ -60,7 +60,12 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)
 
 // One output element group of the wide kernel: 32 consecutive columns of one row.
 template <int EPI>
-__device__ __forceinline__ void store_row32(const LinearParams& p, int row, int col0, const uint32_t (&acc)[32]) {
+__device__ __forceinline__ void store_row32(const LinearParams& p, int row, int col0, uint32_t (&acc)[32]) {
+    if (p.bias != nullptr) {                     // nn::Linear's bias (src/nn/linear.cpp:44-46)
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __ldg(p.bias + col0 + j));
+    }
     if (EPI == VB200_EPI_SWIGLU) {
         // columns (2j, 2j+1) = (gate_j, up_j) -> out[row, col0/2 + j]
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo + (col0 >> 1);
@@ -130,7 +135,7 @@ __device__ __forceinline__ void store_row32(const LinearParams& p, int row, int 
 // ------------------------------------------------------------------------------------------------
 template <int BN>
 struct WideCfg {
-    static constexpr int kStages = 6;
+    static constexpr int kStages = 4;
     static constexpr int kBBytes = BN * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarOffset = kStages * kStageBytes;
@@ -408,6 +413,11 @@ linear_skinny_kernel(const __grid_constant__ LinearMaps maps, LinearParams p, in
     if (warp >= 2 && rank == 0) {
         const int n = nt * kTileA + (warp & 3) * 32 + lane;
         const int m_count = min(p.M, MT);
+        if (p.bias != nullptr && n < p.N) {
+            const float bv = __ldg(p.bias + n);
+#pragma unroll
+            for (int j = 0; j < MT; ++j) acc[j] += bv;
+        }
         if (EPI == VB200_EPI_SWIGLU) {
             __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
 #pragma unroll

@@ -4,8 +4,9 @@ The KV sequence of each (batch, kv_head) is split into ``world`` contiguous
 shards, shard r living on GPU r.  One decode step is
 
     local split-KV decode  ->  partial (O/l, m, l) per query head   [vb200_decode_fwd, partial_out]
-    all-gather of the partials (Hq*(D+2) floats per rank)           [NCCL via torch.distributed]
-    log-sum-exp combine, identical on every rank                    [vb200_lse_combine]
+    exchange of the partials (Hq*(D+2) floats per rank) and log-sum-exp merge, identical on every rank:
+      either ONE kernel over NVLink peer memory                     [vb200_exchange_combine, PeerExchange]
+      or an all-gather followed by the merge                        [NCCL via torch.distributed, vb200_lse_combine]
 
 There is no other exchange on the attention path; prefill and batched decode
 partition by (batch x kv_head) with no collective at all (``unit_range``).
@@ -140,6 +141,11 @@ def cuda_step(step: ShardedDecodeStep, q, k_shard, v_shard, *, scale, theta, par
     B, Hq, _, D = q.shape
     if qpos is None:
         qpos = torch.full((B,), step.context_len, dtype=torch.int32, device=q.device)
+    if step.world == 1 and exchange is None:
+        # one shard: nothing to exchange or merge, the decode call writes the result itself
+        capi.decode(q, out.view(B, Hq, 1, D), k_shard, v_shard, scale=scale, theta=theta, uniform_len=end - begin, max_len=end - begin,
+                    pos_offset=begin, q_positions=qpos, lse=lse, workspace=workspace, stream=stream)
+        return out
     capi.decode(q, None, k_shard, v_shard, scale=scale, theta=theta, uniform_len=end - begin, max_len=end - begin,
                 pos_offset=begin, q_positions=qpos, partial_out=partial_buf, workspace=workspace, stream=stream)
     if exchange is not None:
