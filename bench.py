@@ -108,7 +108,7 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------
 # CPU arm: the reference's own CPU attention on a bounded sample, all host threads
 # ----------------------------------------------------------------------------------------------
-def cpu_prefill_sample(target_seconds=12.0, threads=None):
+def cpu_prefill_sample(target_seconds=12.0, threads=None, S=None, total_slices=None, what="the headline prefill"):
     """Time flash_attention_cpu_dispatch (src/ops/flash_attention.cpp:218-364) on (batch, head)
     slices of the headline workload (S=2048, D=128, causal; RoPE applied to the slice first with
     the reference's functions), independent slices on `threads` host threads.  Returns TFLOP/s."""
@@ -117,7 +117,8 @@ def cpu_prefill_sample(target_seconds=12.0, threads=None):
     kind = "reference" if ref_available() else "port"
     eng = Ref() if kind == "reference" else Oracle()
     threads = threads or max(1, min(os.cpu_count() or 1, 64))
-    S, D = C2["S"], C2["D"]
+    S, D = S or C2["S"], C2["D"]
+    total_slices = total_slices or C2["B"] * C2["Hq"]
     rng = np.random.default_rng(1)
     q = (0.5 * rng.standard_normal((1, 1, S, D))).astype(np.float32)
     k = (0.5 * rng.standard_normal((1, 1, S, D))).astype(np.float32)
@@ -147,7 +148,7 @@ def cpu_prefill_sample(target_seconds=12.0, threads=None):
     slices = sum(done)
     flops = slices * 4.0 * D * S * (S + 1) / 2.0
     return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=threads, kind=kind,
-                sample=f"{slices} of {C2['B'] * C2['Hq']} (batch, head) slices of the headline prefill (S={S}, D={D}, fp32, RoPE + causal flash), "
+                sample=f"{slices} of {total_slices} (batch, head) slices of {what} (S={S}, D={D}, fp32, RoPE + causal flash), "
                        f"{threads} host threads x {per_thread} slices, {dt:.1f} s; single-thread slice {t_one * 1e3:.0f} ms"), dt
 
 
@@ -570,6 +571,12 @@ def bench_model(cx, reps=3, layers=None, new=None):
     pre = cx.max_over_ranks(float(np.median(pre_ms)))
     dec = cx.max_over_ranks(float(np.median(dec_ms)))
     wall = cx.max_over_ranks(float(np.median(wall_ms)))
+    cpu_attn = None
+    if cx.rank == 0 and cx.world == 1 and not layers:
+        # the reference's CPU attention for ONE layer of the prompt pass (128 (batch, head) slices of S = 512), all host threads
+        cb, _ = cpu_prefill_sample(target_seconds=2.0, S=c["P"], total_slices=c["B"] * c["Hq"], what="one layer of the model's prompt pass")
+        layer_flops = 4.0 * c["B"] * c["Hq"] * 128 * c["P"] * (c["P"] + 1) / 2.0
+        cpu_attn = dict(cb, ms_per_layer_prompt_attention=layer_flops / (cb["value"] * 1e12) * 1e3)
     new_tokens = c["B"] * c["new"] * cx.world
     weight_bytes = 2.0 * (n_params - c["vocab"] * c["dim"])          # bf16; the embedding table is gathered, not streamed
     m.close()
@@ -580,6 +587,7 @@ def bench_model(cx, reps=3, layers=None, new=None):
         "attention_time_share": attn_ms / (tp["prefill_ms"] + tp["decode_ms"]),
         "attention_kernel_ms": attn_ms, "attention_kernel_launches": int(attn_launches),
         "graph_replay": True, "launches_recorded_outside_graph": launches, "scaling": "weak",
+        "cpu_baseline_attention": cpu_attn,
         "e2e": {"value": new_tokens / (wall * 1e-3), "unit": "tokens/s", "ms": wall,
                 "h2d_bytes_per_step": int(prompt.nbytes), "d2h_bytes_per_step": int(toks.nbytes)},
         "roofline": {"bound": "hbm", "what": "decode step: bf16 weights streamed once per step",
