@@ -583,6 +583,38 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
             const float inv_l = 1.0f / l_sum;
             const int hq_t = t ? w.hq1 : w.hq;
             T* orow = static_cast<T*>(p.o.ptr) + w.b * p.o.sb + hq_t * p.o.sh + static_cast<long long>(row) * p.o.ss;
+#ifndef VB_EPI_WIDE
+#define VB_EPI_WIDE 1          // 1: several TMEM loads in flight per wait and 32-byte global stores in the epilogue (3 % faster at S = 2048)
+#endif
+#ifndef VB_EPI_BATCH
+#define VB_EPI_BATCH 2         // TMEM loads (32 columns each) per wait
+#endif
+#if VB_EPI_WIDE
+#pragma unroll
+            for (int c = 0; c < D / 32; c += VB_EPI_BATCH) {
+                uint32_t o[VB_EPI_BATCH][32];
+#pragma unroll
+                for (int h2 = 0; h2 < VB_EPI_BATCH; ++h2)
+                    if (c + h2 < D / 32) tmem_ld32(o_addr + (c + h2) * 32, o[h2]);
+                tmem_ld_wait();
+                if (row < p.T) {
+#pragma unroll
+                    for (int h2 = 0; h2 < VB_EPI_BATCH; ++h2) {
+                        if (c + h2 >= D / 32) break;
+#pragma unroll
+                        for (int v = 0; v < 2; ++v) {
+                            uint32_t w8[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                w8[e] = Elem<T>::pack2(__uint_as_float(o[h2][16 * v + 2 * e]) * inv_l, __uint_as_float(o[h2][16 * v + 2 * e + 1]) * inv_l);
+                            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                         ::"l"(orow + (c + h2) * 32 + v * 16), "r"(w8[0]), "r"(w8[1]), "r"(w8[2]), "r"(w8[3]), "r"(w8[4]), "r"(w8[5]),
+                                           "r"(w8[6]), "r"(w8[7]) : "memory");
+                        }
+                    }
+                }
+            }
+#else
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t o[32];
@@ -600,6 +632,7 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                     }
                 }
             }
+#endif
             // O has been read out: the next item's first PV (issued only after this thread's next
             // p_ready arrival) may overwrite it
             tc_fence_before();
