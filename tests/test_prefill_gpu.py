@@ -231,3 +231,23 @@ def test_prefill_chunk_at_far_position(lib, cuda, oracle):
     assert maxabs(from_torch(lse), want_lse) <= 2e-3     # scores of |s| ~ 10 with K rounded to bf16 in the cache
     gk = from_torch(kc)
     assert np.all(np.abs(gk[:, :, P:P + T] - okc[:, :, P:P + T]) <= 2.0 ** -8 * np.abs(okc[:, :, P:P + T]) + 1e-6)
+
+
+def test_output_rows_aligned_to_16_but_not_32_bytes(cuda, oracle):
+    """O with a row stride of 136 elements (272 bytes): every other row starts 16 bytes off a 32-byte
+    boundary, which the 32-byte stores of the epilogue must not be used for."""
+    import torch
+    from vesper_b200 import capi
+    B, H, S, D = 1, 2, 200, 128
+    rng = np.random.default_rng(9)
+    q, k, v = [bf16_round(0.5 * rng.standard_normal((B, H, S, D)).astype(np.float32)) for _ in range(3)]
+    scale = float(1.0 / np.sqrt(D))
+    want, want_lse = oracle.flash_attention(q, k, v, scale, True)
+    buf = torch.zeros(B, H, S, 136, dtype=torch.bfloat16, device=cuda)
+    o = buf[..., :D]
+    lse = torch.empty(B, H, S, dtype=torch.float32, device=cuda)
+    capi.prefill(to_torch(q, torch.bfloat16, cuda), to_torch(k, torch.bfloat16, cuda), to_torch(v, torch.bfloat16, cuda), o, lse, scale=scale, causal=True)
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)
+    assert maxabs(from_torch(o), want) <= 1e-2 and maxabs(from_torch(lse), want_lse) <= 1e-3
+    assert bool((buf[..., D:] == 0).all())

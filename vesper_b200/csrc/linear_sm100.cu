@@ -56,6 +56,28 @@ __device__ __forceinline__ void abort_linger(volatile int* abort_flag) {
     }
     __syncthreads();
 }
+// 32-byte global accesses (sm_100): half as many store instructions per row segment as 16-byte ones.  The
+// interface promises 16-byte alignment only, so a segment that is not 32-byte aligned goes as two halves.
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) {
+    if ((reinterpret_cast<uintptr_t>(ptr) & 31) == 0) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+    } else {
+        uint4* p4 = static_cast<uint4*>(ptr);
+        p4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        p4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+}
+__device__ __forceinline__ void ld_global_v8(const void* ptr, uint32_t (&w)[8]) {
+    if ((reinterpret_cast<uintptr_t>(ptr) & 31) == 0) {
+        asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(ptr) : "memory");
+    } else {
+        const uint4* p4 = static_cast<const uint4*>(ptr);
+        const uint4 a = p4[0], b = p4[1];
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    }
+}
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
 // One output element group of the wide kernel: 32 consecutive columns of one row.
@@ -78,9 +100,7 @@ __device__ __forceinline__ void store_row32(const LinearParams& p, int row, int 
             packed[j] = Elem<__nv_bfloat16>::pack2(a0, a1);
         }
         if (n_out == 16) {
-            uint4* o4 = reinterpret_cast<uint4*>(out);
-            o4[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            o4[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            st_global_v8(out, packed);
         } else {
             for (int j = 0; j < n_out; ++j) {
                 const uint32_t u = packed[j >> 1];
@@ -93,15 +113,12 @@ __device__ __forceinline__ void store_row32(const LinearParams& p, int row, int 
     if (EPI == VB200_EPI_BF16) {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo + col0;
         if (n_valid == 32) {
-            uint4* o4 = reinterpret_cast<uint4*>(out);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint4 v;
-                v.x = Elem<__nv_bfloat16>::pack2(__uint_as_float(acc[8 * j + 0]), __uint_as_float(acc[8 * j + 1]));
-                v.y = Elem<__nv_bfloat16>::pack2(__uint_as_float(acc[8 * j + 2]), __uint_as_float(acc[8 * j + 3]));
-                v.z = Elem<__nv_bfloat16>::pack2(__uint_as_float(acc[8 * j + 4]), __uint_as_float(acc[8 * j + 5]));
-                v.w = Elem<__nv_bfloat16>::pack2(__uint_as_float(acc[8 * j + 6]), __uint_as_float(acc[8 * j + 7]));
-                o4[j] = v;
+            for (int j = 0; j < 2; ++j) {
+                uint32_t w8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) w8[e] = Elem<__nv_bfloat16>::pack2(__uint_as_float(acc[16 * j + 2 * e]), __uint_as_float(acc[16 * j + 2 * e + 1]));
+                st_global_v8(out + 16 * j, w8);
             }
         } else {
             for (int j = 0; j < n_valid; ++j) out[j] = __float2bfloat16_rn(__uint_as_float(acc[j]));
@@ -109,16 +126,21 @@ __device__ __forceinline__ void store_row32(const LinearParams& p, int row, int 
     } else {
         float* out = static_cast<float*>(p.out) + static_cast<long long>(row) * p.ldo + col0;
         if (n_valid == 32) {
-            float4* o4 = reinterpret_cast<float4*>(out);
+            uint32_t hres[4][8];
+            if (EPI == VB200_EPI_ADD_F32) {                     // all four 32-byte loads of the residual in flight at once
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float4 v = make_float4(__uint_as_float(acc[4 * j]), __uint_as_float(acc[4 * j + 1]),
-                                       __uint_as_float(acc[4 * j + 2]), __uint_as_float(acc[4 * j + 3]));
-                if (EPI == VB200_EPI_ADD_F32) {
-                    const float4 h = o4[j];
-                    v.x += h.x; v.y += h.y; v.z += h.z; v.w += h.w;
+                for (int j = 0; j < 4; ++j) ld_global_v8(out + 8 * j, hres[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t w8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float v = __uint_as_float(acc[8 * j + e]);
+                    if (EPI == VB200_EPI_ADD_F32) v += __uint_as_float(hres[j][e]);
+                    w8[e] = __float_as_uint(v);
                 }
-                o4[j] = v;
+                st_global_v8(out + 8 * j, w8);
             }
         } else {
             for (int j = 0; j < n_valid; ++j) {

@@ -590,6 +590,7 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
 #define VB_EPI_BATCH 2         // TMEM loads (32 columns each) per wait
 #endif
 #if VB_EPI_WIDE
+            const bool o32 = (reinterpret_cast<uintptr_t>(orow) & 31) == 0;     // every segment offset below is a multiple of 32 bytes
 #pragma unroll
             for (int c = 0; c < D / 32; c += VB_EPI_BATCH) {
                 uint32_t o[VB_EPI_BATCH][32];
@@ -607,9 +608,15 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
 #pragma unroll
                             for (int e = 0; e < 8; ++e)
                                 w8[e] = Elem<T>::pack2(__uint_as_float(o[h2][16 * v + 2 * e]) * inv_l, __uint_as_float(o[h2][16 * v + 2 * e + 1]) * inv_l);
-                            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                                         ::"l"(orow + (c + h2) * 32 + v * 16), "r"(w8[0]), "r"(w8[1]), "r"(w8[2]), "r"(w8[3]), "r"(w8[4]), "r"(w8[5]),
-                                           "r"(w8[6]), "r"(w8[7]) : "memory");
+                            if (o32) {
+                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                             ::"l"(orow + (c + h2) * 32 + v * 16), "r"(w8[0]), "r"(w8[1]), "r"(w8[2]), "r"(w8[3]), "r"(w8[4]), "r"(w8[5]),
+                                               "r"(w8[6]), "r"(w8[7]) : "memory");
+                            } else {                     // the interface promises 16-byte alignment only
+                                uint4* o4 = reinterpret_cast<uint4*>(orow + (c + h2) * 32 + v * 16);
+                                o4[0] = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+                                o4[1] = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+                            }
                         }
                     }
                 }
