@@ -36,15 +36,18 @@ def maxabs(a, b):
 
 
 # ---- decoder model: seeded weights and the oracle composition -------------------------------
-def model_weights(shapes, seed, std=0.02):
+def model_weights(shapes, seed, std=0.02, single=False):
     """N(0, std) matrices and (1 + 0.1 N(0,1)) norm weights, seeded per parameter name order;
-    matrices are rounded to bf16 so the GPU (bf16 storage) and the CPU checkers see the same values."""
+    matrices are rounded to bf16 so the GPU (bf16 storage) and the CPU checkers see the same values.
+    single=True draws in float32 (a different, faster stream: for large models without fixtures)."""
     rng = np.random.default_rng(seed)
     out = {}
     for name in sorted(shapes):
         shape = shapes[name]
         if len(shape) == 1:
             out[name] = (1.0 + 0.1 * rng.standard_normal(shape)).astype(np.float32)
+        elif single:
+            out[name] = bf16_round(np.float32(std) * rng.standard_normal(shape, dtype=np.float32))
         else:
             out[name] = bf16_round((std * rng.standard_normal(shape)).astype(np.float32))
     return out

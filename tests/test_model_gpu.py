@@ -107,3 +107,29 @@ def test_model_argument_errors(cuda):
         m.set_param("layers.0.bogus", np.zeros(4, np.float32))
     with pytest.raises(RuntimeError, match="max_seq_len"):
         m.generate_greedy(np.zeros((1, 10), np.int32), 10)
+
+
+def test_full_width_single_layer(cuda, oracle):
+    """One layer at the full width of the 24-layer benchmark model (d_model 2048, 16 query / 4 KV heads of 128,
+    SwiGLU 5632, vocab 32000, weights N(0, 0.02) rounded to bf16): prompt pass of 2 x 40 tokens through the tiled
+    GEMM, then two single-token steps through the weight-streaming GEMM and the split-KV decode kernel, against the
+    oracle composition on the same values."""
+    from vesper_b200.model import TransformerLM
+    vocab, dim, Hq, Hkv, ffn = 32000, 2048, 16, 4, 5632
+    w = model_weights(param_shapes(vocab, dim, 1, Hq, Hkv, ffn), 7, std=0.02, single=True)
+    m = TransformerLM(vocab, dim, 1, Hq, Hkv, ffn, 64)
+    for k, v in w.items():
+        m.set_param(k, v)
+    d = OracleDecoder(oracle, w, n_layers=1, n_heads=Hq, n_kv_heads=Hkv, max_seq_len=64)
+    ids = np.random.default_rng(8).integers(0, vocab, size=(2, 42)).astype(np.int32)
+    m.init_cache(2)
+    d.init_cache(2)
+    got = m.forward_with_cache(ids[:, :40], 0, last_only=True)[:, 0]
+    want = d.forward_with_cache(ids[:, :40], 0)[:, -1]
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= LOGIT_TOL * scale
+    for t in (40, 41):
+        got = m.forward_with_cache(ids[:, t:t + 1], t)[:, 0]
+        want = d.forward_with_cache(ids[:, t:t + 1], t)[:, 0]
+        assert np.abs(got - want).max() <= LOGIT_TOL * scale, t
+    m.close()
