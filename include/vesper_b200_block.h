@@ -50,6 +50,40 @@ int vb200_linear_bias(int device, void* stream, const void* x, int64_t ldx, cons
                       const float* bias, void* out, int64_t ldo, int32_t M, int32_t N, int32_t K,
                       int32_t epilogue, int32_t splits);
 
+/* The general form, with every option of the GEMM kernels.  Beyond bias and epilogue it carries the two
+ * halves of a DEFERRED RMSNorm, which removes the norm kernels from a decode step:
+ *     rmsnorm(h) * g @ W^T  =  inv_rms(h) * ((h * g) @ W^T)        (inv_rms is one scalar per row)
+ *   producer (epilogue VB200_EPI_ADD_F32, out = the fp32 residual stream h): scaled_copy [M, N] bf16 also
+ *     receives bf16(h_new * copy_scale), copy_scale [N] = the weight g of the NEXT norm;
+ *   consumer (x = that scaled copy): every output row is multiplied by inv_rms of the matching fp32 row of
+ *     rms_rows [M, rms_dim] (M <= 64: computed inside the kernel while the weights stream), or by
+ *     row_scale [M] precomputed with vb200_row_inv_rms (any M).  The scale applies before bias and epilogue. */
+typedef struct vb200_linear_args {
+    size_t struct_size;
+    int32_t device;
+    void* stream;
+    const void* x;  int64_t ldx;        /* [M, K] bf16 */
+    const void* w;  int64_t ldw;        /* [N, K] bf16 */
+    void* out;      int64_t ldo;
+    int32_t M, N, K;
+    int32_t epilogue;                   /* vb200_epilogue */
+    int32_t splits;
+    const float* bias;                  /* [N] or NULL */
+    void* scaled_copy;                  /* [M, N] bf16, row stride N, or NULL (VB200_EPI_ADD_F32 only) */
+    const float* copy_scale;            /* [N] */
+    const float* rms_rows;              /* [M, rms_dim] fp32, row stride rms_ld elements (0 = rms_dim), or NULL */
+    int64_t rms_ld;
+    int32_t rms_dim;
+    float rms_eps;
+    const float* row_scale;             /* [M] or NULL */
+} vb200_linear_args;
+int vb200_linear_ex(const vb200_linear_args* a);
+/* inv_rms[m] = 1 / sqrt(mean(h[m, :]^2) + eps), h fp32 [M, dim] with row stride ld elements. */
+int vb200_row_inv_rms(int device, void* stream, const float* h, int64_t ld, float* inv_rms, int32_t M, int32_t dim, float eps);
+/* vb200_embedding plus scaled_out[m, :] = bf16(out[m, :] * scale) (no 1/rms): the producer half of a deferred norm. */
+int vb200_embedding_scaled(int device, void* stream, const void* ids, int32_t ids64, const void* table,
+                           float* out, int32_t M, int32_t dim, int32_t vocab, const float* scale, void* scaled_out);
+
 /* h += x W^T followed by the RMSNorm of the finished rows, xn = rmsnorm(h) * norm_weight (bf16) -- the
  * output projection / down projection of a block, its residual add, and the NEXT norm in the block
  * sequence (src/models/transformer_block.cpp:183-205) as one call (two launches chained by

@@ -269,3 +269,58 @@ def test_linear_with_bias(cuda, oracle, M, epilogue):
     torch.cuda.synchronize()
     tol = 2.0 ** -8 * np.abs(want) + 2e-3 if epilogue in (capi.EPI_BF16, capi.EPI_SWIGLU) else 1e-3 * (1.0 + np.abs(want))
     assert np.all(np.abs(from_torch(out) - want) <= tol)
+
+
+@pytest.mark.parametrize("M", [8, 40, 200])
+def test_deferred_rms_norm_chain(cuda, oracle, M):
+    """rmsnorm(h) * g @ W^T through the deferred form: a += GEMM that also emits bf16(h * g) (producer), then a GEMM
+    whose output rows are scaled by 1/rms(h) -- inside the weight-streaming kernel (M <= 64) or from
+    vb200_row_inv_rms (tiled kernel) -- must equal the oracle's linear(rms_norm(h, g), W)."""
+    import torch
+    from vesper_b200 import capi
+    dim, N2, K1 = 512, 384, 256
+    rng = np.random.default_rng(300 + M)
+    x = bf16_round(rng.standard_normal((M, K1)).astype(np.float32))
+    w1 = bf16_round((rng.standard_normal((dim, K1)) / np.sqrt(K1)).astype(np.float32))
+    w2 = bf16_round((rng.standard_normal((N2, dim)) / np.sqrt(dim)).astype(np.float32))
+    g = (1.0 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    h0 = rng.standard_normal((M, dim)).astype(np.float32)
+    h = to_torch(h0, torch.float32, cuda)
+    hg = torch.empty(M, dim, dtype=torch.bfloat16, device=cuda)
+    tg = to_torch(g, torch.float32, cuda)
+    capi.linear_ex(to_torch(x, torch.bfloat16, cuda), to_torch(w1, torch.bfloat16, cuda), h, epilogue=capi.EPI_ADD_F32, scaled_copy=hg, copy_scale=tg)
+    y = torch.empty(M, N2, dtype=torch.float32, device=cuda)
+    if M <= 64:
+        capi.linear_ex(hg, to_torch(w2, torch.bfloat16, cuda), y, epilogue=capi.EPI_F32, rms_rows=h, rms_eps=1e-6)
+    else:
+        inv = torch.empty(M, dtype=torch.float32, device=cuda)
+        capi.row_inv_rms(h, inv, 1e-6)
+        capi.linear_ex(hg, to_torch(w2, torch.bfloat16, cuda), y, epilogue=capi.EPI_F32, row_scale=inv)
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)
+    h_new = from_torch(h)
+    assert np.all(np.abs(h_new - (h0 + oracle.linear(x, w1))) <= 1e-3 * (1.0 + np.abs(h0)))
+    assert np.all(np.abs(from_torch(hg) - h_new * g[None, :]) <= 2.0 ** -8 * np.abs(h_new * g[None, :]) + 1e-6)
+    want = oracle.linear(oracle.rms_norm(h_new, g, 1e-6), w2)
+    # one bf16 rounding of the activations on the GPU side (2^-9 relative per element, averaged over the dot product)
+    assert np.abs(from_torch(y) - want).max() <= 1e-2 * max(1.0, np.abs(want).max())
+
+
+def test_embedding_scaled_and_row_inv_rms(cuda, oracle):
+    import torch
+    from vesper_b200 import capi
+    rng = np.random.default_rng(13)
+    table = bf16_round(rng.standard_normal((300, 1024)).astype(np.float32))
+    g = (1.0 + 0.1 * rng.standard_normal(1024)).astype(np.float32)
+    ids = rng.integers(0, 300, size=(5,)).astype(np.int32)
+    out = torch.empty(5, 1024, dtype=torch.float32, device=cuda)
+    sc = torch.empty(5, 1024, dtype=torch.bfloat16, device=cuda)
+    capi.embedding_scaled(torch.from_numpy(ids).to(cuda), to_torch(table, torch.bfloat16, cuda), out, to_torch(g, torch.float32, cuda), sc)
+    inv = torch.empty(5, dtype=torch.float32, device=cuda)
+    capi.row_inv_rms(out, inv, 1e-6)
+    torch.cuda.synchronize()
+    e = oracle.embedding(ids, table)
+    assert np.array_equal(from_torch(out), e)
+    assert np.all(np.abs(from_torch(sc) - e * g[None, :]) <= 2.0 ** -8 * np.abs(e * g[None, :]) + 1e-6)
+    want_inv = 1.0 / np.sqrt((e.astype(np.float64) ** 2).mean(axis=1) + 1e-6)
+    assert np.abs(from_torch(inv) - want_inv).max() <= 1e-5 * want_inv.max()

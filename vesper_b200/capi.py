@@ -58,7 +58,7 @@ EXPORTS = [
     "vb200_reset_launch_count", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
 ]
 BLOCK_EXPORTS = [
-    "vb200_linear", "vb200_linear_bias", "vb200_linear_add_rmsnorm", "vb200_embedding_rmsnorm", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
+    "vb200_linear", "vb200_linear_bias", "vb200_linear_ex", "vb200_row_inv_rms", "vb200_embedding_scaled", "vb200_linear_add_rmsnorm", "vb200_embedding_rmsnorm", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
 ]
 
 
@@ -76,6 +76,16 @@ class ExchangeArgs(C.Structure):
         ("struct_size", C.c_size_t), ("device", C.c_int32), ("stream", C.c_void_p), ("world", C.c_int32), ("rank", C.c_int32),
         ("peer_buffers", C.POINTER(C.c_void_p)), ("partial", C.c_void_p), ("rows", C.c_int64), ("D", C.c_int32), ("dtype", C.c_int32),
         ("out", C.c_void_p), ("lse", C.c_void_p), ("step", C.c_uint32), ("timeout_cycles", C.c_int64),
+    ]
+
+
+class LinearArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_size_t), ("device", C.c_int32), ("stream", C.c_void_p),
+        ("x", C.c_void_p), ("ldx", C.c_int64), ("w", C.c_void_p), ("ldw", C.c_int64), ("out", C.c_void_p), ("ldo", C.c_int64),
+        ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("epilogue", C.c_int32), ("splits", C.c_int32),
+        ("bias", C.c_void_p), ("scaled_copy", C.c_void_p), ("copy_scale", C.c_void_p),
+        ("rms_rows", C.c_void_p), ("rms_ld", C.c_int64), ("rms_dim", C.c_int32), ("rms_eps", C.c_float), ("row_scale", C.c_void_p),
     ]
 
 
@@ -139,6 +149,10 @@ def load():
     # decoder-block operators (include/vesper_b200_block.h)
     L.vb200_linear.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64] + [C.c_int32] * 5
     L.vb200_linear_bias.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64] + [C.c_int32] * 5
+    L.vb200_linear_ex.argtypes = [C.POINTER(LinearArgs)]
+    L.vb200_row_inv_rms.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_float]
+    L.vb200_embedding_scaled.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                         C.c_void_p, C.c_void_p]
     L.vb200_linear_add_rmsnorm.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                            C.c_void_p, C.c_float, C.c_void_p, C.c_int32]
     L.vb200_embedding_rmsnorm.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
@@ -348,6 +362,37 @@ def linear(x, w, out, epilogue=EPI_BF16, splits=0, stream=None, bias=None):
     check(load().vb200_linear_bias(x.device.index or 0, _stream_ptr(stream), _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias),
                                    _ptr(out), out.stride(0), M, N, K, epilogue, splits))
     return out
+
+
+def linear_ex(x, w, out, *, epilogue=EPI_BF16, splits=0, bias=None, scaled_copy=None, copy_scale=None, rms_rows=None, rms_eps=0.0,
+              row_scale=None, stream=None):
+    """vb200_linear_ex: the GEMM with bias and the two halves of a deferred RMSNorm."""
+    a = LinearArgs()
+    a.struct_size = C.sizeof(LinearArgs)
+    a.device = x.device.index or 0
+    a.stream = _stream_ptr(stream)
+    a.x, a.ldx, a.w, a.ldw, a.out, a.ldo = _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0)
+    a.M, a.K = x.shape
+    a.N = w.shape[0]
+    a.epilogue, a.splits = epilogue, splits
+    a.bias, a.scaled_copy, a.copy_scale, a.row_scale = _ptr(bias), _ptr(scaled_copy), _ptr(copy_scale), _ptr(row_scale)
+    if rms_rows is not None:
+        a.rms_rows, a.rms_ld, a.rms_dim, a.rms_eps = _ptr(rms_rows), rms_rows.stride(0), rms_rows.shape[1], rms_eps
+    check(load().vb200_linear_ex(C.byref(a)))
+    return out
+
+
+def row_inv_rms(h, out, eps, stream=None):
+    check(load().vb200_row_inv_rms(h.device.index or 0, _stream_ptr(stream), _ptr(h), h.stride(0), _ptr(out), h.shape[0], h.shape[1], eps))
+    return out
+
+
+def embedding_scaled(ids, table, out, scale, scaled_out, stream=None):
+    import torch
+    ids64 = 1 if ids.dtype == torch.int64 else 0
+    check(load().vb200_embedding_scaled(table.device.index or 0, _stream_ptr(stream), _ptr(ids), ids64, _ptr(table), _ptr(out), ids.numel(),
+                                        table.shape[1], table.shape[0], _ptr(scale), _ptr(scaled_out)))
+    return out, scaled_out
 
 
 def linear_add_rmsnorm(x, w, h, norm_weight, eps, xn_out, splits=0, stream=None):

@@ -511,6 +511,61 @@ int vb200_linear(int device, void* stream, const void* x, int64_t ldx, const voi
     return vb200_linear_bias(device, stream, x, ldx, w, ldw, nullptr, out, ldo, M, N, K, epilogue, splits);
 }
 
+int vb200_linear_ex(const vb200_linear_args* a) {
+    if (!a || a->struct_size != sizeof(vb200_linear_args)) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_args: null or struct_size mismatch");
+    if (!a->x || !a->w || !a->out || a->M <= 0 || a->N <= 0 || a->K <= 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_ex: null pointer or non-positive size");
+    if (a->epilogue < VB200_EPI_BF16 || a->epilogue > VB200_EPI_SWIGLU) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_ex: unknown epilogue");
+    if (a->ldx < a->K || a->ldw < a->K) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_ex: ldx and ldw must be >= K");
+    const int64_t out_cols = a->epilogue == VB200_EPI_SWIGLU ? a->N / 2 : a->N;
+    if (a->ldo < out_cols) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_ex: ldo smaller than the output row");
+    if (a->epilogue == VB200_EPI_SWIGLU && a->N % 2 != 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_ex: the SwiGLU epilogue needs an even N");
+    const int out_elem = (a->epilogue == VB200_EPI_F32 || a->epilogue == VB200_EPI_ADD_F32) ? 4 : 2;
+    if (a->K % 8 != 0 || a->ldx % 8 != 0 || a->ldw % 8 != 0 || (a->ldo * out_elem) % 16 != 0 || !aligned16(a->x) || !aligned16(a->w) || !aligned16(a->out))
+        return set_detail(VB200_ERR_ALIGNMENT, "vb200_linear_ex: K % 8, and 16-byte aligned bases and row strides, are required");
+    if (a->scaled_copy && (a->epilogue != VB200_EPI_ADD_F32 || !a->copy_scale))
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_ex: scaled_copy needs the += epilogue and copy_scale");
+    if (a->rms_rows && (a->rms_dim <= 0 || a->rms_dim % 4 != 0 || a->rms_ld % 4 != 0 || (a->rms_ld != 0 && a->rms_ld < a->rms_dim) || !aligned16(a->rms_rows)))
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_ex: rms_dim must be a positive multiple of 4 and rms_rows 16-byte aligned");
+    if (a->rms_rows && a->M > 64 && !a->row_scale)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_ex: for M > 64 pass row_scale (vb200_row_inv_rms) instead of rms_rows");
+    DeviceGuard g;
+    if (int rc = g.init(a->device)) return rc;
+    LinearParams p{};
+    p.x = a->x; p.ldx = a->ldx; p.w = a->w; p.ldw = a->ldw; p.out = a->out; p.ldo = a->ldo;
+    p.M = a->M; p.N = a->N; p.K = a->K; p.epilogue = a->epilogue; p.splits = a->splits;
+    p.bias = a->bias;
+    p.scaled_copy = a->scaled_copy; p.copy_scale = a->copy_scale;
+    if (a->row_scale) p.row_scale = a->row_scale;              // a precomputed factor wins over the in-kernel one
+    else if (a->rms_rows && a->M <= 64) {
+        p.rms_rows = a->rms_rows; p.rms_dim = a->rms_dim; p.rms_eps = a->rms_eps;
+        p.rms_ld = a->rms_ld > 0 ? a->rms_ld : a->rms_dim;
+    }
+    p.status = kernel_status_word();
+    if (!p.status) return VB200_ERR_CUDA;
+    return launch_linear(static_cast<cudaStream_t>(a->stream), p);
+}
+
+int vb200_row_inv_rms(int device, void* stream, const float* h, int64_t ld, float* inv_rms, int32_t M, int32_t dim, float eps) {
+    if (!h || !inv_rms || M <= 0 || dim <= 0 || ld < dim) return set_detail(VB200_ERR_INVALID_ARG, "vb200_row_inv_rms: bad arguments");
+    if (!aligned16(h)) return set_detail(VB200_ERR_ALIGNMENT, "vb200_row_inv_rms: 16-byte alignment required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    return launch_row_inv_rms(static_cast<cudaStream_t>(stream), h, ld, inv_rms, M, dim, eps);
+}
+
+int vb200_embedding_scaled(int device, void* stream, const void* ids, int32_t ids64, const void* table,
+                           float* out, int32_t M, int32_t dim, int32_t vocab, const float* scale, void* scaled_out) {
+    if (!ids || !table || !out || !scale || !scaled_out || M <= 0 || dim <= 0 || vocab <= 0)
+        return set_detail(VB200_ERR_INVALID_ARG, "vb200_embedding_scaled: bad arguments");
+    if (!aligned16(table) || !aligned16(out) || !aligned16(scale) || !aligned16(scaled_out))
+        return set_detail(VB200_ERR_ALIGNMENT, "vb200_embedding_scaled: 16-byte alignment required");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    int* status = kernel_status_word();
+    if (!status) return VB200_ERR_CUDA;
+    return launch_embedding(static_cast<cudaStream_t>(stream), ids, ids64, table, out, M, dim, vocab, status, scale, scaled_out, 0.f, 1);
+}
+
 int vb200_linear_add_rmsnorm(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
                              float* h, int32_t M, int32_t N, int32_t K, const float* norm_weight, float eps,
                              void* xn_out, int32_t splits) {

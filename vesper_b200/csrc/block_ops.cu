@@ -59,6 +59,22 @@ rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, __nv_b
     }
 }
 
+// inv_rms[m] = 1 / sqrt(mean(x[m,:]^2) + eps): the per-row factor of a deferred RMSNorm.  One warp per row.
+__global__ void row_inv_rms_kernel(const float* __restrict__ x, long long ld, float* __restrict__ inv_rms, int M, int dim, float eps) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= M) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + static_cast<long long>(row) * ld);
+    float ss = 0.f;
+    for (int c = lane; c < dim / 4; c += 32) {
+        const float4 v = xr[c];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) inv_rms[row] = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
+}
+
 // silu(g) * u with silu(g) = g * sigmoid(g) -- ops::silu_mul, src/ops/elementwise.cpp:1297-1328.
 __global__ void silu_mul_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ out, long long nvec) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -82,7 +98,7 @@ __global__ void silu_mul_kernel(const uint4* __restrict__ gate, const uint4* __r
 __global__ void __launch_bounds__(256)
 embedding_kernel(const void* __restrict__ ids, int ids64, const __nv_bfloat16* __restrict__ table,
                  float* __restrict__ out, int dim, int vocab, int* status, const float* __restrict__ norm_w,
-                 __nv_bfloat16* __restrict__ norm_out, float norm_eps) {
+                 __nv_bfloat16* __restrict__ norm_out, float norm_eps, int scaled_copy_only) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long m = blockIdx.x;
@@ -108,7 +124,8 @@ embedding_kernel(const void* __restrict__ ids, int ids64, const __nv_bfloat16* _
     float tot = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) tot += part[i];
-    const float inv_rms = 1.0f / sqrtf(tot / static_cast<float>(dim) + norm_eps);
+    // scaled_copy_only: the consumer GEMM applies 1/rms to its output rows (deferred norm)
+    const float inv_rms = scaled_copy_only ? 1.0f : 1.0f / sqrtf(tot / static_cast<float>(dim) + norm_eps);
     uint4* nd = reinterpret_cast<uint4*>(norm_out + m * dim);
     const float4* g = reinterpret_cast<const float4*>(norm_w);
     for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) {
@@ -215,6 +232,11 @@ int launch_rms_norm(cudaStream_t s, const float* x, const float* weight, void* o
                       static_cast<__nv_bfloat16*>(out_bf16), dim, eps);
 }
 
+int launch_row_inv_rms(cudaStream_t s, const float* h, long long ld, float* inv_rms, int M, int dim, float eps) {
+    if (dim % 4 != 0 || ld % 4 != 0) return set_detail(VB200_ERR_ALIGNMENT, "row_inv_rms: dim must be a multiple of 4");
+    return launch_pdl(row_inv_rms_kernel, dim3(static_cast<unsigned>((M + 7) / 8)), dim3(256), s, h, ld, inv_rms, M, dim, eps);
+}
+
 int launch_silu_mul(cudaStream_t s, const void* gate, const void* up, void* out, long long n) {
     if (n % 8 != 0) return set_detail(VB200_ERR_ALIGNMENT, "silu_mul: element count must be a multiple of 8");
     const long long nvec = n / 8;
@@ -226,11 +248,11 @@ int launch_silu_mul(cudaStream_t s, const void* gate, const void* up, void* out,
 }
 
 int launch_embedding(cudaStream_t s, const void* ids, int ids64, const void* table, float* out, int M, int dim,
-                     int vocab, int* status, const float* norm_w, void* norm_out, float norm_eps) {
+                     int vocab, int* status, const float* norm_w, void* norm_out, float norm_eps, int scaled_copy_only) {
     if (dim % 8 != 0) return set_detail(VB200_ERR_ALIGNMENT, "embedding: dim must be a multiple of 8");
     return launch_pdl(embedding_kernel, dim3(static_cast<unsigned>(M)), dim3(256), s, ids, ids64,
                       static_cast<const __nv_bfloat16*>(table), out, dim, vocab, status, norm_w,
-                      static_cast<__nv_bfloat16*>(norm_out), norm_eps);
+                      static_cast<__nv_bfloat16*>(norm_out), norm_eps, scaled_copy_only);
 }
 
 int launch_greedy_step(cudaStream_t s, const vb200_greedy_args& a) {

@@ -122,8 +122,22 @@ struct LinearParams {
     void* norm_out;                  // [M, N] bf16, row stride norm_ld; null = no fused norm
     long long norm_ld;
     float norm_eps;
+    // Deferred RMSNorm (decode path: no norm kernel at all).  rmsnorm(h) * g @ W^T = inv_rms(h) * ((h * g) @ W^T):
+    //   producer side, with the += epilogue: also scaled_copy[m,n] = bf16(out[m,n] * copy_scale[n])  (h * g of the NEXT norm)
+    //   consumer side: the rows of the output are multiplied by inv_rms of the fp32 rows `rms_rows` (the residual
+    //   stream h, [M, rms_dim], contiguous), computed inside the skinny kernel while the weights stream, or taken
+    //   from the precomputed array `row_scale` [M] (tiled kernel)
+    void* scaled_copy;               // [M, N] bf16, row stride N, or null
+    const float* copy_scale;         // [N]
+    const float* rms_rows;           // [M, rms_dim] fp32 (row stride rms_ld) or null
+    long long rms_ld;
+    int rms_dim;
+    float rms_eps;
+    const float* row_scale;          // [M] or null
 };
 int launch_linear(cudaStream_t s, const LinearParams& p);
+// inv_rms[m] = 1 / sqrt(mean(h[m,:]^2) + eps)
+int launch_row_inv_rms(cudaStream_t s, const float* h, long long ld, float* inv_rms, int M, int dim, float eps);
 
 // ---- block_ops.cu ----
 int launch_interleave_rows(cudaStream_t s, const void* a, const void* b, void* out, long long rows, long long cols);
@@ -131,7 +145,8 @@ int launch_rms_norm(cudaStream_t s, const float* x, const float* weight, void* o
 int launch_silu_mul(cudaStream_t s, const void* gate, const void* up, void* out, long long n);
 // norm_w / norm_out (nullable): also out_norm[m,:] = rmsnorm(out[m,:]) * norm_w as bf16
 int launch_embedding(cudaStream_t s, const void* ids, int ids64, const void* table, float* out, int M, int dim,
-                     int vocab, int* status, const float* norm_w = nullptr, void* norm_out = nullptr, float norm_eps = 0.f);
+                     int vocab, int* status, const float* norm_w = nullptr, void* norm_out = nullptr, float norm_eps = 0.f,
+                     int scaled_copy_only = 0);   // 1: norm_out = bf16(out * norm_w) without the 1/rms factor (deferred norm)
 int launch_greedy_step(cudaStream_t s, const vb200_greedy_args& a);
 
 }  // namespace vb200

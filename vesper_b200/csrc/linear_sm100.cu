@@ -83,6 +83,11 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)
 // One output element group of the wide kernel: 32 consecutive columns of one row.
 template <int EPI>
 __device__ __forceinline__ void store_row32(const LinearParams& p, int row, int col0, uint32_t (&acc)[32]) {
+    if (p.row_scale != nullptr) {                // deferred RMSNorm: this row's 1/rms
+        const float rs = __ldg(p.row_scale + row);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * rs);
+    }
     if (p.bias != nullptr) {                     // nn::Linear's bias (src/nn/linear.cpp:44-46)
 #pragma unroll
         for (int j = 0; j < 32; ++j)
@@ -139,6 +144,7 @@ __device__ __forceinline__ void store_row32(const LinearParams& p, int row, int 
                     float v = __uint_as_float(acc[8 * j + e]);
                     if (EPI == VB200_EPI_ADD_F32) v += __uint_as_float(hres[j][e]);
                     w8[e] = __float_as_uint(v);
+                    acc[8 * j + e] = w8[e];                     // the new residual value, for the scaled copy below
                 }
                 st_global_v8(out + 8 * j, w8);
             }
@@ -147,6 +153,26 @@ __device__ __forceinline__ void store_row32(const LinearParams& p, int row, int 
                 float v = __uint_as_float(acc[j]);
                 if (EPI == VB200_EPI_ADD_F32) v += out[j];
                 out[j] = v;
+                acc[j] = __float_as_uint(v);
+            }
+        }
+        if (EPI == VB200_EPI_ADD_F32 && p.scaled_copy != nullptr) {
+            __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(p.scaled_copy) + static_cast<long long>(row) * p.N + col0;
+            if (n_valid == 32) {
+                const float4* g4 = reinterpret_cast<const float4*>(p.copy_scale + col0);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    uint32_t w8[8];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float4 gw = __ldg(g4 + 4 * j + e);
+                        w8[2 * e] = Elem<__nv_bfloat16>::pack2(__uint_as_float(acc[16 * j + 4 * e]) * gw.x, __uint_as_float(acc[16 * j + 4 * e + 1]) * gw.y);
+                        w8[2 * e + 1] = Elem<__nv_bfloat16>::pack2(__uint_as_float(acc[16 * j + 4 * e + 2]) * gw.z, __uint_as_float(acc[16 * j + 4 * e + 3]) * gw.w);
+                    }
+                    st_global_v8(cp + 16 * j, w8);
+                }
+            } else {
+                for (int j = 0; j < n_valid; ++j) cp[j] = __float2bfloat16_rn(__uint_as_float(acc[j]) * __ldg(p.copy_scale + col0 + j));
             }
         }
     }
@@ -332,6 +358,7 @@ linear_skinny_kernel(const __grid_constant__ LinearMaps maps, LinearParams p, in
     const int kb0 = static_cast<int>(rank) * kb_per;
     const int nkb = max(0, min(k_blocks, kb0 + kb_per) - kb0);
     const WaitCtx ctx{abort_flag, p.status};
+    __shared__ float s_inv_rms[MT];
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -396,6 +423,28 @@ linear_skinny_kernel(const __grid_constant__ LinearMaps maps, LinearParams p, in
     } else {
         const int quarter = warp & 3;
         asm volatile("griddepcontrol.wait;" ::: "memory");      // before any global access of the epilogue
+        if (p.rms_rows != nullptr && rank == 0) {
+            // deferred RMSNorm: 1/rms of the token rows, computed while the weights stream (these warps are idle
+            // until the accumulator is complete); one warp per row, every load of a 2048-column chunk in flight
+            const int m_count = min(p.M, MT), nv = p.rms_dim / 4;
+            for (int j = warp - 2; j < m_count; j += 4) {
+                const float4* hr = reinterpret_cast<const float4*>(p.rms_rows + static_cast<long long>(j) * p.rms_ld);
+                float ss = 0.f;
+                for (int c0 = 0; c0 < nv; c0 += 512) {
+                    float4 v[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int c = c0 + lane + 32 * i;
+                        v[i] = c < nv ? __ldcg(hr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                if (lane == 0) s_inv_rms[j] = 1.0f / sqrtf(ss / static_cast<float>(p.rms_dim) + p.rms_eps);
+            }
+        }
         // wait even when this slice is empty: the commit above always arrives
         if (mbar_wait_warp(acc_full, 0, ctx, 0x53) && nkb > 0) {
             tc_fence_after();
@@ -435,6 +484,11 @@ linear_skinny_kernel(const __grid_constant__ LinearMaps maps, LinearParams p, in
     if (warp >= 2 && rank == 0) {
         const int n = nt * kTileA + (warp & 3) * 32 + lane;
         const int m_count = min(p.M, MT);
+        if (p.rms_rows != nullptr) {
+            asm volatile("bar.sync 2, 128;" ::: "memory");       // s_inv_rms written by the four epilogue warps
+#pragma unroll
+            for (int j = 0; j < MT; ++j) acc[j] *= (j < m_count ? s_inv_rms[j] : 0.f);
+        }
         if (p.bias != nullptr && n < p.N) {
             const float bv = __ldg(p.bias + n);
 #pragma unroll
@@ -455,7 +509,12 @@ linear_skinny_kernel(const __grid_constant__ LinearMaps maps, LinearParams p, in
                 const long long idx = static_cast<long long>(j) * p.ldo + n;
                 if (EPI == VB200_EPI_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(acc[j]);
                 else if (EPI == VB200_EPI_F32) static_cast<float*>(p.out)[idx] = acc[j];
-                else static_cast<float*>(p.out)[idx] += acc[j];
+                else {
+                    const float hv = static_cast<float*>(p.out)[idx] + acc[j];
+                    static_cast<float*>(p.out)[idx] = hv;
+                    if (p.scaled_copy != nullptr)
+                        static_cast<__nv_bfloat16*>(p.scaled_copy)[static_cast<long long>(j) * p.N + n] = __float2bfloat16_rn(hv * __ldg(p.copy_scale + n));
+                }
             }
         }
     }

@@ -46,7 +46,8 @@ struct TransformerLM::Layer {
 struct TransformerLM::Buffers {
     int64_t rows = 0, batch = 0;
     Tensor h;          // [rows, dim] fp32 residual stream
-    Tensor xn;         // [rows, dim] bf16 normalised activations
+    Tensor xn;         // [rows, dim] bf16: the residual stream times the weight of the norm that comes next (its 1/rms is applied by the consuming GEMM)
+    Tensor inv;        // [rows] fp32: 1/rms of the residual rows (prompt passes; decode steps compute it inside the GEMM)
     Tensor qkv;        // [rows, (Hq + 2 Hkv) * D] bf16
     Tensor attn;       // [rows, Hq * D] bf16, heads merged
     Tensor act;        // [rows, hidden] bf16
@@ -174,6 +175,7 @@ void TransformerLM::ensure_buffers(int64_t rows, int64_t batch) {
     const int64_t qkv_n = (config_.n_heads + 2 * config_.kv_heads()) * D;
     b.h = empty({rows, dim}, DType::Float32, Device::CUDA);
     b.xn = empty({rows, dim}, DType::BFloat16, Device::CUDA);
+    b.inv = empty({rows}, DType::Float32, Device::CUDA);
     b.qkv = empty({rows, qkv_n}, DType::BFloat16, Device::CUDA);
     b.attn = empty({rows, config_.n_heads * D}, DType::BFloat16, Device::CUDA);
     b.act = empty({rows, hid}, DType::BFloat16, Device::CUDA);
@@ -208,6 +210,31 @@ void TransformerLM::run_blocks(int64_t B, int64_t T, int64_t start_pos, bool dev
     const int qkv_n = (Hq + 2 * Hkv) * D;
     const float scale = 1.0f / std::sqrt(static_cast<float>(D));
     uint16_t* qkv = b.qkv.data_ptr<uint16_t>();
+    // RMSNorm is deferred: b.xn holds bf16(h * g) of the norm that comes next, and the GEMM that consumes it scales
+    // its output rows by 1/rms(h) -- computed inside the weight-streaming kernel for up to 64 rows, from b.inv
+    // (one small kernel per norm) for prompt passes.  No stand-alone norm kernel runs in a decode step.
+    auto consume = [&](const void* x, const Tensor& w, void* out, int64_t ldo, int N, int epilogue, const char* who) {
+        vb200_linear_args a{};
+        a.struct_size = sizeof(a);
+        a.device = dev; a.stream = s;
+        a.x = x; a.ldx = dim; a.w = w.data_ptr<char>(); a.ldw = dim; a.out = out; a.ldo = ldo;
+        a.M = M; a.N = N; a.K = dim; a.epilogue = epilogue;
+        if (M <= 64) { a.rms_rows = b.h.data_ptr<float>(); a.rms_dim = dim; a.rms_ld = dim; a.rms_eps = config_.norm_eps; }
+        else {
+            check(vb200_row_inv_rms(dev, s, b.h.data_ptr<float>(), dim, b.inv.data_ptr<float>(), M, dim, config_.norm_eps), "row_inv_rms");
+            a.row_scale = b.inv.data_ptr<float>();
+        }
+        check(vb200_linear_ex(&a), who);
+    };
+    auto produce = [&](const void* x, int K, const Tensor& w, const float* next_norm, const char* who) {
+        vb200_linear_args a{};
+        a.struct_size = sizeof(a);
+        a.device = dev; a.stream = s;
+        a.x = x; a.ldx = K; a.w = w.data_ptr<char>(); a.ldw = K; a.out = b.h.data_ptr<float>(); a.ldo = dim;
+        a.M = M; a.N = dim; a.K = K; a.epilogue = VB200_EPI_ADD_F32;
+        a.scaled_copy = b.xn.data_ptr<char>(); a.copy_scale = next_norm;
+        check(vb200_linear_ex(&a), who);
+    };
     // [B,T,H,D] memory seen as [B,H,T,D]: strides (batch, head, row) in elements
     const vb200_tensor4 qv{qkv, static_cast<int64_t>(T) * qkv_n, D, qkv_n};
     const vb200_tensor4 kv{qkv + Hq * D, static_cast<int64_t>(T) * qkv_n, D, qkv_n};
@@ -216,9 +243,9 @@ void TransformerLM::run_blocks(int64_t B, int64_t T, int64_t start_pos, bool dev
     for (size_t l = 0; l < layers_.size(); ++l) {
         Layer& L = *layers_[l];
         nn::KVCache& cache = *kv_caches_[l];
-        // on entry b.xn = attention_norm_l(h): written by the embedding call (l = 0) or by the previous
-        // block's down projection call, which ends with the next norm
-        check(vb200_linear(dev, s, b.xn.data_ptr<char>(), dim, L.wqkv.data_ptr<char>(), dim, qkv, qkv_n, M, qkv_n, dim, VB200_EPI_BF16, 0), "linear(wqkv)");
+        // on entry b.xn = bf16(h * attention_norm_l): written by the embedding call (l = 0) or by the previous
+        // block's down projection
+        consume(b.xn.data_ptr<char>(), L.wqkv, qkv, qkv_n, qkv_n, VB200_EPI_BF16, "linear(wqkv)");
         const vb200_tensor4 kc{cache.k().data_ptr<char>(), cache.k().strides()[0], cache.k().strides()[1], cache.k().strides()[2]};
         const vb200_tensor4 vc{cache.v().data_ptr<char>(), cache.v().strides()[0], cache.v().strides()[1], cache.v().strides()[2]};
         if (T == 1 && D == 128) {
@@ -258,12 +285,10 @@ void TransformerLM::run_blocks(int64_t B, int64_t T, int64_t start_pos, bool dev
             check(vb200_prefill_fwd(&a), "attention(prefill)");
         }
         if (!device_positions) cache.set_current_len(std::max(cache.current_seq_len(), static_cast<int>(start_pos + T)));
-        check(vb200_linear_add_rmsnorm(dev, s, b.attn.data_ptr<char>(), Hq * D, L.wo.data_ptr<char>(), Hq * D, b.h.data_ptr<float>(), M, dim, Hq * D,
-                                       L.ffn_norm.data_ptr<float>(), config_.norm_eps, b.xn.data_ptr<char>(), 0), "linear(wo) + ffn_norm");
-        check(vb200_linear(dev, s, b.xn.data_ptr<char>(), dim, L.w13.data_ptr<char>(), dim, b.act.data_ptr<char>(), hid, M, 2 * hid, dim, VB200_EPI_SWIGLU, 0), "linear(gate,up)");
+        produce(b.attn.data_ptr<char>(), Hq * D, L.wo, L.ffn_norm.data_ptr<float>(), "linear(wo) + residual");
+        consume(b.xn.data_ptr<char>(), L.w13, b.act.data_ptr<char>(), hid, 2 * hid, VB200_EPI_SWIGLU, "linear(gate,up)");
         const float* next_norm = (l + 1 < layers_.size()) ? layers_[l + 1]->attn_norm.data_ptr<float>() : final_norm_.data_ptr<float>();
-        check(vb200_linear_add_rmsnorm(dev, s, b.act.data_ptr<char>(), hid, L.w2.data_ptr<char>(), hid, b.h.data_ptr<float>(), M, dim, hid,
-                                       next_norm, config_.norm_eps, b.xn.data_ptr<char>(), 0), "linear(down) + next norm");
+        produce(b.act.data_ptr<char>(), hid, L.w2, next_norm, "linear(down) + residual");
     }
 }
 
@@ -283,18 +308,32 @@ Tensor TransformerLM::forward_with_cache(const Tensor& tokens, int64_t start_pos
     Tensor ids = tokens.is_contiguous() ? tokens : tokens.contiguous();
     if (ids.device() != Device::CUDA) ids = ids.to(Device::CUDA);
     const float* first_norm = layers_.empty() ? final_norm_.data_ptr<float>() : layers_[0]->attn_norm.data_ptr<float>();
-    check(vb200_embedding_rmsnorm(dev, s, ids.data_ptr<char>(), ids.dtype() == DType::Int64 ? 1 : 0, tok_emb_.data_ptr<char>(), b.h.data_ptr<float>(),
-                                  static_cast<int>(B * T), dim, vocab, first_norm, config_.norm_eps, b.xn.data_ptr<char>()), "embedding + norm");
-    run_blocks(B, T, start_pos, false, nullptr, 0);          // leaves final_norm(h) in b.xn
+    check(vb200_embedding_scaled(dev, s, ids.data_ptr<char>(), ids.dtype() == DType::Int64 ? 1 : 0, tok_emb_.data_ptr<char>(), b.h.data_ptr<float>(),
+                                 static_cast<int>(B * T), dim, vocab, first_norm, b.xn.data_ptr<char>()), "embedding");
+    run_blocks(B, T, start_pos, false, nullptr, 0);          // leaves bf16(h * final_norm) in b.xn
     const int64_t out_rows = last_only ? B : B * T;
     if (b.logit_rows < out_rows) {
         b.logits = empty({out_rows, config_.vocab_size}, DType::Float32, Device::CUDA);
         b.logit_rows = out_rows;
     }
     // last_only: row b of the GEMM input is the last new token of sequence b (row stride T * dim)
-    const uint16_t* x = b.xn.data_ptr<uint16_t>() + (last_only ? (T - 1) * dim : 0);
-    check(vb200_linear(dev, s, x, last_only ? T * static_cast<int64_t>(dim) : dim, lm_head_.data_ptr<char>(), dim, b.logits.data_ptr<float>(),
-                       vocab, static_cast<int>(out_rows), vocab, dim, VB200_EPI_F32, 0), "linear(output)");
+    {
+        const int64_t row_ld = last_only ? T * static_cast<int64_t>(dim) : dim;
+        const int64_t first = last_only ? (T - 1) * static_cast<int64_t>(dim) : 0;
+        vb200_linear_args a{};
+        a.struct_size = sizeof(a);
+        a.device = dev; a.stream = s;
+        a.x = b.xn.data_ptr<uint16_t>() + first; a.ldx = row_ld;
+        a.w = lm_head_.data_ptr<char>(); a.ldw = dim; a.out = b.logits.data_ptr<float>(); a.ldo = vocab;
+        a.M = static_cast<int>(out_rows); a.N = vocab; a.K = dim; a.epilogue = VB200_EPI_F32;
+        // the final norm's 1/rms of the same rows of the residual stream
+        if (out_rows <= 64) { a.rms_rows = b.h.data_ptr<float>() + first; a.rms_ld = row_ld; a.rms_dim = dim; a.rms_eps = config_.norm_eps; }
+        else {
+            check(vb200_row_inv_rms(dev, s, b.h.data_ptr<float>() + first, row_ld, b.inv.data_ptr<float>(), static_cast<int>(out_rows), dim, config_.norm_eps), "row_inv_rms");
+            a.row_scale = b.inv.data_ptr<float>();
+        }
+        check(vb200_linear_ex(&a), "linear(output)");
+    }
     Tensor out = b.logits.narrow(0, 0, out_rows).view({B, last_only ? 1 : T, config_.vocab_size});
     return out;
 }
@@ -337,11 +376,22 @@ void TransformerLM::decode_step(DecodeState& st) {
     const int dev = b.h.device_index();
     const int dim = static_cast<int>(config_.dim), vocab = static_cast<int>(config_.vocab_size);
     const float* first_norm = layers_.empty() ? final_norm_.data_ptr<float>() : layers_[0]->attn_norm.data_ptr<float>();
-    check(vb200_embedding_rmsnorm(dev, s, st.ids.data_ptr<char>(), 0, tok_emb_.data_ptr<char>(), b.h.data_ptr<float>(), static_cast<int>(B), dim, vocab,
-                                  first_norm, config_.norm_eps, b.xn.data_ptr<char>()), "embedding + norm");
-    run_blocks(B, 1, 0, true, st.lens.data_ptr<int32_t>(), st.max_len);      // leaves final_norm(h) in b.xn
-    check(vb200_linear(dev, s, b.xn.data_ptr<char>(), dim, lm_head_.data_ptr<char>(), dim, b.logits.data_ptr<float>(), vocab, static_cast<int>(B), vocab, dim,
-                       VB200_EPI_F32, 0), "linear(output)");
+    check(vb200_embedding_scaled(dev, s, st.ids.data_ptr<char>(), 0, tok_emb_.data_ptr<char>(), b.h.data_ptr<float>(), static_cast<int>(B), dim, vocab,
+                                 first_norm, b.xn.data_ptr<char>()), "embedding");
+    run_blocks(B, 1, 0, true, st.lens.data_ptr<int32_t>(), st.max_len);      // leaves bf16(h * final_norm) in b.xn
+    {
+        vb200_linear_args a{};
+        a.struct_size = sizeof(a);
+        a.device = dev; a.stream = s;
+        a.x = b.xn.data_ptr<char>(); a.ldx = dim; a.w = lm_head_.data_ptr<char>(); a.ldw = dim; a.out = b.logits.data_ptr<float>(); a.ldo = vocab;
+        a.M = static_cast<int>(B); a.N = vocab; a.K = dim; a.epilogue = VB200_EPI_F32;
+        if (B <= 64) { a.rms_rows = b.h.data_ptr<float>(); a.rms_ld = dim; a.rms_dim = dim; a.rms_eps = config_.norm_eps; }
+        else {
+            check(vb200_row_inv_rms(dev, s, b.h.data_ptr<float>(), dim, b.inv.data_ptr<float>(), static_cast<int>(B), dim, config_.norm_eps), "row_inv_rms");
+            a.row_scale = b.inv.data_ptr<float>();
+        }
+        check(vb200_linear_ex(&a), "linear(output)");
+    }
     pick_from_last_logits(st);
 }
 
