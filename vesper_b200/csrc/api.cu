@@ -153,6 +153,8 @@ DecodePlan plan_decode(const vb200_decode_args* a) {
         int want = static_cast<int>((592 + units - 1) / units);
         chunk = (max_total + want - 1) / want;
         if (chunk > 512 && a->seq_lens) chunk = 512;
+        // short contexts: at most 16 splits, so that they can run as one cluster that merges its own partials
+        if (max_total <= 16 * 2 * tile && (max_total + chunk - 1) / chunk > 16) chunk = (max_total + 15) / 16;
     }
     chunk = (chunk + tile - 1) / tile * tile;
     if (chunk < tile) chunk = tile;

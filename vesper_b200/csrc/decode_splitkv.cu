@@ -193,10 +193,14 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(Dec
     }
     // let the combine kernel's blocks be scheduled as soon as every CTA of this grid has started
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (k_begin >= total) return;                                   // nothing for this split
+    const bool nothing = k_begin >= total;                          // no key for this split
+    if (nothing && !p.cluster_merge) return;                        // (a cluster member stays for the cluster barriers)
     const int k_end = min(len, k_begin + p.chunk);                  // cached keys [k_begin, k_end)
-    const bool owns_new = p.append && (len / p.chunk == split);
-    const int ntiles = (k_end > k_begin) ? (k_end - k_begin + kTile - 1) / kTile : 0;
+    const bool owns_new = !nothing && p.append && (len / p.chunk == split);
+    const int ntiles = (!nothing && k_end > k_begin) ? (k_end - k_begin + kTile - 1) / kTile : 0;
+    // cluster merge: where this CTA parks its per-head (acc, m, l) until the leader's ring is free to receive them
+    constexpr int kParkOffset = kStages * 2 * kTile * 128 * static_cast<int>(sizeof(T)) - 4096;   // the ring's last 4 KB
+    static_assert(NREP * (D + 2) * 4 <= 4096 && 16 * NREP * (D + 2) * 4 <= kParkOffset, "park area and the leader's receive area must not overlap");
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], CW); }
@@ -344,9 +348,72 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(Dec
                     L += gl[g * NREP + h] * w;
                     acc += go[(g * NREP + h) * 128 + d] * w;
                 }
-                float* out = wsp + ((static_cast<long long>(b) * p.Hkv + kvh) * nsplits + split) * NREP * (D + 2) + h * (D + 2);
-                out[d] = acc / L;
-                if (d == 0) { out[D] = M * kLn2; out[D + 1] = L; }
+                if (p.cluster_merge) {
+                    // parked in this CTA's own (drained) ring, clear of the go/gm/gl buffers other threads still read
+                    float* tx = reinterpret_cast<float*>(smem_raw + kParkOffset) + h * (D + 2);
+                    tx[d] = acc;
+                    if (d == 0) { tx[D] = M; tx[D + 1] = L; }
+                } else {
+                    float* out = wsp + ((static_cast<long long>(b) * p.Hkv + kvh) * nsplits + split) * NREP * (D + 2) + h * (D + 2);
+                    out[d] = acc / L;
+                    if (d == 0) { out[D] = M * kLn2; out[D + 1] = L; }
+                }
+            }
+        }
+    }
+
+    if (p.cluster_merge) {
+        // The splits of this (batch, kv_head) are one cluster: every member parks its per-head (acc, m, l) in the
+        // leader's shared memory (distributed shared memory; the leader's ring is free after the first barrier),
+        // the leader merges them in split order and writes the final rows -- no combine kernel, no workspace trip.
+        const unsigned nsp = gridDim.x;
+        unsigned rank = 0;
+        if (nsp > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+        float* rx = reinterpret_cast<float*>(smem_raw);              // leader: [nsp][NREP][D + 2]
+        if (nsp > 1) {
+            __syncwarp();
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            if (tid < 128 && rank != 0 && !nothing) {
+                const float* tx = reinterpret_cast<const float*>(smem_raw + kParkOffset);
+                uint32_t base;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base) : "r"(smem_u32(rx)), "r"(0));
+#pragma unroll
+                for (int h = 0; h < NREP; ++h) {
+                    const uint32_t a = base + ((rank * NREP + h) * (D + 2)) * 4;
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a + tid * 4), "f"(tx[h * (D + 2) + tid]) : "memory");
+                    if (tid == 0) {
+                        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a + D * 4), "f"(tx[h * (D + 2) + D]) : "memory");
+                        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a + (D + 1) * 4), "f"(tx[h * (D + 2) + D + 1]) : "memory");
+                    }
+                }
+            }
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
+        if (rank == 0 && tid < 128) {
+            const int d = tid;
+            const unsigned nvalid = min(nsp, static_cast<unsigned>((total + p.chunk - 1) / p.chunk));
+#pragma unroll
+            for (int h = 0; h < NREP; ++h) {
+                // a member without keys parked nothing: its slot is skipped (splits beyond the sequence are a suffix)
+                const float* own = reinterpret_cast<const float*>(smem_raw + kParkOffset) + h * (D + 2);
+                const float m0 = nothing ? -INFINITY : own[D];
+                float M = m0;
+                for (unsigned r = 1; r < nvalid; ++r) M = fmaxf(M, rx[(r * NREP + h) * (D + 2) + D]);
+                float L = (m0 == -INFINITY) ? 0.f : own[D + 1] * fast_exp2(m0 - M);
+                float acc = (m0 == -INFINITY) ? 0.f : own[d] * fast_exp2(m0 - M);
+                for (unsigned r = 1; r < nvalid; ++r) {
+                    const float* pr = rx + (r * NREP + h) * (D + 2);
+                    const float mr = pr[D];
+                    const float w = (mr == -INFINITY) ? 0.f : fast_exp2(mr - M);
+                    L += pr[D + 1] * w;
+                    acc += pr[d] * w;
+                }
+                const int hq = kvh * NREP + h;
+                const float o = (total > 0) ? acc / L : 0.f;
+                static_cast<T*>(p.o.ptr)[b * p.o.sb + hq * p.o.sh + d] = Elem<T>::from_f(o);
+                if (p.lse && d == 0) p.lse[static_cast<long long>(b) * p.Hq + hq] = M * kLn2 + logf(L);
             }
         }
     }
@@ -438,6 +505,8 @@ __global__ void lse_combine_kernel(const float* __restrict__ partials, int R, lo
     if (lse && d == 0) lse[row] = M + logf(L);
 }
 
+constexpr int kMaxClusterSplits = 16;   // cluster sizes above 8 are allowed on this part (non-portable size attribute)
+
 template <typename T, int NREP>
 int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
     constexpr int D = 128;
@@ -450,7 +519,7 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
     // Groups of 8 heads are compute-bound on CUDA cores and always take the warp-MMA split kernel; groups of 4
     // take it when a CTA streams at least 256 keys (measured: 5.7 vs 5.3 TB/s on 1-8 K contexts) and the
     // CUDA-core kernel below that, where its lighter prologue wins (3 us per call at 600-key contexts).
-    bool use_mma = false;
+    bool use_mma = false, need_combine = true;
     if constexpr (NREP == 8) use_mma = true;
     if constexpr (NREP == 4) use_mma = p.chunk >= 256;
     if (use_mma) {
@@ -461,14 +530,47 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
     } else if constexpr (NREP != 8) {       // (the CUDA-core kernel is never the choice for 8-head groups)
         size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + D * sizeof(float) + D * sizeof(T) + 2 * CW * 16 * sizeof(float) + sizeof(DecodeSmem<CW, kStages>);
         static_assert(2 * CW * NREP * 128 * 4 + 2 * 2 * CW * NREP * 4 <= kStages * 2 * kTile * 128 * 2, "merge buffers must fit in the ring");
+        static_assert(kMaxClusterSplits * NREP * 130 * 4 <= kStages * 2 * kTile * 128 * 2, "the cluster's partials must fit in the leader's ring");
         static thread_local int configured_dev = -1;
         int dev = 0;
         VB200_CUDA_TRY(cudaGetDevice(&dev));
         if (configured_dev != dev) {
             VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
             configured_dev = dev;
         }
+        // Up to 16 splits per (batch, kv_head): they run as one thread-block cluster that merges its partials through
+        // distributed shared memory and writes the final rows -- the combine kernel and the workspace round trip drop
+        // out.  Not when the caller wants the partial record or the length array advanced (the combine kernel does
+        // that after every CTA of the grid has read the lengths).
+        DecodeParams q = p;
+        q.cluster_merge = (!p.partial_out && !(p.seq_lens && p.advance_lens && p.append) && p.num_splits <= kMaxClusterSplits) ? 1 : 0;
         dim3 grid(p.num_splits, p.Hkv, p.B);
+        if (q.cluster_merge && p.num_splits > 8) {
+            // a size above the portable 8 must fit one GPC of this device: asked once per size
+            static thread_local int fits[kMaxClusterSplits + 1] = {};   // 0 unknown, 1 yes, -1 no
+            static thread_local int fits_dev = -1;
+            if (fits_dev != dev) { for (int& f : fits) f = 0; fits_dev = dev; }
+            if (fits[p.num_splits] == 0) {
+                cudaLaunchConfig_t probe{};
+                probe.gridDim = grid;
+                probe.blockDim = dim3((CW + 1) * 32);
+                probe.dynamicSmemBytes = smem;
+                cudaLaunchAttribute pa[1];
+                pa[0].id = cudaLaunchAttributeClusterDimension;
+                pa[0].val.clusterDim.x = static_cast<unsigned>(p.num_splits);
+                pa[0].val.clusterDim.y = 1;
+                pa[0].val.clusterDim.z = 1;
+                probe.attrs = pa;
+                probe.numAttrs = 1;
+                int n_clusters = 0;
+                cudaError_t e = cudaOccupancyMaxActiveClusters(&n_clusters, decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, &probe);
+                if (e != cudaSuccess) { (void)cudaGetLastError(); n_clusters = 0; }
+                fits[p.num_splits] = n_clusters > 0 ? 1 : -1;
+            }
+            if (fits[p.num_splits] < 0) q.cluster_merge = 0;
+        }
+        need_combine = !q.cluster_merge;
         profile_mark_begin(s);
         {
             cudaLaunchConfig_t cfg{};
@@ -476,18 +578,26 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
             cfg.blockDim = dim3((CW + 1) * 32);
             cfg.dynamicSmemBytes = smem;
             cfg.stream = s;
-            cudaLaunchAttribute attr[1];
+            cudaLaunchAttribute attr[2];
             attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[0].val.programmaticStreamSerializationAllowed = 1;
+            int n_attr = 1;
+            if (q.cluster_merge && p.num_splits > 1) {
+                attr[1].id = cudaLaunchAttributeClusterDimension;
+                attr[1].val.clusterDim.x = static_cast<unsigned>(p.num_splits);
+                attr[1].val.clusterDim.y = 1;
+                attr[1].val.clusterDim.z = 1;
+                n_attr = 2;
+            }
             cfg.attrs = attr;
-            cfg.numAttrs = 1;
-            VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, p));
+            cfg.numAttrs = n_attr;
+            VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, q));
         }
     }
     profile_mark_end(s);
     note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());
-    {
+    if (need_combine) {
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(p.Hq, p.B);
         cfg.blockDim = dim3(128 * kCombineGroups);
@@ -499,8 +609,8 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_combine_kernel<T>, p));
+        note_launch();
     }
-    note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());
     return VB200_OK;
 }

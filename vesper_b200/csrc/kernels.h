@@ -72,6 +72,7 @@ struct DecodeParams {
     float* workspace;    // ws_header ints (length used per sequence), then [B,Hkv,num_splits,n_rep,D+2]
     int ws_header;       // floats reserved at the front of the workspace (multiple of 64)
     int* status;         // device status word (bounded waits)
+    int cluster_merge;   // 1: the splits of a (batch, kv_head) form one thread-block cluster that merges its partials itself
 };
 int decode_tile_keys();
 int launch_decode(cudaStream_t s, const DecodeParams& p);
