@@ -148,11 +148,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     for (uint32_t it = 0;; ++it) {
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-#ifdef VB_SPIN_TEST
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
             "selp.b32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
         if (ok) return true;
