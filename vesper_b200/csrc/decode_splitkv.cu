@@ -158,6 +158,13 @@ struct __align__(16) DecodeSmem {
     int pad[3];
 };
 
+// Bytes of dynamic shared memory up to (not including) the cluster-merge receive area, a multiple of 16.
+template <typename T, int NREP, int CW, int kStages>
+__host__ __device__ constexpr int decode_base_smem() {
+    return (kStages * 2 * kTile * 128 * static_cast<int>(sizeof(T)) + 128 * static_cast<int>(sizeof(float)) + 128 * static_cast<int>(sizeof(T)) +
+            2 * CW * 16 * static_cast<int>(sizeof(float)) + static_cast<int>(sizeof(DecodeSmem<CW, kStages>)) + 15) & ~15;
+}
+
 // Dynamic shared memory layout (D = 128, 16-bit T):
 //   [0, kStages * 2 * kTile * 256)   K/V ring: stage s -> K at s*32 KB, V at s*32 KB + 16 KB
 //   then the new token's rotated key (fp32) and value, the per-group p buffers, DecodeSmem.
@@ -176,10 +183,17 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(Dec
     T* newv = reinterpret_cast<T*>(smem_raw + kStages * kStageBytes + kNewBytes - kRowBytes);   // new value [128]
     float* pbuf_all = reinterpret_cast<float*>(smem_raw + kStages * kStageBytes + kNewBytes);   // [kGroups][16]
     DecodeSmem<CW, kStages>* sm = reinterpret_cast<DecodeSmem<CW, kStages>*>(smem_raw + kStages * kStageBytes + kNewBytes + kGroups * 16 * sizeof(float));
+    // cluster merge (only when every CTA streams at most one tile, so ring stage 1 is never loaded): the receive area
+    // [splits][NREP][D + 2] floats lives in stage 1 -- no extra shared memory, and free from the start of the kernel
+    static_assert(kStages >= 2, "the receive area takes the second ring stage");
+    float* rx = reinterpret_cast<float*>(smem_raw + kStageBytes);
 
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, l16 = lane & 15;
 
+    // cluster merge: first phase of the cluster barrier, arrived at once and waited for only before the first access to
+    // the leader's shared memory (every CTA of the cluster must have started by then; by that time it long has)
+    if (p.cluster_merge && gridDim.x > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     // launched with the programmatic-dependent-launch attribute: q / k_new / v_new and the length array
     // may come from the kernel just before this one
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -198,10 +212,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(Dec
     const int k_end = min(len, k_begin + p.chunk);                  // cached keys [k_begin, k_end)
     const bool owns_new = !nothing && p.append && (len / p.chunk == split);
     const int ntiles = (!nothing && k_end > k_begin) ? (k_end - k_begin + kTile - 1) / kTile : 0;
-    // cluster merge: where this CTA parks its per-head (acc, m, l) until the leader's ring is free to receive them
-    constexpr int kParkOffset = kStages * 2 * kTile * 128 * static_cast<int>(sizeof(T)) - 4096;   // the ring's last 4 KB
-    static_assert(NREP * (D + 2) * 4 <= 4096 && 16 * NREP * (D + 2) * 4 <= kParkOffset, "park area and the leader's receive area must not overlap");
-
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], CW); }
         sm->abort_flag = 0;
@@ -349,10 +359,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(Dec
                     acc += go[(g * NREP + h) * 128 + d] * w;
                 }
                 if (p.cluster_merge) {
-                    // parked in this CTA's own (drained) ring, clear of the go/gm/gl buffers other threads still read
-                    float* tx = reinterpret_cast<float*>(smem_raw + kParkOffset) + h * (D + 2);
-                    tx[d] = acc;
-                    if (d == 0) { tx[D] = M; tx[D + 1] = L; }
+                    // this split's row of the receive area, in this CTA's own shared memory (the leader's is final)
+                    if (!nothing) {
+                        float* own = rx + (split * NREP + h) * (D + 2);
+                        own[d] = acc;
+                        if (d == 0) { own[D] = M; own[D + 1] = L; }
+                    }
                 } else {
                     float* out = wsp + ((static_cast<long long>(b) * p.Hkv + kvh) * nsplits + split) * NREP * (D + 2) + h * (D + 2);
                     out[d] = acc / L;
@@ -363,47 +375,45 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(Dec
     }
 
     if (p.cluster_merge) {
-        // The splits of this (batch, kv_head) are one cluster: every member parks its per-head (acc, m, l) in the
-        // leader's shared memory (distributed shared memory; the leader's ring is free after the first barrier),
-        // the leader merges them in split order and writes the final rows -- no combine kernel, no workspace trip.
+        // The splits of this (batch, kv_head) are one cluster: every member forwards its per-head (acc, m, l) into the
+        // leader's receive area (ring stage 1, never loaded here, so nobody waits for the leader's ring to drain); after the
+        // cluster barrier the leader merges them in split order and writes the final rows -- no combine kernel, no
+        // workspace trip.
         const unsigned nsp = gridDim.x;
-        unsigned rank = 0;
-        if (nsp > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-        float* rx = reinterpret_cast<float*>(smem_raw);              // leader: [nsp][NREP][D + 2]
         if (nsp > 1) {
             __syncwarp();
-            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-            if (tid < 128 && rank != 0 && !nothing) {
-                const float* tx = reinterpret_cast<const float*>(smem_raw + kParkOffset);
-                uint32_t base;
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base) : "r"(smem_u32(rx)), "r"(0));
+            asm volatile("barrier.cluster.wait.aligned;" ::: "memory");           // phase 1: every member is running
+            if (split != 0 && !nothing && tid < 128) {
+                // each thread forwards what it wrote itself: column tid of every head (thread 0 also m and l)
+                uint32_t dst;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(smem_u32(rx + split * NREP * (D + 2))), "r"(0));
+                const float* own = rx + split * NREP * (D + 2);
 #pragma unroll
                 for (int h = 0; h < NREP; ++h) {
-                    const uint32_t a = base + ((rank * NREP + h) * (D + 2)) * 4;
-                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a + tid * 4), "f"(tx[h * (D + 2) + tid]) : "memory");
+                    const uint32_t a = dst + h * (D + 2) * 4;
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a + tid * 4), "f"(own[h * (D + 2) + tid]) : "memory");
                     if (tid == 0) {
-                        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a + D * 4), "f"(tx[h * (D + 2) + D]) : "memory");
-                        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a + (D + 1) * 4), "f"(tx[h * (D + 2) + D + 1]) : "memory");
+                        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a + D * 4), "f"(own[h * (D + 2) + D]) : "memory");
+                        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a + (D + 1) * 4), "f"(own[h * (D + 2) + D + 1]) : "memory");
                     }
                 }
             }
-            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            __syncwarp();
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // phase 2: the rows are in the leader's memory
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        } else {
+            __syncthreads();
         }
-        if (rank == 0 && tid < 128) {
+        if (split == 0 && tid < 128) {
             const int d = tid;
+            // members without keys stored nothing: splits beyond the sequence are a suffix
             const unsigned nvalid = min(nsp, static_cast<unsigned>((total + p.chunk - 1) / p.chunk));
 #pragma unroll
             for (int h = 0; h < NREP; ++h) {
-                // a member without keys parked nothing: its slot is skipped (splits beyond the sequence are a suffix)
-                const float* own = reinterpret_cast<const float*>(smem_raw + kParkOffset) + h * (D + 2);
-                const float m0 = nothing ? -INFINITY : own[D];
-                float M = m0;
-                for (unsigned r = 1; r < nvalid; ++r) M = fmaxf(M, rx[(r * NREP + h) * (D + 2) + D]);
-                float L = (m0 == -INFINITY) ? 0.f : own[D + 1] * fast_exp2(m0 - M);
-                float acc = (m0 == -INFINITY) ? 0.f : own[d] * fast_exp2(m0 - M);
-                for (unsigned r = 1; r < nvalid; ++r) {
+                float M = -INFINITY;
+                for (unsigned r = 0; r < nvalid; ++r) M = fmaxf(M, rx[(r * NREP + h) * (D + 2) + D]);
+                float L = 0.f, acc = 0.f;
+                for (unsigned r = 0; r < nvalid; ++r) {
                     const float* pr = rx + (r * NREP + h) * (D + 2);
                     const float mr = pr[D];
                     const float w = (mr == -INFINITY) ? 0.f : fast_exp2(mr - M);
@@ -528,23 +538,27 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
             if (int rc = launch_decode_gqa_mma_split<T, NREP>(s, p)) return rc;
         }
     } else if constexpr (NREP != 8) {       // (the CUDA-core kernel is never the choice for 8-head groups)
-        size_t smem = static_cast<size_t>(kStages) * 2 * kTile * D * sizeof(T) + D * sizeof(float) + D * sizeof(T) + 2 * CW * 16 * sizeof(float) + sizeof(DecodeSmem<CW, kStages>);
-        static_assert(2 * CW * NREP * 128 * 4 + 2 * 2 * CW * NREP * 4 <= kStages * 2 * kTile * 128 * 2, "merge buffers must fit in the ring");
-        static_assert(kMaxClusterSplits * NREP * 130 * 4 <= kStages * 2 * kTile * 128 * 2, "the cluster's partials must fit in the leader's ring");
+        constexpr size_t kBaseSmem = decode_base_smem<T, NREP, CW, kStages>();
+        constexpr size_t kRxRow = NREP * (D + 2) * sizeof(float);                       // one split's (acc, m, l) per head
+        static_assert(2 * CW * NREP * 128 * 4 + 2 * 2 * CW * NREP * 4 <= 2 * kTile * 128 * sizeof(T), "merge buffers must fit in the first ring stage (the second may hold the cluster receive area)");
         static thread_local int configured_dev = -1;
         int dev = 0;
         VB200_CUDA_TRY(cudaGetDevice(&dev));
         if (configured_dev != dev) {
-            VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                static_cast<int>(kBaseSmem)));
             VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
             configured_dev = dev;
         }
-        // Up to 16 splits per (batch, kv_head): they run as one thread-block cluster that merges its partials through
-        // distributed shared memory and writes the final rows -- the combine kernel and the workspace round trip drop
-        // out.  Not when the caller wants the partial record or the length array advanced (the combine kernel does
-        // that after every CTA of the grid has read the lengths).
+        // Up to 16 one-tile splits per (batch, kv_head): they run as one thread-block cluster that merges its partials
+        // through distributed shared memory and writes the final rows -- the combine kernel and the workspace round
+        // trip drop out.  Not when the caller wants the partial record or the length array advanced (the combine
+        // kernel does that after every CTA of the grid has read the lengths), nor when a CTA streams more than one
+        // tile (the receive area is the ring's second stage).
         DecodeParams q = p;
-        q.cluster_merge = (!p.partial_out && !(p.seq_lens && p.advance_lens && p.append) && p.num_splits <= kMaxClusterSplits) ? 1 : 0;
+        constexpr size_t kStageBytesHost = 2 * kTile * D * sizeof(T);
+        q.cluster_merge = (!p.partial_out && !(p.seq_lens && p.advance_lens && p.append) && p.num_splits <= kMaxClusterSplits &&
+                           p.chunk <= kTile && p.num_splits * kRxRow <= kStageBytesHost) ? 1 : 0;
         dim3 grid(p.num_splits, p.Hkv, p.B);
         if (q.cluster_merge && p.num_splits > 8) {
             // a size above the portable 8 must fit one GPC of this device: asked once per size
@@ -555,7 +569,7 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
                 cudaLaunchConfig_t probe{};
                 probe.gridDim = grid;
                 probe.blockDim = dim3((CW + 1) * 32);
-                probe.dynamicSmemBytes = smem;
+                probe.dynamicSmemBytes = kBaseSmem;
                 cudaLaunchAttribute pa[1];
                 pa[0].id = cudaLaunchAttributeClusterDimension;
                 pa[0].val.clusterDim.x = static_cast<unsigned>(p.num_splits);
@@ -571,6 +585,7 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
             if (fits[p.num_splits] < 0) q.cluster_merge = 0;
         }
         need_combine = !q.cluster_merge;
+        const size_t smem = kBaseSmem;
         profile_mark_begin(s);
         {
             cudaLaunchConfig_t cfg{};
