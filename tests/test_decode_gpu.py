@@ -88,6 +88,46 @@ def test_decode_ragged_rope_append_steps(lib, cuda, oracle, num_splits):
         assert not gk[b, :, cur[b]:].any() and not gv[b, :, cur[b]:].any()
 
 
+@pytest.mark.parametrize("num_splits", [0, 11, 15])
+@pytest.mark.parametrize("n_rep", [1, 4])
+def test_decode_ragged_no_advance_cluster_merge(lib, cuda, oracle, num_splits, n_rep):
+    """Ragged lengths with one-tile splits and no length advance: the splits of a (sequence, kv head) run as one
+    thread-block cluster (sizes above 8 included) that merges its own partials; short sequences leave most members
+    of their cluster without keys.  RoPE at position len, append, attend."""
+    import torch
+    from vesper_b200 import capi
+    B, Hkv, D, cap = 5, 2, 128, 800
+    Hq = Hkv * n_rep
+    lens = [1, 63, 64, 700, 512]
+    rng = np.random.default_rng(57 + n_rep)
+    k, v = make_cache(rng, B, Hkv, cap, D, lens, bf16_round)
+    tk, tv = to_torch(k, torch.bfloat16, cuda), to_torch(v, torch.bfloat16, cuda)
+    seq = torch.tensor(lens, dtype=torch.int32, device=cuda)
+    scale = float(1.0 / np.sqrt(D))
+    q = bf16_round(rng.standard_normal((B, Hq, 1, D), dtype=np.float32))
+    kn = bf16_round(rng.standard_normal((B, Hkv, 1, D), dtype=np.float32))
+    vn = bf16_round(rng.standard_normal((B, Hkv, 1, D), dtype=np.float32))
+    tq, tkn, tvn = (to_torch(x, torch.bfloat16, cuda) for x in (q, kn, vn))
+    o = torch.empty_like(tq)
+    lse = torch.empty(B, Hq, dtype=torch.float32, device=cuda)
+    capi.decode(tq, o, tk, tv, scale=scale, k_new=tkn, v_new=tvn, lse=lse, theta=10000.0, seq_lens=seq,
+                advance_lens=False, max_len=max(lens) + 1, num_splits=num_splits)
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)
+    assert seq.tolist() == lens                                   # not advanced
+    for b in range(B):
+        kc1, vc1 = k[b:b + 1].copy(), v[b:b + 1].copy()
+        want_o, want_lse, n = oracle.gqa_attention_cached(q[b:b + 1], kn[b:b + 1], vn[b:b + 1], kc1, vc1, lens[b], lens[b])
+        assert n == lens[b] + 1
+        assert maxabs(from_torch(o)[b], want_o[0]) <= 1e-2, f"seq {b}"
+        assert maxabs(from_torch(lse)[b], want_lse[0, :, 0]) <= 1e-3, f"seq {b}"
+    # the new rows were appended at position len of each sequence, nothing beyond
+    gk, gv = from_torch(tk), from_torch(tv)
+    for b in range(B):
+        assert np.array_equal(gv[b, :, lens[b]], vn[b, :, 0])
+        assert not gk[b, :, lens[b] + 1:].any() and not gv[b, :, lens[b] + 1:].any()
+
+
 def test_decode_sharded_partials_combine(lib, cuda, oracle):
     """Sequence-sharded form on one GPU: R shards of the KV sequence each emit (O/l, m, l);
     vb200_lse_combine merges them to the unsharded result (the algebra of
