@@ -119,25 +119,27 @@ def cpu_prefill_sample(target_seconds=12.0, threads=None, S=None, total_slices=N
     threads = threads or max(1, min(os.cpu_count() or 1, 64))
     S, D = S or C2["S"], C2["D"]
     total_slices = total_slices or C2["B"] * C2["Hq"]
-    rng = np.random.default_rng(1)
-    q = (0.5 * rng.standard_normal((1, 1, S, D))).astype(np.float32)
-    k = (0.5 * rng.standard_normal((1, 1, S, D))).astype(np.float32)
-    v = (0.5 * rng.standard_normal((1, 1, S, D))).astype(np.float32)
     scale = float(1.0 / np.sqrt(D))
 
-    def one_slice():
+    def make_slice(seed):
+        rng = np.random.default_rng(seed)
+        return tuple((0.5 * rng.standard_normal((1, 1, S, D))).astype(np.float32) for _ in range(3))
+
+    def one_slice(qkv):
+        q, k, v = qkv
         qr = eng.apply_rope(q, 0, C2["theta"])
         kr = eng.apply_rope(k, 0, C2["theta"])
         eng.flash_attention(qr, kr, v, scale, True)
 
-    t0 = time.time(); one_slice(); t_one = time.time() - t0          # calibrate (single thread)
+    t0 = time.time(); one_slice(make_slice(1)); t_one = time.time() - t0          # calibrate (single thread)
     per_thread = max(1, int(target_seconds / max(t_one, 1e-3)))
     per_thread = min(per_thread, 64)
     done = [0] * threads
+    data = [make_slice(1 + i) for i in range(threads)]            # one distinct (batch, head) slice per thread
 
     def work(i):
         for _ in range(per_thread):
-            one_slice()
+            one_slice(data[i])
             done[i] += 1
 
     ths = [threading.Thread(target=work, args=(i,)) for i in range(threads)]
@@ -148,8 +150,9 @@ def cpu_prefill_sample(target_seconds=12.0, threads=None, S=None, total_slices=N
     slices = sum(done)
     flops = slices * 4.0 * D * S * (S + 1) / 2.0
     return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=threads, kind=kind,
-                sample=f"{slices} of {total_slices} (batch, head) slices of {what} (S={S}, D={D}, fp32, RoPE + causal flash), "
-                       f"{threads} host threads x {per_thread} slices, {dt:.1f} s; single-thread slice {t_one * 1e3:.0f} ms"), dt
+                sample=f"{slices} slice passes = {threads} distinct seeded (batch, head) slices of {what} (one per host thread; the workload has "
+                       f"{total_slices}) x {per_thread} repeats each (S={S}, D={D}, fp32, RoPE + causal flash), {dt:.1f} s; "
+                       f"single-thread slice {t_one * 1e3:.0f} ms"), dt
 
 
 def run_reference(args):
@@ -216,6 +219,35 @@ class Ctx:
         return self.torch.cuda.Event(enable_timing=True)
 
 
+def bind_to_gpu_numa_node(torch, local):
+    """Pin this process (and so the pages its pinned buffers are first touched on, and its copy threads) to the CPUs of
+    the NUMA node the GPU hangs off, read from sysfs.  Returns what was done, for the JSON line."""
+    info = {"numa_node": None, "cpus": None}
+    try:
+        try:
+            props = torch.cuda.get_device_properties(local)
+            bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        except AttributeError:
+            out = subprocess.run(["nvidia-smi", f"--id={local}", "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                                 capture_output=True, text=True, timeout=20).stdout.strip().lower()
+            bdf = out[-12:]                                      # "00000000:1b:00.0" -> "0000:1b:00.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read().strip())
+        info["numa_node"] = node
+        if node < 0:
+            return info
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            info["cpus"] = len(cpus)
+    except (OSError, ValueError, subprocess.SubprocessError):
+        pass
+    return info
+
+
 def bench_prefill(cx, K, W, quick=False):
     """Headline: C2 prefill.  Returns the fields of the JSON line that come from it."""
     import ctypes as C
@@ -223,6 +255,7 @@ def bench_prefill(cx, K, W, quick=False):
     torch, capi, L, dev = cx.torch, cx.capi, cx.L, cx.dev
     c = C2
     B, Hq, Hkv, S, D = c["B"], c["Hq"], c["Hkv"], c["S"], c["D"]
+    placement = bind_to_gpu_numa_node(torch, cx.local)          # before the pinned host buffers are allocated
     g = torch.Generator(device="cpu").manual_seed(1 + cx.rank)
     hq = (0.5 * torch.randn(B, Hq, S, D, generator=g)).to(torch.bfloat16).pin_memory()
     hk = (0.5 * torch.randn(B, Hkv, S, D, generator=g)).to(torch.bfloat16).pin_memory()
@@ -360,7 +393,8 @@ def bench_prefill(cx, K, W, quick=False):
                      "peak_source": pk["source"] + " (burst cuBLAS bf16)", "frac_of_sustained": achieved / pk["tf_sustained"],
                      "frac_of_nominal_2250": achieved / 2250.0, "kernel": "prefill_sm100_kernel", "kernel_ms": kern_avg_ms,
                      "traffic": cx.traffic.get("prefill_sm100_bytes_per_launch")},
-        "e2e": {"value": cx.world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "e2e": {"value": cx.world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "value_per_gpu": flops / (e2e_ms * 1e-3) / 1e12,
+                "host_placement": placement,
                 "h2d_bytes_per_step": (hq.numel() + hk.numel() + hv.numel()) * 2, "d2h_bytes_per_step": ho.numel() * 2 + hl.numel() * 4,
                 "ms_per_step": e2e_ms, "how": f"the batch as {len(slices)} sequence slices pipelined over copy-in / compute / copy-out streams",
                 "ms_per_step_serial_single_stream": e2e_serial_ms, "result_copied_back_matches_device": e2e_ok},
@@ -433,6 +467,8 @@ def bench_decode(cx, nsteps, W):
         "roofline": {"bound": "hbm", "achieved": kgbs, "peak": pk["hbm"], "unit": "GB/s", "frac": (kgbs / pk["hbm"]) if kgbs else None,
                      "peak_source": pk["source"], "frac_of_nominal_8TBs": (kgbs / 8000.0) if kgbs else None,
                      "kernel": "decode_gqa_mma_kernel", "kernel_ms": kern_ms / max(1, nprof),
+                     "step_achieved": dec_bytes / (dec_ms * 1e-3) / 1e9, "step_frac": dec_bytes / (dec_ms * 1e-3) / 1e9 / pk["hbm"],
+                     "step_frac_of_nominal_8TBs": dec_bytes / (dec_ms * 1e-3) / 1e9 / 8000.0,
                      "traffic": cx.traffic.get("decode_splitkv_bytes_per_launch")},
     }
 
@@ -507,6 +543,47 @@ def bench_sharded(cx, nsteps=50):
             ms_graph = cx.max_over_ranks(s0.elapsed_time(s1)) / nsteps
         except Exception as e:
             exchange_error = f"graph: {type(e).__name__}: {e}"[:200]
+    # correctness of what was timed (a 1-GPU test box cannot run the N > 1 parity tests): the chosen path's result
+    # against the all-gather path's, bit for bit, and against the CPU oracle's attention over the whole 131072-key
+    # context for 4 sampled query heads (their KV heads' shards are collected on rank 0 for that)
+    paths_bit_identical, max_abs_err, err_heads = None, None, [0, 21, 42, 63]
+    step_gather()
+    cx.sync_all()
+    out_gather = out4.clone()
+    if exchange is not None:
+        out4.zero_()
+        step_fused()
+        cx.sync_all()
+        same = bool(torch.equal(out4, out_gather))
+        if ms_graph is not None:
+            out4.zero_()
+            graph.replay()
+            cx.sync_all()
+            same = same and bool(torch.equal(out4, out_gather))
+        flag = torch.tensor([1 if same else 0], dtype=torch.int32, device=dev)
+        cx.dist.all_reduce(flag, op=cx.dist.ReduceOp.MIN)
+        paths_bit_identical = bool(flag.item())
+    try:
+        n_rep = Hq // Hkv
+        kv_sel = [h // n_rep for h in err_heads]
+        k_loc, v_loc = ks[:, kv_sel].contiguous(), vs[:, kv_sel].contiguous()
+        if world > 1:
+            k_all = [torch.empty_like(k_loc) for _ in range(world)]
+            v_all = [torch.empty_like(v_loc) for _ in range(world)]
+            cx.dist.all_gather(k_all, k_loc)
+            cx.dist.all_gather(v_all, v_loc)
+            k_full, v_full = torch.cat(k_all, dim=2), torch.cat(v_all, dim=2)
+        else:
+            k_full, v_full = k_loc, v_loc
+        if cx.rank == 0:
+            from oracle.binding import Oracle          # the checker, outside every timed region
+            orc = Oracle()
+            q_rot = orc.apply_rope(q4[:, err_heads].float().cpu().numpy(), L4, 10000.0)
+            want, _ = orc.decode_ragged(q_rot[:, :, 0], k_full.float().cpu().numpy(), v_full.float().cpu().numpy(), [L4])
+            got = out_gather.view(Bq, Hq, D)[:, err_heads].float().cpu().numpy()
+            max_abs_err = float(np.abs(got - want).max())
+    except Exception as e:
+        exchange_error = (exchange_error or "") + f" oracle check: {type(e).__name__}: {e}"[:200]
     candidates = [("all-gather + combine", ms_gather)] + ([("fused peer-memory exchange", ms_fused)] if ms_fused else []) + \
                  ([("fused peer-memory exchange, CUDA-graph replay", ms_graph)] if ms_graph else [])
     path, ms = min(candidates, key=lambda c: c[1])
@@ -518,6 +595,8 @@ def bench_sharded(cx, nsteps=50):
         "ms_per_step": ms, "scaling": "strong", "path": path,
         "ms_per_step_all_gather_path": ms_gather, "ms_per_step_fused_exchange": ms_fused, "ms_per_step_fused_exchange_graph": ms_graph,
         "exchange_error": exchange_error,
+        "paths_bit_identical": paths_bit_identical, "max_abs_err": max_abs_err,
+        "max_abs_err_what": f"query heads {err_heads} over the whole context against the CPU oracle (gate 1e-2, bf16)",
         "config": {"workload": f"split-KV decode B=1 Hq={Hq} Hkv={Hkv} D={D} bf16, context {L4} sharded over {world} GPU(s); "
                                f"partial (O/l, m, l) records of {Hq * (D + 2) * 4} B per rank exchanged, then LSE merge"},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": cx.peaks["hbm"], "unit": "GB/s per GPU",

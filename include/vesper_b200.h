@@ -31,7 +31,11 @@ typedef enum vb200_status {
     VB200_ERR_WORKSPACE = -4,     /* workspace missing or too small                   */
     VB200_ERR_CUDA = -5,          /* a CUDA runtime/driver call failed                */
     VB200_ERR_NO_DEVICE = -6,     /* no usable sm_100 device                          */
-    VB200_ERR_KERNEL_TIMEOUT = -7 /* a bounded in-kernel wait expired (status word)   */
+    VB200_ERR_KERNEL_TIMEOUT = -7,/* a bounded in-kernel wait expired (status word)   */
+    VB200_ERR_CACHE_OVERFLOW = -8 /* a decode step met a sequence whose new token does
+                                     not fit the cache or the planned max_len (status
+                                     word; the reference throws from KVCache::update,
+                                     src/nn/transformer.cpp:62-66)                     */
 } vb200_status;
 
 typedef enum vb200_dtype {
@@ -89,6 +93,12 @@ typedef struct vb200_prefill_args {
     vb200_rope rope;
     vb200_tensor4 k_cache, v_cache; /* [B,Hkv,cap,D]; ptr NULL = no cache            */
     int32_t cache_cap;
+    int32_t cache_read_only;     /* 1: the cache already holds the (rotated) keys and
+                                    the values of rows [0, start_pos+T); k and v are
+                                    ignored (may be NULL) and nothing is written to
+                                    the cache -- the T < L shape of
+                                    scaled_dot_product_attention,
+                                    src/nn/functional.cpp:399-421                     */
     void* workspace;             /* vb200_prefill_workspace_bytes() bytes, 256-aligned */
     size_t workspace_bytes;
 } vb200_prefill_args;
@@ -123,6 +133,13 @@ int vb200_prefill_fwd(const vb200_prefill_args* a);
  * int32[B], nullable) gives the query's absolute position for RoPE when it is
  * not pos_offset + seq_lens[b] (i.e. on every shard but the last);
  * append_enabled = 0 makes a shard attend without appending.
+ *
+ * Capacity: a sequence whose new token would not fit -- seq_lens[b] + 1 greater
+ * than cache_cap, or than the max_len the step was planned for -- is not
+ * appended, its length is not advanced, it attends to the keys it has, and the
+ * device status word records the sequence: vb200_check_kernel_status then
+ * returns VB200_ERR_CACHE_OVERFLOW (with seq_lens == NULL the same condition is
+ * refused on the host with VB200_ERR_INVALID_ARG).
  */
 typedef struct vb200_decode_args {
     uint32_t struct_size;
@@ -154,6 +171,13 @@ typedef struct vb200_decode_args {
 } vb200_decode_args;
 
 size_t vb200_decode_workspace_bytes(const vb200_decode_args* a);
+/* The largest vb200_decode_workspace_bytes of any step these arguments can make
+ * as the sequences grow: the maximum over max_len = 1 .. cache_cap, with and
+ * without seq_lens (the plan is not monotone in max_len: a shorter step can use
+ * more, smaller splits).  Size a buffer once with this and reuse it for every
+ * step of a generation (what TransformerLM::forward_with_cache and
+ * Generator::generate need, src/models/transformer.cpp:152-188). */
+size_t vb200_decode_workspace_bytes_max(const vb200_decode_args* a);
 int vb200_decode_fwd(const vb200_decode_args* a);
 
 /* The same decode step for callers that cannot supply a workspace and may not
@@ -171,7 +195,9 @@ int vb200_decode_fwd(const vb200_decode_args* a);
  *     contents (none of it needs clearing: a step writes each slot before it
  *     reads it).  Calls that may overlap on one GPU race: keep them on one stream.
  *   - The first call on a device resolves the array's device address; make that
- *     first call before starting any stream capture. */
+ *     first call before starting any stream capture.  The address is kept for the
+ *     life of the process: after a cudaDeviceReset() of that device do not call
+ *     this entry point on it again. */
 #define VB200_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
 int vb200_decode_fwd_static(const vb200_decode_args* a);
 
@@ -285,8 +311,9 @@ void vb200_reset_launch_count(void);
  * leave it on in production. */
 int vb200_profile_enable(int enable);
 int vb200_profile_read(double* total_ms, uint64_t* launches);
-/* Reads and clears the device-side status word that bounded waits set
- * (synchronises the given stream).  Returns VB200_OK or VB200_ERR_KERNEL_TIMEOUT. */
+/* Reads and clears the device-side status word that bounded waits and the decode
+ * kernels' capacity check set (synchronises the given stream).  Returns VB200_OK,
+ * VB200_ERR_KERNEL_TIMEOUT or VB200_ERR_CACHE_OVERFLOW. */
 int vb200_check_kernel_status(int device, void* stream);
 
 #ifdef __cplusplus

@@ -50,6 +50,13 @@ int vb200_linear_bias(int device, void* stream, const void* x, int64_t ldx, cons
                       const float* bias, void* out, int64_t ldo, int32_t M, int32_t N, int32_t K,
                       int32_t epilogue, int32_t splits);
 
+/* The same product in fp32 (x, W, out fp32; bias fp32 [N] or NULL; any M, N, K and strides >= the row), on CUDA
+ * cores: the number format of the reference's own modules (nn::Linear::forward, src/nn/linear.cpp:41-48, on fp32
+ * tensors through gemm_cuda_dispatch, src/ops/cuda/gemm.cu:257-388), kept so that fp32 modules are not silently
+ * down-converted.  Not tuned: the serving path is bf16. */
+int vb200_linear_f32(int device, void* stream, const float* x, int64_t ldx, const float* w, int64_t ldw, const float* bias,
+                     float* out, int64_t ldo, int32_t M, int32_t N, int32_t K);
+
 /* The general form, with every option of the GEMM kernels.  Beyond bias and epilogue it carries the two
  * halves of a DEFERRED RMSNorm, which removes the norm kernels from a decode step:
  *     rmsnorm(h) * g @ W^T  =  inv_rms(h) * ((h * g) @ W^T)        (inv_rms is one scalar per row)

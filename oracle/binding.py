@@ -34,9 +34,10 @@ def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 
 
-def build_oracle(ref: bool = True) -> None:
-    """Compile liboracle.so (always) and _ref (only when the reference tree exists)."""
-    targets = ["oracle"] + (["ref"] if ref else [])
+def build_oracle(ref: bool = True, dropin: bool = False) -> None:
+    """Compile liboracle.so (always), _ref (only when the reference tree exists) and, on request, the reference's
+    own test programs linked against this repository's CUDA backend (_ref/dropin; needs nvcc and the built library)."""
+    targets = ["oracle"] + (["ref"] if ref else []) + (["dropin"] if dropin else [])
     subprocess.check_call(["make", "-s", "-C", HERE, "-j8"] + targets)
 
 
@@ -386,6 +387,42 @@ class Ref:
 
     def gqa(self, C_, Hq, Hkv, max_seq, theta, wqkv, wo):
         return Ref.GQA(self, C_, Hq, Hkv, max_seq, theta, wqkv, wo)
+
+    class MHA:
+        """nn::MultiHeadAttention (src/nn/transformer.cpp:97-216) with caller-set c_attn / c_proj weights and biases."""
+
+        def __init__(self, ref, C_, H, use_rope, w_attn, b_attn, w_proj, b_proj):
+            self.ref = ref
+            L = ref.lib
+            L.ref_mha_new.restype = C.c_void_p
+            L.ref_mha_new.argtypes = [C.c_int, C.c_int, C.c_int] + [_f32p] * 4
+            L.ref_mha_free.argtypes = [C.c_void_p]
+            L.ref_mha_forward.argtypes = [C.c_void_p, _f32p, _f32p, _i64, _i64, _i64, C.c_int, C.c_int, C.c_void_p, C.c_int]
+            arrs = [_f32(a) for a in (w_attn, b_attn, w_proj, b_proj)]
+            self.h = L.ref_mha_new(C_, H, int(use_rope), *[_fp(a) for a in arrs])
+            if not self.h:
+                raise RuntimeError(L.ref_last_error().decode())
+
+        def _run(self, x, mode, causal=False, cache=None, start_pos=0):
+            x = _f32(x)
+            B, T, C_ = x.shape
+            y = np.empty_like(x)
+            self.ref._chk(self.ref.lib.ref_mha_forward(self.h, _fp(x), _fp(y), B, T, C_, mode, int(causal), cache.h if cache else None, start_pos))
+            return y
+
+        def forward(self, x, causal=None):
+            return self._run(x, 0) if causal is None else self._run(x, 1, causal)
+
+        def forward_cached(self, cache, x, start_pos):
+            return self._run(x, 2, False, cache, start_pos)
+
+        def __del__(self):
+            if getattr(self, "h", None):
+                self.ref.lib.ref_mha_free(self.h)
+                self.h = None
+
+    def mha(self, C_, H, use_rope, w_attn, b_attn, w_proj, b_proj):
+        return Ref.MHA(self, C_, H, use_rope, w_attn, b_attn, w_proj, b_proj)
 
     def flash_attention_bwd(self, d_out, q, k, v, out, lse, scale, causal=True):
         d_out, q, k, v, out, lse = _f32(d_out), _f32(q), _f32(k), _f32(v), _f32(out), _f32(lse)

@@ -251,6 +251,33 @@ int ref_gqa_forward_cached(void* m, void* cache, const float* x, float* y,
     } catch (const std::exception& e) { g_err = e.what(); return -1; }
 }
 
+// ---- module level: MultiHeadAttention (src/nn/transformer.cpp:97-216) with caller-supplied weights ----
+// c_attn: weight [3C, C] + bias [3C]; c_proj: weight [C, C] + bias [C].
+void* ref_mha_new(int C, int H, int use_rope, const float* w_attn, const float* b_attn, const float* w_proj, const float* b_proj) {
+    try {
+        auto* m = new vesper::nn::MultiHeadAttention(C, H, 0.0f, use_rope != 0);
+        m->eval();
+        m->c_attn.weight.copy_from_host(w_attn);
+        m->c_attn.bias.copy_from_host(b_attn);
+        m->c_proj.weight.copy_from_host(w_proj);
+        m->c_proj.bias.copy_from_host(b_proj);
+        return m;
+    } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
+}
+void ref_mha_free(void* m) { delete static_cast<vesper::nn::MultiHeadAttention*>(m); }
+// mode 0: forward(x) (non-causal by default, :108-110); 1: forward(x, causal); 2: forward(x, cache, start_pos)
+int ref_mha_forward(void* m, const float* x, float* y, int64_t B, int64_t T, int64_t C, int mode, int causal, void* cache, int start_pos) {
+    try {
+        vesper::autograd::NoGradGuard ng;
+        auto* g = static_cast<vesper::nn::MultiHeadAttention*>(m);
+        Tensor tx = from_host(x, {B, T, C});
+        Tensor ty = mode == 0 ? g->forward(tx) : mode == 1 ? g->forward(tx, causal != 0)
+                                                           : g->forward(tx, static_cast<vesper::nn::KVCache*>(cache), start_pos);
+        to_host(ty, y);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+
 // ops::flash_attention_backward (src/ops/flash_attention.cpp:165-215 -> CPU backward :366-482)
 int ref_flash_attention_backward(const float* d_out, const float* q, const float* k, const float* v,
                                  const float* out, const float* lse, float* dq, float* dk, float* dv,

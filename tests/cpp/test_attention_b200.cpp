@@ -220,6 +220,22 @@ static void test_sdpa_routes() {                // src/nn/functional.cpp:370-422
         Tensor o = nn::functional::scaled_dot_product_attention(to_cuda(q, {B, H, S, D}), to_cuda(k, {B, H, S, D}), to_cuda(v, {B, H, S, D}), true);
         CHECK(allclose(to_host(o), o_cpu, 1e-3f, 1e-4f));
     }
+    // the decode shape: one query row against L cached keys, non-causal (src/nn/functional.cpp:399-421); key and
+    // value are inputs and must come back untouched.  fp32 / head_dim 64 takes the read-only-cache prefill route,
+    // bf16 / head_dim 128 the split-KV decode kernel.
+    struct Case { int L, D; DType dt; float atol; };
+    for (const Case& c : {Case{37, 64, DType::Float32, 1e-4f}, Case{300, 128, DType::BFloat16, 1e-2f}, Case{300, 128, DType::Float16, 2e-3f}}) {
+        const int Bq = 2, Hh = 4;
+        size_t nq = static_cast<size_t>(Bq) * Hh * c.D, nk = nq * c.L;
+        auto q = round_like(randn(nq, 34, 0.5f), c.dt), k = round_like(randn(nk, 35, 0.5f), c.dt), v = round_like(randn(nk, 36, 0.5f), c.dt);
+        std::vector<float> o_cpu(nq);
+        vo_sdpa_standard(q.data(), k.data(), v.data(), o_cpu.data(), nullptr, Bq, Hh, 1, c.L, c.D, 0);
+        Tensor tk = to_cuda(k, {Bq, Hh, c.L, c.D}, c.dt), tv = to_cuda(v, {Bq, Hh, c.L, c.D}, c.dt);
+        Tensor o = nn::functional::scaled_dot_product_attention(to_cuda(q, {Bq, Hh, 1, c.D}, c.dt), tk, tv, false);
+        CHECK(o.shape() == (std::vector<int64_t>{Bq, Hh, 1, c.D}));
+        CHECK(allclose(to_host(o), o_cpu, 0.f, c.atol));
+        CHECK(to_host(tk) == k && to_host(tv) == v);
+    }
 }
 
 static void test_flash_backward() {             // tests/test_flash_attention.cpp:292-339: d(sum(out)) exists, finite, non-zero

@@ -120,6 +120,24 @@ def main():
     save("gqa_module_forward", wqkv=wqkv, wo=wo, x=x, y=g.forward(x, True),
          dims=np.array([Cdim, Hq, Hkv, T], np.int32))
 
+    # -- module level: MultiHeadAttention (src/nn/transformer.cpp:97-216), c_attn = Linear(C, 3C) and c_proj with BIAS:
+    #    forward(x) (non-causal, :108-110), forward(x, causal=True), and forward(x, cache, pos) as a prompt pass of
+    #    T=9 then two single-token steps (Hkv == Hq: the reference's cached path is right); with and without RoPE.
+    Cm, Hm, Tm = 64, 4, 9
+    for tag, use_rope in (("rope", True), ("norope", False)):
+        rngm = np.random.default_rng(900 + int(use_rope))
+        w_attn = (0.1 * rngm.standard_normal((3 * Cm, Cm))).astype(np.float32)
+        b_attn = (0.1 * rngm.standard_normal(3 * Cm)).astype(np.float32)
+        w_proj = (0.1 * rngm.standard_normal((Cm, Cm))).astype(np.float32)
+        b_proj = (0.1 * rngm.standard_normal(Cm)).astype(np.float32)
+        x = rngm.standard_normal((2, Tm + 2, Cm), dtype=np.float32)
+        m = r.mha(Cm, Hm, use_rope, w_attn, b_attn, w_proj, b_proj)
+        c = r.kvcache(2, Hm, 16, Cm // Hm)
+        save("mha_module_" + tag, w_attn=w_attn, b_attn=b_attn, w_proj=w_proj, b_proj=b_proj, x=x,
+             y_default=m.forward(x[:, :Tm]), y_causal=m.forward(x[:, :Tm], True),
+             y_cached_prefill=m.forward_cached(c, x[:, :Tm], 0), y_cached_step1=m.forward_cached(c, x[:, Tm:Tm + 1], Tm),
+             y_cached_step2=m.forward_cached(c, x[:, Tm + 1:Tm + 2], Tm + 1), dims=np.array([Cm, Hm, Tm, int(use_rope)], np.int32))
+
     # -- ops::flash_attention_backward (src/ops/flash_attention.cpp:165-215, CPU form :366-482), the shapes of
     #    tests/test_flash_attention.cpp:295,345 plus a ragged one, causal and not
     bw = {}

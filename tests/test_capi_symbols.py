@@ -62,6 +62,39 @@ def test_decode_workspace_plan_is_consistent(lib):
     assert lib.vb200_decode_workspace_bytes(C.byref(d)) < n
 
 
+def test_decode_workspace_max_covers_every_step_of_a_generation(lib):
+    """The split plan is not monotone in max_len (chunks round up to 64 keys and are capped at 512 with
+    per-sequence lengths), so a buffer sized for max_len == cache capacity can be too small for a shorter
+    step.  vb200_decode_workspace_bytes_max is what the model's buffers are sized with: no step it can be
+    asked for -- a common length start_pos (max_len = start_pos + 1) or the device length array with any
+    max_len up to the capacity -- may need more."""
+    from vesper_b200 import capi
+    found_non_monotone = False
+    for B, Hq, Hkv, cap in ((8, 32, 8, 1024), (8, 32, 8, 2048), (4, 16, 4, 4096), (1, 64, 8, 8192), (2, 8, 2, 777), (32, 32, 8, 8448)):
+        d = capi.DecodeArgs()
+        d.struct_size = C.sizeof(capi.DecodeArgs)
+        d.B, d.Hq, d.Hkv, d.D, d.cache_cap = B, Hq, Hkv, 128, cap
+        worst = lib.vb200_decode_workspace_bytes_max(C.byref(d))
+        d.max_len = cap
+        at_cap = lib.vb200_decode_workspace_bytes(C.byref(d))
+        assert worst >= at_cap > 0
+        step = 1 if cap <= 2048 else 7
+        for pos in list(range(1, cap + 1, step)) + [cap]:
+            d.max_len = pos
+            d.seq_lens = None
+            n0 = lib.vb200_decode_workspace_bytes(C.byref(d))
+            d.seq_lens = 0x1000
+            n1 = lib.vb200_decode_workspace_bytes(C.byref(d))
+            assert n0 <= worst and n1 <= worst, (B, Hkv, cap, pos)
+            found_non_monotone |= max(n0, n1) > at_cap
+        d.seq_lens = None
+    assert found_non_monotone          # the case the helper exists for does occur
+    bad = capi.DecodeArgs()
+    bad.struct_size = C.sizeof(capi.DecodeArgs)
+    bad.B, bad.Hq, bad.Hkv, bad.D, bad.cache_cap = 1, 8, 2, 0, 64
+    assert lib.vb200_decode_workspace_bytes(C.byref(bad)) == 0 and lib.vb200_decode_workspace_bytes_max(C.byref(bad)) == 0
+
+
 def test_host_layer_facade_exports(lib):
     """libvesper_b200_host.so (models::TransformerLM / generation::Generator behind a C facade) loads without
     a GPU and exports what vesper_b200/model.py binds."""

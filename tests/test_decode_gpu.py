@@ -161,41 +161,131 @@ def test_decode_sharded_partials_combine(lib, cuda, oracle):
     assert maxabs(from_torch(lse), want_lse[0]) <= 1e-3
 
 
-def test_config3_full_size_one_step(lib, cuda, oracle):
+def test_config3_full_size_steps_0_1_255(lib, cuda, oracle):
     """Batched GQA decode at the benchmark size: B=32, Hq=32, Hkv=8, D=128, ragged lengths
-    U[1024, 8192]; one step with RoPE + append.  Oracle parity on 4 sequences x all heads."""
+    U[1024, 8192]; 256 consecutive steps with RoPE + append, the kernel advancing the length
+    array on the device.  Oracle parity on steps 0, 1 and 255 for 4 sequences x all heads."""
     import torch
     from vesper_b200 import capi
-    B, Hq, Hkv, D = 32, 32, 8, 128
+    B, Hq, Hkv, D, steps = 32, 32, 8, 128, 256
     rs = np.random.RandomState(2)
     lens = rs.randint(1024, 8193, size=B).astype(np.int32)
-    cap = 8192 + 256
+    cap = 8192 + steps
     g = torch.Generator(device="cuda").manual_seed(3)
     tk = torch.randn(B, Hkv, cap, D, generator=g, device=cuda, dtype=torch.float32).to(torch.bfloat16)
     tv = torch.randn(B, Hkv, cap, D, generator=g, device=cuda, dtype=torch.float32).to(torch.bfloat16)
     for b in range(B):
         tk[b, :, lens[b]:] = 0
         tv[b, :, lens[b]:] = 0
-    tq = torch.randn(B, Hq, 1, D, generator=g, device=cuda).to(torch.bfloat16)
-    tkn = torch.randn(B, Hkv, 1, D, generator=g, device=cuda).to(torch.bfloat16)
-    tvn = torch.randn(B, Hkv, 1, D, generator=g, device=cuda).to(torch.bfloat16)
     seq = torch.from_numpy(lens).to(cuda)
-    o = torch.empty_like(tq)
+    o = torch.empty(B, Hq, 1, D, dtype=torch.bfloat16, device=cuda)
     lse = torch.empty(B, Hq, dtype=torch.float32, device=cuda)
     scale = float(1.0 / np.sqrt(D))
     check = [0, 7, int(np.argmin(lens)), int(np.argmax(lens))]
-    before = {b: (from_torch(tk[b:b + 1]), from_torch(tv[b:b + 1])) for b in check}
-    capi.decode(tq, o, tk, tv, scale=scale, k_new=tkn, v_new=tvn, lse=lse, theta=10000.0, seq_lens=seq,
-                advance_lens=True, max_len=int(lens.max()) + 1)
+    ws = None
+    max_len = int(lens.max()) + steps
+    for step in range(steps):
+        gs = torch.Generator(device="cuda").manual_seed(4 + step)
+        tq = torch.randn(B, Hq, 1, D, generator=gs, device=cuda).to(torch.bfloat16)
+        tkn = torch.randn(B, Hkv, 1, D, generator=gs, device=cuda).to(torch.bfloat16)
+        tvn = torch.randn(B, Hkv, 1, D, generator=gs, device=cuda).to(torch.bfloat16)
+        checked = step in (0, 1, steps - 1)
+        if checked:
+            before = {b: (from_torch(tk[b:b + 1]), from_torch(tv[b:b + 1])) for b in check}
+        ws = capi.decode(tq, o, tk, tv, scale=scale, k_new=tkn, v_new=tvn, lse=lse, theta=10000.0, seq_lens=seq,
+                         advance_lens=True, max_len=max_len, workspace=ws)
+        if not checked:
+            continue
+        torch.cuda.synchronize()
+        capi.check_kernel_status(0)
+        assert torch.isfinite(o.float()).all()
+        assert seq.tolist() == (lens + step + 1).tolist()
+        for b in check:
+            kc1, vc1 = before[b]
+            L = int(lens[b]) + step
+            want_o, want_lse, n = oracle.gqa_attention_cached(from_torch(tq[b:b + 1]), from_torch(tkn[b:b + 1]), from_torch(tvn[b:b + 1]),
+                                                              kc1, vc1, L, L)
+            assert n == L + 1
+            assert maxabs(from_torch(o[b]), want_o[0]) <= 1e-2, f"step {step} sequence {b}"
+            assert maxabs(from_torch(lse[b]), want_lse[0, :, 0]) <= 1e-3, f"step {step} sequence {b}"
+            assert torch.equal(tv[b, :, L], tvn[b, :, 0])
+            gk = from_torch(tk[b, :, L])
+            assert np.all(np.abs(gk - kc1[0, :, L]) <= 2.0 ** -8 * np.abs(kc1[0, :, L]) + 1e-6)
     torch.cuda.synchronize()
     capi.check_kernel_status(0)
-    assert torch.isfinite(o.float()).all()
-    assert seq.tolist() == (lens + 1).tolist()
+    # nothing was written past the final lengths
     for b in check:
-        kc1, vc1 = before[b]
-        L = int(lens[b])
-        want_o, want_lse, _ = oracle.gqa_attention_cached(from_torch(tq[b:b + 1]), from_torch(tkn[b:b + 1]), from_torch(tvn[b:b + 1]),
-                                                          kc1, vc1, L, L)
-        assert maxabs(from_torch(o[b]), want_o[0]) <= 1e-2
-        assert maxabs(from_torch(lse[b]), want_lse[0, :, 0]) <= 1e-3
-        assert torch.equal(tv[b, :, L], tvn[b, :, 0])
+        assert not tk[b, :, int(lens[b]) + steps:].any() and not tv[b, :, int(lens[b]) + steps:].any()
+
+
+def test_config4_full_context_131072_keys_against_the_oracle(lib, cuda, oracle):
+    """Long-context decode at the benchmark size on one GPU: B=1, Hq=64, Hkv=8, D=128, 131072 cached keys,
+    the query rotated at position 131072.  Checked against the oracle's attention over all 131072 keys
+    for all 64 heads (src/nn/functional.cpp:399-421 on contiguous fp32 copies; RoPE src/nn/functional.cpp:424-494):
+    once as a single call, once as 8 sequence shards whose (O/l, m, l) records vb200_lse_combine merges
+    (the algebra of src/ops/flash_attention.cpp:309-345)."""
+    import torch
+    from vesper_b200 import capi
+    B, Hq, Hkv, D, L, R = 1, 64, 8, 128, 131072, 8
+    g = torch.Generator(device="cuda").manual_seed(5)
+    tk = torch.randn(B, Hkv, L, D, generator=g, device=cuda, dtype=torch.float32).to(torch.bfloat16)
+    tv = torch.randn(B, Hkv, L, D, generator=g, device=cuda, dtype=torch.float32).to(torch.bfloat16)
+    tq = torch.randn(B, Hq, 1, D, generator=torch.Generator(device="cuda").manual_seed(6), device=cuda).to(torch.bfloat16)
+    scale = float(1.0 / np.sqrt(D))
+    qpos = torch.tensor([L], dtype=torch.int32, device=cuda)
+    # one call over the whole context
+    o1 = torch.empty_like(tq)
+    lse1 = torch.empty(B, Hq, dtype=torch.float32, device=cuda)
+    capi.decode(tq, o1, tk, tv, scale=scale, lse=lse1, theta=10000.0, uniform_len=L, max_len=L, q_positions=qpos)
+    # eight contiguous shards, then the LSE merge
+    partials = torch.empty(R, B * Hq, D + 2, dtype=torch.float32, device=cuda)
+    per = L // R
+    for r in range(R):
+        capi.decode(tq, None, tk[:, :, r * per:(r + 1) * per], tv[:, :, r * per:(r + 1) * per], scale=scale, theta=10000.0,
+                    uniform_len=per, max_len=per, pos_offset=r * per, q_positions=qpos, partial_out=partials[r])
+    o8 = torch.empty(B * Hq, D, dtype=torch.bfloat16, device=cuda)
+    lse8 = torch.empty(B * Hq, dtype=torch.float32, device=cuda)
+    capi.lse_combine(partials, o8, lse8)
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)
+    q_rot = oracle.apply_rope(from_torch(tq), L, 10000.0)
+    want_o, want_lse = oracle.decode_ragged(q_rot[:, :, 0], from_torch(tk), from_torch(tv), [L])
+    assert maxabs(from_torch(o1)[:, :, 0], want_o) <= 1e-2
+    assert maxabs(from_torch(lse1), want_lse) <= 1e-3
+    assert maxabs(from_torch(o8), want_o[0]) <= 1e-2
+    assert maxabs(from_torch(lse8), want_lse[0]) <= 1e-3
+
+
+def test_decode_full_sequence_is_reported_not_overrun(lib, cuda, oracle):
+    """A sequence whose length already equals the cache capacity cannot take its new token: the kernel must
+    not write, not advance that length, attend to the keys it has, and leave VB200_ERR_CACHE_OVERFLOW in the
+    status word; its neighbours step normally.  (The reference throws from KVCache::update,
+    src/nn/transformer.cpp:62-66.)  Also a length that exceeds the planned max_len."""
+    import torch
+    from vesper_b200 import capi
+    B, Hq, Hkv, D, cap = 3, 8, 2, 128, 256
+    for lens, max_len in (([cap, 100, 255], 0), ([200, 100, 64], 128)):
+        rng = np.random.default_rng(90 + max_len)
+        k, v = make_cache(rng, B, Hkv, cap, D, lens, bf16_round)
+        tk, tv = to_torch(k, torch.bfloat16, cuda), to_torch(v, torch.bfloat16, cuda)
+        seq = torch.tensor(lens, dtype=torch.int32, device=cuda)
+        q = bf16_round(rng.standard_normal((B, Hq, 1, D), dtype=np.float32))
+        kn = bf16_round(rng.standard_normal((B, Hkv, 1, D), dtype=np.float32))
+        vn = bf16_round(rng.standard_normal((B, Hkv, 1, D), dtype=np.float32))
+        tq, tkn, tvn = (to_torch(x, torch.bfloat16, cuda) for x in (q, kn, vn))
+        o = torch.empty_like(tq)
+        capi.decode(tq, o, tk, tv, scale=float(1.0 / np.sqrt(D)), k_new=tkn, v_new=tvn, theta=10000.0, seq_lens=seq,
+                    advance_lens=True, max_len=max_len)
+        torch.cuda.synchronize()
+        with pytest.raises(capi.Vb200Error) as e:
+            capi.check_kernel_status(0)
+        assert e.value.status == -8 and "sequence 0" in str(e.value)
+        capi.check_kernel_status(0)                                  # the word was cleared
+        assert seq.tolist() == [lens[0], lens[1] + 1, lens[2] + 1]
+        gk, gv = from_torch(tk), from_torch(tv)
+        assert np.array_equal(gk[0], k[0]) and np.array_equal(gv[0], v[0])          # sequence 0: cache untouched
+        assert torch.isfinite(o.float()).all()
+        for b in (1, 2):
+            kc1, vc1 = k[b:b + 1].copy(), v[b:b + 1].copy()
+            want_o, _, _ = oracle.gqa_attention_cached(q[b:b + 1], kn[b:b + 1], vn[b:b + 1], kc1, vc1, lens[b], lens[b])
+            assert maxabs(from_torch(o)[b], want_o[0]) <= 1e-2

@@ -79,7 +79,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 HOST_DIR = os.path.join(PKG, "host")
 HOST_LIB = os.path.join(LIBDIR, "libvesper_b200_host.so")
-HOST_SOURCES = ["tensor.cpp", "attention.cpp", "transformer.cpp", "generator.cpp", "modules.cpp", "c_api.cpp"]
+HOST_SOURCES = ["tensor.cpp", "attention.cpp", "attention_modules.cpp", "transformer.cpp", "generator.cpp", "modules.cpp", "c_api.cpp"]
 
 
 def build_host(force: bool = False) -> str:

@@ -32,7 +32,7 @@ class PrefillArgs(C.Structure):
         ("start_pos", C.c_int32), ("causal", C.c_int32), ("scale", C.c_float),
         ("q", Tensor4), ("k", Tensor4), ("v", Tensor4), ("o", Tensor4), ("lse", C.c_void_p),
         ("rope", Rope), ("k_cache", Tensor4), ("v_cache", Tensor4), ("cache_cap", C.c_int32),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("cache_read_only", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -50,7 +50,7 @@ class DecodeArgs(C.Structure):
 
 
 EXPORTS = [
-    "vb200_prefill_workspace_bytes", "vb200_prefill_fwd", "vb200_decode_workspace_bytes", "vb200_decode_fwd",
+    "vb200_prefill_workspace_bytes", "vb200_prefill_fwd", "vb200_decode_workspace_bytes", "vb200_decode_workspace_bytes_max", "vb200_decode_fwd",
     "vb200_decode_fwd_static", "vb200_exchange_buffer_bytes", "vb200_exchange_combine",
     "vb200_attention_bwd_workspace_bytes", "vb200_attention_bwd",
     "vb200_lse_combine", "vb200_kv_append", "vb200_apply_rope", "vb200_repeat_kv", "vb200_rope_inv_freq",
@@ -58,7 +58,7 @@ EXPORTS = [
     "vb200_reset_launch_count", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
 ]
 BLOCK_EXPORTS = [
-    "vb200_linear", "vb200_linear_bias", "vb200_linear_ex", "vb200_row_inv_rms", "vb200_embedding_scaled", "vb200_linear_add_rmsnorm", "vb200_embedding_rmsnorm", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
+    "vb200_linear", "vb200_linear_bias", "vb200_linear_f32", "vb200_linear_ex", "vb200_row_inv_rms", "vb200_embedding_scaled", "vb200_linear_add_rmsnorm", "vb200_embedding_rmsnorm", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
 ]
 
 
@@ -124,6 +124,8 @@ def load():
     L.vb200_prefill_fwd.argtypes = [C.POINTER(PrefillArgs)]
     L.vb200_decode_workspace_bytes.argtypes = [C.POINTER(DecodeArgs)]
     L.vb200_decode_workspace_bytes.restype = C.c_size_t
+    L.vb200_decode_workspace_bytes_max.argtypes = [C.POINTER(DecodeArgs)]
+    L.vb200_decode_workspace_bytes_max.restype = C.c_size_t
     L.vb200_decode_fwd.argtypes = [C.POINTER(DecodeArgs)]
     L.vb200_decode_fwd_static.argtypes = [C.POINTER(DecodeArgs)]
     L.vb200_lse_combine.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
@@ -149,6 +151,7 @@ def load():
     # decoder-block operators (include/vesper_b200_block.h)
     L.vb200_linear.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64] + [C.c_int32] * 5
     L.vb200_linear_bias.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64] + [C.c_int32] * 5
+    L.vb200_linear_f32.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64] + [C.c_int32] * 3
     L.vb200_linear_ex.argtypes = [C.POINTER(LinearArgs)]
     L.vb200_row_inv_rms.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_float]
     L.vb200_embedding_scaled.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
@@ -202,14 +205,15 @@ def _ptr(t):
 
 
 def prefill_args(q, k, v, o, lse=None, *, scale, causal=True, start_pos=0, theta=None,
-                 k_cache=None, v_cache=None, workspace=None, stream=None):
+                 k_cache=None, v_cache=None, workspace=None, stream=None, cache_read_only=False):
     B, Hq, T, D = q.shape
     a = PrefillArgs()
     a.struct_size = C.sizeof(PrefillArgs)
     a.device = q.device.index if q.device.index is not None else -1
     a.stream = _stream_ptr(stream)
     a.dtype = dtype_code(q)
-    a.B, a.Hq, a.Hkv, a.T, a.D = B, Hq, k.shape[1], T, D
+    a.B, a.Hq, a.Hkv, a.T, a.D = B, Hq, (k if k is not None else k_cache).shape[1], T, D
+    a.cache_read_only = int(cache_read_only)
     a.start_pos, a.causal, a.scale = start_pos, int(causal), scale
     a.q, a.k, a.v, a.o = view4(q), view4(k), view4(v), view4(o)
     a.lse = _ptr(lse)
@@ -228,12 +232,12 @@ def prefill_args(q, k, v, o, lse=None, *, scale, causal=True, start_pos=0, theta
 
 
 def prefill(q, k, v, o, lse=None, *, scale, causal=True, start_pos=0, theta=None,
-            k_cache=None, v_cache=None, workspace=None, stream=None):
+            k_cache=None, v_cache=None, workspace=None, stream=None, cache_read_only=False):
     """vb200_prefill_fwd on torch CUDA tensors.  Allocates a workspace with torch when none is given."""
     import torch
     L = load()
     a = prefill_args(q, k, v, o, lse, scale=scale, causal=causal, start_pos=start_pos, theta=theta,
-                     k_cache=k_cache, v_cache=v_cache, workspace=workspace, stream=stream)
+                     k_cache=k_cache, v_cache=v_cache, workspace=workspace, stream=stream, cache_read_only=cache_read_only)
     need = L.vb200_prefill_workspace_bytes(C.byref(a))
     if need > a.workspace_bytes:
         workspace = torch.empty(need, dtype=torch.uint8, device=q.device)

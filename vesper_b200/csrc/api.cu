@@ -110,8 +110,13 @@ int validate_prefill(const vb200_prefill_args* a) {
     if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->T <= 0 || a->D <= 0) return set_detail(VB200_ERR_INVALID_ARG, "B, Hq, Hkv, T, D must be positive");
     if (a->Hq % a->Hkv != 0) return set_detail(VB200_ERR_INVALID_ARG, "Hq must be divisible by Hkv");
     if (a->start_pos < 0) return set_detail(VB200_ERR_INVALID_ARG, "start_pos must be >= 0");
-    if (!a->q.ptr || !a->k.ptr || !a->v.ptr || !a->o.ptr) return set_detail(VB200_ERR_INVALID_ARG, "q, k, v, o must be non-null");
+    if (!a->q.ptr || !a->o.ptr) return set_detail(VB200_ERR_INVALID_ARG, "q, k, v, o must be non-null");
+    const bool ro = a->cache_read_only != 0;
+    if (ro && !a->k_cache.ptr) return set_detail(VB200_ERR_INVALID_ARG, "cache_read_only needs k_cache and v_cache");
+    if (!ro && (!a->k.ptr || !a->v.ptr)) return set_detail(VB200_ERR_INVALID_ARG, "q, k, v, o must be non-null");
     if (a->D % 8 != 0 || a->D > 128) return set_detail(VB200_ERR_UNSUPPORTED, "head_dim must be a multiple of 8 and <= 128");
+    // checked here, ahead of every launch: a call either does all of its work or none of it
+    if (a->dtype != VB200_F32 && a->D != 64 && a->D != 128) return set_detail(VB200_ERR_UNSUPPORTED, "bf16/fp16 attention supports head_dim 64 and 128");
     if ((a->k_cache.ptr == nullptr) != (a->v_cache.ptr == nullptr)) return set_detail(VB200_ERR_INVALID_ARG, "k_cache and v_cache must both be given or both be null");
     if (a->k_cache.ptr) {
         if (a->start_pos + a->T > a->cache_cap) return set_detail(VB200_ERR_INVALID_ARG, "start_pos + T exceeds the cache capacity");
@@ -120,7 +125,7 @@ int validate_prefill(const vb200_prefill_args* a) {
     }
     if (a->rope.enabled && !a->rope.inv_freq_host) return set_detail(VB200_ERR_INVALID_ARG, "rope enabled without inv_freq_host");
     int esz = elem_size(a->dtype);
-    if (!view_aligned(a->q, esz) || !view_aligned(a->k, esz) || !view_aligned(a->v, esz) || !view_aligned(a->o, esz))
+    if (!view_aligned(a->q, esz) || !view_aligned(a->o, esz) || (!ro && (!view_aligned(a->k, esz) || !view_aligned(a->v, esz))))
         return set_detail(VB200_ERR_ALIGNMENT, "q/k/v/o base and strides must be 16-byte aligned");
     if (a->k_cache.ptr && (!view_aligned(a->k_cache, esz) || !view_aligned(a->v_cache, esz)))
         return set_detail(VB200_ERR_ALIGNMENT, "cache base and strides must be 16-byte aligned");
@@ -137,6 +142,20 @@ struct DecodePlan {
     size_t total;
 };
 
+// Streaming multiprocessors of the current device, asked once per ordinal (148 where no device answers,
+// e.g. when only workspace sizes are computed on a machine without a GPU).
+int sm_count() {
+    static int cache[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return 148; }
+    if (cache[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = 148; }
+        cache[dev] = n;
+    }
+    return cache[dev];
+}
+
 DecodePlan plan_decode(const vb200_decode_args* a) {
     DecodePlan pl{};
     const int tile = decode_tile_keys();
@@ -146,11 +165,12 @@ DecodePlan plan_decode(const vb200_decode_args* a) {
     if (a->num_splits > 0) {
         chunk = (max_total + a->num_splits - 1) / a->num_splits;
     } else {
-        // enough CTAs for about two waves of 2 CTAs/SM on 148 SMs; with per-sequence lengths never
+        // enough CTAs for about two waves of 2 CTAs per SM; with per-sequence lengths never
         // more than 512 keys per CTA so ragged batches balance (one common length needs no such cap:
         // longer chunks spend less of a CTA's life in its prologue and merge)
         long long units = static_cast<long long>(a->B) * a->Hkv;
-        int want = static_cast<int>((592 + units - 1) / units);
+        const long long ctas = 2LL * 2 * sm_count();
+        int want = static_cast<int>((ctas + units - 1) / units);
         chunk = (max_total + want - 1) / want;
         if (chunk > 512 && a->seq_lens) chunk = 512;
         // short contexts: at most 16 splits, so that they can run as one cluster that merges its own partials
@@ -208,6 +228,7 @@ const char* vb200_strerror(int status) {
         case VB200_ERR_CUDA: return "CUDA error";
         case VB200_ERR_NO_DEVICE: return "no usable CUDA device";
         case VB200_ERR_KERNEL_TIMEOUT: return "a bounded in-kernel wait expired";
+        case VB200_ERR_CACHE_OVERFLOW: return "a sequence's new token does not fit the KV cache / planned max_len";
         default: return "unknown status";
     }
 }
@@ -233,6 +254,10 @@ int vb200_check_kernel_status(int device, void* stream) {
     VB200_CUDA_TRY(cudaMemcpyToSymbolAsync(g_kernel_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, s));
     VB200_CUDA_TRY(cudaStreamSynchronize(s));
     char buf[96];
+    if ((host >> 24) == 2) {
+        std::snprintf(buf, sizeof(buf), "decode: sequence %d is full (token not appended, length not advanced)", host & 0xFFFFFF);
+        return set_detail(VB200_ERR_CACHE_OVERFLOW, buf);
+    }
     std::snprintf(buf, sizeof(buf), "kernel wait expired: code %d, site 0x%x", host >> 24, host & 0xFFFFFF);
     return set_detail(VB200_ERR_KERNEL_TIMEOUT, buf);
 }
@@ -306,7 +331,11 @@ int vb200_prefill_fwd(const vb200_prefill_args* a) {
     p.status = kernel_status_word();
     if (!p.status) return set_detail(VB200_ERR_CUDA, "cannot resolve the device status word");
 
-    if (a->k_cache.ptr) {
+    if (a->k_cache.ptr && a->cache_read_only) {
+        // the cache already holds every key and value this call attends to
+        p.k = to_view(a->k_cache);
+        p.v = to_view(a->v_cache);
+    } else if (a->k_cache.ptr) {
         // fused RoPE(K) + append; attention then reads K/V straight from the cache
         if (int rc = launch_kv_append(s, a->dtype, a->B, a->Hkv, a->T, a->D, to_view(a->k), to_view(a->v),
                                       to_view(a->k_cache), to_view(a->v_cache), a->start_pos, table)) return rc;
@@ -329,8 +358,25 @@ int vb200_prefill_fwd(const vb200_prefill_args* a) {
 
 size_t vb200_decode_workspace_bytes(const vb200_decode_args* a) {
     if (!a || a->struct_size != sizeof(vb200_decode_args)) return 0;
-    if (a->B <= 0 || a->Hkv <= 0 || a->Hq <= 0 || a->Hq % a->Hkv != 0) return 0;
+    if (a->B <= 0 || a->Hkv <= 0 || a->Hq <= 0 || a->D <= 0 || a->Hq % a->Hkv != 0) return 0;
     return plan_decode(a).total;
+}
+
+size_t vb200_decode_workspace_bytes_max(const vb200_decode_args* a) {
+    if (!a || a->struct_size != sizeof(vb200_decode_args)) return 0;
+    if (a->B <= 0 || a->Hkv <= 0 || a->Hq <= 0 || a->D <= 0 || a->Hq % a->Hkv != 0 || a->cache_cap <= 0) return 0;
+    vb200_decode_args t = *a;
+    int32_t lens_tag = 0;                       // only the pointer's presence enters the plan
+    size_t best = 0;
+    for (int with_lens = 0; with_lens < 2; ++with_lens) {
+        t.seq_lens = with_lens ? &lens_tag : nullptr;
+        for (int len = 1; len <= a->cache_cap; ++len) {
+            t.max_len = len;
+            const size_t n = plan_decode(&t).total;
+            if (n > best) best = n;
+        }
+    }
+    return best;
 }
 
 int vb200_decode_fwd(const vb200_decode_args* a) {
@@ -511,6 +557,15 @@ int vb200_linear_bias(int device, void* stream, const void* x, int64_t ldx, cons
 int vb200_linear(int device, void* stream, const void* x, int64_t ldx, const void* w, int64_t ldw,
                  void* out, int64_t ldo, int32_t M, int32_t N, int32_t K, int32_t epilogue, int32_t splits) {
     return vb200_linear_bias(device, stream, x, ldx, w, ldw, nullptr, out, ldo, M, N, K, epilogue, splits);
+}
+
+int vb200_linear_f32(int device, void* stream, const float* x, int64_t ldx, const float* w, int64_t ldw, const float* bias,
+                     float* out, int64_t ldo, int32_t M, int32_t N, int32_t K) {
+    if (!x || !w || !out || M <= 0 || N <= 0 || K <= 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_f32: null pointer or non-positive size");
+    if (ldx < K || ldw < K || ldo < N) return set_detail(VB200_ERR_INVALID_ARG, "vb200_linear_f32: a row stride is smaller than its row");
+    DeviceGuard g;
+    if (int rc = g.init(device)) return rc;
+    return launch_linear_f32(static_cast<cudaStream_t>(stream), x, ldx, w, ldw, bias, out, ldo, M, N, K);
 }
 
 int vb200_linear_ex(const vb200_linear_args* a) {

@@ -237,6 +237,51 @@ int launch_row_inv_rms(cudaStream_t s, const float* h, long long ld, float* inv_
     return launch_pdl(row_inv_rms_kernel, dim3(static_cast<unsigned>((M + 7) / 8)), dim3(256), s, h, ld, inv_rms, M, dim, eps);
 }
 
+// fp32 y = x W^T + bias on CUDA cores: 64 x 64 output tiles, 16 x 16 threads with a 4 x 4 register block each, K in
+// steps of 16 through shared memory.  For the reference's fp32 modules (parity at 1e-4); bf16 goes to linear_sm100.cu.
+__global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w, long long ldw,
+                                                         const float* __restrict__ bias, float* __restrict__ out, long long ldo, int M, int N, int K) {
+    __shared__ float xs[16][64 + 1], ws[16][64 + 1];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            const int r = i >> 4, k = i & 15;
+            xs[k][r] = (m0 + r < M && k0 + k < K) ? x[static_cast<long long>(m0 + r) * ldx + k0 + k] : 0.f;
+            ws[k][r] = (n0 + r < N && k0 + k < K) ? w[static_cast<long long>(n0 + r) * ldw + k0 + k] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = xs[k][ty * 4 + i]; b[i] = ws[k][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (m < M && n < N) out[static_cast<long long>(m) * ldo + n] = acc[i][j] + (bias ? bias[n] : 0.f);
+        }
+}
+
+int launch_linear_f32(cudaStream_t s, const float* x, long long ldx, const float* w, long long ldw, const float* bias, float* out,
+                      long long ldo, int M, int N, int K) {
+    dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64));
+    linear_f32_kernel<<<grid, 256, 0, s>>>(x, ldx, w, ldw, bias, out, ldo, M, N, K);
+    note_launch();
+    VB200_CUDA_TRY(cudaPeekAtLastError());
+    return VB200_OK;
+}
+
 int launch_silu_mul(cudaStream_t s, const void* gate, const void* up, void* out, long long n) {
     if (n % 8 != 0) return set_detail(VB200_ERR_ALIGNMENT, "silu_mul: element count must be a multiple of 8");
     const long long nvec = n / 8;

@@ -91,15 +91,17 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa_mma_kernel(con
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     asm volatile("griddepcontrol.wait;" ::: "memory");       // q / k_new / v_new / lengths may come from the previous kernel
-    int len = p.seq_lens ? p.seq_lens[b] : p.uniform_len;
-    len = max(0, min(len, p.cache_cap));
-    const int total = len + (p.append ? 1 : 0);
+    const StepLen sl = step_length(p, b);
+    const int len = sl.len, total = sl.total;
     const int k_begin = split * p.chunk;
-    if (split == 0 && kvh == 0 && threadIdx.x == 0) reinterpret_cast<int*>(p.workspace)[b] = len;
+    if (split == 0 && kvh == 0 && threadIdx.x == 0) {
+        reinterpret_cast<int*>(p.workspace)[b] = sl.header();
+        if (sl.overflow) atomicCAS(p.status, 0, (2 << 24) | (b & 0xFFFFFF));
+    }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (k_begin >= total) return;
     const int k_end = min(len, k_begin + p.chunk);
-    const bool owns_new = p.append && (len / p.chunk == split);
+    const bool owns_new = sl.append && (len / p.chunk == split);
     const int ntiles = (k_end > k_begin) ? (k_end - k_begin + kTileM - 1) / kTileM : 0;
 
     if (tid == 0) {
@@ -190,10 +192,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa_mma_kernel(con
             newk[l16 * 8 + 2 * i + 1] = t.y;
         }
         *reinterpret_cast<uint4*>(newv + l16 * 8) = vraw;
-        if (len < p.cache_cap) {
-            *reinterpret_cast<uint4*>(const_cast<T*>(kc) + static_cast<long long>(len) * D + l16 * 8) = kraw;
-            *reinterpret_cast<uint4*>(const_cast<T*>(vc) + static_cast<long long>(len) * D + l16 * 8) = vraw;
-        }
+        // owns_new implies len < cache_cap (step_length refuses the append otherwise)
+        *reinterpret_cast<uint4*>(const_cast<T*>(kc) + static_cast<long long>(len) * D + l16 * 8) = kraw;
+        *reinterpret_cast<uint4*>(const_cast<T*>(vc) + static_cast<long long>(len) * D + l16 * 8) = vraw;
     }
 
     FragState st;

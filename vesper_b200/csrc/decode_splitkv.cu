@@ -197,20 +197,20 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(Dec
     // launched with the programmatic-dependent-launch attribute: q / k_new / v_new and the length array
     // may come from the kernel just before this one
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    int len = p.seq_lens ? p.seq_lens[b] : p.uniform_len;          // cached keys before this token
-    len = max(0, min(len, p.cache_cap));
-    const int total = len + (p.append ? 1 : 0);
+    const StepLen sl = step_length(p, b);                           // cached keys before this token, and whether it fits
+    const int len = sl.len, total = sl.total;
     const int k_begin = split * p.chunk;
     if (split == 0 && kvh == 0 && threadIdx.x == 0) {
-        // length this step used, for the combine kernel (stable even when seq_lens advances)
-        reinterpret_cast<int*>(p.workspace)[b] = len;
+        // what this step used, for the combine kernel (stable even when seq_lens advances)
+        reinterpret_cast<int*>(p.workspace)[b] = sl.header();
+        if (sl.overflow) atomicCAS(p.status, 0, (2 << 24) | (b & 0xFFFFFF));
     }
     // let the combine kernel's blocks be scheduled as soon as every CTA of this grid has started
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const bool nothing = k_begin >= total;                          // no key for this split
     if (nothing && !p.cluster_merge) return;                        // (a cluster member stays for the cluster barriers)
     const int k_end = min(len, k_begin + p.chunk);                  // cached keys [k_begin, k_end)
-    const bool owns_new = !nothing && p.append && (len / p.chunk == split);
+    const bool owns_new = !nothing && sl.append && (len / p.chunk == split);
     const int ntiles = (!nothing && k_end > k_begin) ? (k_end - k_begin + kTile - 1) / kTile : 0;
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], CW); }
@@ -295,7 +295,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_splitkv_kernel(Dec
                 }
             }
             *reinterpret_cast<uint4*>(newv + l16 * 8) = vraw;
-            if (len < p.cache_cap) {    // never write past the cache, whatever seq_lens holds
+            {   // owns_new implies len < cache_cap: step_length refuses the append otherwise, whatever seq_lens holds
                 T* kdst = const_cast<T*>(kc) + static_cast<long long>(len) * D + l16 * 8;
                 T* vdst = const_cast<T*>(vc) + static_cast<long long>(len) * D + l16 * 8;
                 *reinterpret_cast<uint4*>(kdst) = kraw;
@@ -444,9 +444,10 @@ __global__ void __launch_bounds__(128 * kCombineGroups) decode_combine_kernel(De
     // Launched with programmatic stream serialization: the blocks may become resident while the
     // split kernel drains; nothing of its output is touched before this wait returns.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int len = reinterpret_cast<const int*>(p.workspace)[b];
-    const int total = len + (p.append ? 1 : 0);
-    const int nsp = (total + p.chunk - 1) / p.chunk;
+    const int hdr = reinterpret_cast<const int*>(p.workspace)[b];
+    const int total = StepLen::header_total(hdr);                    // keys this step attended to (new token included)
+    const bool appended = StepLen::header_appended(hdr);
+    const int nsp = min((total + p.chunk - 1) / p.chunk, p.num_splits);
     const float* base = p.workspace + p.ws_header +
                         ((static_cast<long long>(b) * p.Hkv + kvh) * p.num_splits) * nrep * (D + 2) + h * (D + 2);
     const long long sstride = static_cast<long long>(nrep) * (D + 2);
@@ -491,7 +492,8 @@ __global__ void __launch_bounds__(128 * kCombineGroups) decode_combine_kernel(De
         og[d] = Elem<T>::from_f(o);
         if (p.lse && d == 0) p.lse[static_cast<long long>(b) * p.Hq + hq] = M + logf(L);
     }
-    if (hq == 0 && d == 0 && p.seq_lens && p.append && p.advance_lens) p.seq_lens[b] = len + 1;
+    // a full sequence (token not appended) keeps its length
+    if (hq == 0 && d == 0 && p.seq_lens && appended && p.advance_lens) p.seq_lens[b] = total;
 }
 
 // partials [R, rows, D+2] -> out [rows, D], lse [rows]
@@ -515,7 +517,7 @@ __global__ void lse_combine_kernel(const float* __restrict__ partials, int R, lo
     if (lse && d == 0) lse[row] = M + logf(L);
 }
 
-constexpr int kMaxClusterSplits = 16;   // cluster sizes above 8 are allowed on this part (non-portable size attribute)
+constexpr int kMaxClusterSplits = 16;   // cluster sizes above 8 need the non-portable cluster size attribute
 
 template <typename T, int NREP>
 int launch_decode_t(cudaStream_t s, const DecodeParams& p) {

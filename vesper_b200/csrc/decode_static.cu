@@ -21,6 +21,10 @@
 //   * The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current).  That first call
 //     should be made before any stream capture begins.
+//   * The address is remembered per device ordinal for the life of the process.
+//     A host program that calls cudaDeviceReset() destroys the context the
+//     address belongs to; do not call this entry point again on that device
+//     afterwards (reload the library instead).
 //   * The call allocates and frees nothing: no cudaMalloc / cudaFree, no
 //     allocating library routine.
 #include <cstdio>
@@ -66,7 +70,9 @@ extern "C" int vb200_decode_fwd_static(const vb200_decode_args* a) {
     if (!a || a->struct_size != sizeof(vb200_decode_args))
         return set_detail(VB200_ERR_INVALID_ARG, "vb200_decode_args: null or struct_size mismatch");
     const size_t need = vb200_decode_workspace_bytes(a);
-    if (need == 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_decode_fwd_static: bad shape (B, Hq, Hkv)");
+    // 0 = a shape no plan exists for (non-positive B, Hq, Hkv or D, Hq not a multiple of Hkv): an argument
+    // error, reported as such before the size comparison below can misread it
+    if (need == 0) return set_detail(VB200_ERR_INVALID_ARG, "vb200_decode_fwd_static: bad shape (B, Hq, Hkv, D)");
     if (need > static_cast<size_t>(VB200_STATIC_SCRATCH_BYTES)) {
         static thread_local char msg[200];
         snprintf(msg, sizeof(msg),

@@ -74,6 +74,32 @@ struct DecodeParams {
     int* status;         // device status word (bounded waits)
     int cluster_merge;   // 1: the splits of a (batch, kv_head) form one thread-block cluster that merges its partials itself
 };
+// Length bookkeeping of one decode step for sequence b, shared by the split kernels and the combine
+// kernel.  len = cached keys attended to; append = whether the new token is written and attended to.
+// The token does not fit when len + 1 exceeds the cache capacity or the num_splits * chunk keys the
+// grid was planned for: then it is skipped (no write, no length advance), `overflow` is set and the
+// split kernel records it in the status word.  A length beyond what the grid covers is clamped too.
+struct StepLen {
+    int len, total;
+    bool append, overflow;
+    // packed into the workspace header slot of the sequence: bit 30 = appended, low bits = total
+    __host__ __device__ int header() const { return total | (append ? (1 << 30) : 0); }
+    __host__ __device__ static int header_total(int h) { return h & ((1 << 30) - 1); }
+    __host__ __device__ static bool header_appended(int h) { return (h >> 30) & 1; }
+};
+#ifdef __CUDACC__
+__device__ __forceinline__ StepLen step_length(const DecodeParams& p, int b) {
+    StepLen s;
+    const int raw = p.seq_lens ? p.seq_lens[b] : p.uniform_len;
+    const long long planned = static_cast<long long>(p.num_splits) * p.chunk;
+    const int limit = static_cast<int>(planned < p.cache_cap ? planned : p.cache_cap);
+    s.overflow = raw < 0 || raw + (p.append ? 1 : 0) > limit;
+    s.len = raw < 0 ? 0 : (raw > limit ? limit : raw);
+    s.append = p.append && !s.overflow;
+    s.total = s.len + (s.append ? 1 : 0);
+    return s;
+}
+#endif
 int decode_tile_keys();
 int launch_decode(cudaStream_t s, const DecodeParams& p);
 // decode_gqa_mma.cu: split kernel with warp-MMA products (instantiated for Hq / Hkv of 4 and 8); same workspace layout
@@ -144,6 +170,8 @@ int launch_row_inv_rms(cudaStream_t s, const float* h, long long ld, float* inv_
 int launch_interleave_rows(cudaStream_t s, const void* a, const void* b, void* out, long long rows, long long cols);
 int launch_rms_norm(cudaStream_t s, const float* x, const float* weight, void* out_bf16, int M, int dim, float eps);
 int launch_silu_mul(cudaStream_t s, const void* gate, const void* up, void* out, long long n);
+int launch_linear_f32(cudaStream_t s, const float* x, long long ldx, const float* w, long long ldw, const float* bias, float* out,
+                      long long ldo, int M, int N, int K);
 // norm_w / norm_out (nullable): also out_norm[m,:] = rmsnorm(out[m,:]) * norm_w as bf16
 int launch_embedding(cudaStream_t s, const void* ids, int ids64, const void* table, float* out, int M, int dim,
                      int vocab, int* status, const float* norm_w = nullptr, void* norm_out = nullptr, float norm_eps = 0.f,

@@ -125,6 +125,9 @@ public:
     Tensor contiguous() const;
     Tensor index(const std::vector<IndexSelector>& selectors) const;
     Tensor narrow(int64_t dim, int64_t start, int64_t length) const;
+    // Splits the last dimension (which must have stride 1) into [outer, inner] without a copy, whatever the other
+    // strides are: how q / k / v heads are seen inside a slice of the fused projection's output.
+    Tensor unflatten_last(int64_t outer, int64_t inner) const;
     Tensor to(Device device) const;
     Tensor clone() const { return contiguous_copy(); }
     void zero_();

@@ -3,6 +3,7 @@
 // (include/vesper/nn/transformer.h:21-56, src/nn/transformer.cpp:32-93,166-216).
 #pragma once
 #include <vesper/core/tensor.h>
+#include <vesper/nn/linear.h>
 #include <utility>
 
 namespace vesper::nn {
@@ -39,7 +40,32 @@ private:
 // append of rotated k and raw v to the cache, grouped-query attention over the cached
 // context with causal = (T > 1).  q: [B,Hq,T,D]; k, v: [B,Hkv,T,D]; returns [B,Hq,T,D].
 // cache == nullptr: attention over the T new tokens only (the uncached forward).
+// out_view (optional): where the result goes -- a [B,Hq,T,D] view with any batch / head / row strides, e.g. the
+// transposed view of a [B,T,Hq,D] buffer, so that the heads come out already merged.
 Tensor fused_attention(const Tensor& q, const Tensor& k, const Tensor& v, KVCache* cache, int64_t start_pos,
-                       bool use_rope = true, float rope_base = 10000.0f, bool causal_when_uncached = true);
+                       bool use_rope = true, float rope_base = 10000.0f, bool causal_when_uncached = true,
+                       Tensor* out_view = nullptr);
+
+// nn::MultiHeadAttention (include/vesper/nn/transformer.h:41-56, src/nn/transformer.cpp:97-216): c_attn =
+// Linear(C, 3C) with bias, three slices of its output as q, k, v, optional RoPE with theta fixed at 10000,
+// attention, c_proj = Linear(C, C) with bias.  forward(x) is NON-causal, as in the reference (:108-110);
+// forward(x, cache, start_pos) masks causally when more than one token comes in.  Dropout is training-only in the
+// reference and this layer is the inference path: a non-zero dropout is accepted and never applied.
+// The trailing dtype argument (not in the reference, whose modules are Float32) selects the number format of the
+// weights and activations: Float32 reproduces the reference at 1e-4, BFloat16 is the serving format.
+class MultiHeadAttention {
+public:
+    MultiHeadAttention(int embed_dim, int num_heads, float dropout = 0.0, bool use_rope = true, DType dtype = DType::Float32);
+    Tensor forward(const Tensor& x);
+    Tensor forward(const Tensor& x, bool causal);
+    Tensor forward(const Tensor& x, KVCache* cache, int start_pos = 0);
+
+    Linear c_attn;
+    Linear c_proj;
+    int n_head;
+    int n_embd;
+    float dropout_;
+    bool use_rope_;
+};
 
 }  // namespace vesper::nn

@@ -193,7 +193,7 @@ std::pair<Tensor, Tensor> KVCache::update(const Tensor& new_k, const Tensor& new
 }
 
 Tensor fused_attention(const Tensor& q, const Tensor& k, const Tensor& v, KVCache* cache, int64_t start_pos,
-                       bool use_rope, float rope_base, bool causal_when_uncached) {
+                       bool use_rope, float rope_base, bool causal_when_uncached, Tensor* out_view) {
     if (q.ndim() != 4 || k.ndim() != 4 || v.ndim() != 4) throw std::runtime_error("attention: q, k, v must be 4D [B, H, T, D]");
     if (k.shape() != v.shape()) throw std::runtime_error("attention: k and v must have the same shape");
     const int B = static_cast<int>(q.shape()[0]), Hq = static_cast<int>(q.shape()[1]), T = static_cast<int>(q.shape()[2]),
@@ -206,8 +206,12 @@ Tensor fused_attention(const Tensor& q, const Tensor& k, const Tensor& v, KVCach
         vb200_rope_inv_freq(rope_base, D, inv_freq);
     }
     const float scale = 1.0f / std::sqrt(static_cast<float>(D));
-    Tensor out = empty(q.shape(), q.dtype(), Device::CUDA);
-    const bool fast_decode = cache && T == 1 && D == 128 && q.dtype() != DType::Float32;
+    if (out_view && (out_view->shape() != q.shape() || out_view->dtype() != q.dtype() || out_view->strides()[3] != 1))
+        throw std::runtime_error("attention: the output view must have q's shape and dtype with contiguous head_dim");
+    if (cache && cache->k().dtype() != q.dtype()) throw std::runtime_error("attention: the KV cache must have the dtype of q, k, v");
+    Tensor out = out_view ? *out_view : empty(q.shape(), q.dtype(), Device::CUDA);
+    const int n_rep = Hq / Hkv;
+    const bool fast_decode = cache && T == 1 && D == 128 && q.dtype() != DType::Float32 && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 8);
     if (fast_decode) {
         vb200_decode_args d{};
         d.struct_size = sizeof(d);
@@ -264,23 +268,46 @@ Tensor scaled_dot_product_attention(const Tensor& query, const Tensor& key, cons
     const float scale = 1.0f / std::sqrt(static_cast<float>(D));
     if (T == L) return ops::flash_attention_with_lse(query, key, value, scale, is_causal).first;
     if (T > L) throw std::runtime_error("scaled_dot_product_attention: more queries than keys");
-    // T queries against L > T keys: the keys already are the "cache"; the last T rows are
-    // re-written onto themselves by the append stage (same values), then attended to.
+    // T queries against L > T keys (src/nn/functional.cpp:399-421; the decode shape is T = 1): key and value
+    // already hold every row attended to, so they are passed as a read-only cache -- nothing is written.
     Tensor out = empty(query.shape(), query.dtype(), Device::CUDA);
+    const int B = static_cast<int>(query.shape()[0]), Hq = static_cast<int>(query.shape()[1]), Hkv = static_cast<int>(key.shape()[1]);
+    if (Hq % Hkv != 0) throw std::runtime_error("scaled_dot_product_attention: query heads must be a multiple of key heads");
+    const int n_rep = Hq / Hkv;
+    if (T == 1 && !is_causal && D == 128 && query.dtype() != DType::Float32 && key.strides()[2] == D && value.strides()[2] == D &&
+        (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 8)) {
+        // one query row per head: the split-KV kernel, no append, no rotation
+        vb200_decode_args d{};
+        d.struct_size = sizeof(d);
+        d.device = query.device_index();
+        d.stream = current_stream();
+        d.dtype = dtype_of(query, "scaled_dot_product_attention");
+        d.B = B; d.Hq = Hq; d.Hkv = Hkv; d.D = static_cast<int>(D); d.scale = scale;
+        d.q = view4(query); d.o = view4(out);
+        d.k_cache = view4(key); d.v_cache = view4(value);
+        d.cache_cap = static_cast<int>(L);
+        d.uniform_len = static_cast<int>(L);
+        d.max_len = static_cast<int>(L);
+        Tensor ws = workspace(vb200_decode_workspace_bytes(&d));
+        d.workspace = ws.data_ptr<char>();
+        d.workspace_bytes = ws.numel() * 4;
+        check(vb200_decode_fwd(&d), "scaled_dot_product_attention");
+        return out;
+    }
     vb200_prefill_args a{};
     a.struct_size = sizeof(a);
     a.device = query.device_index();
     a.stream = current_stream();
     a.dtype = dtype_of(query, "scaled_dot_product_attention");
-    a.B = static_cast<int>(query.shape()[0]); a.Hq = static_cast<int>(query.shape()[1]); a.Hkv = static_cast<int>(key.shape()[1]);
+    a.B = B; a.Hq = Hq; a.Hkv = Hkv;
     a.T = static_cast<int>(T); a.D = static_cast<int>(D);
     a.start_pos = static_cast<int>(L - T);
     a.causal = is_causal ? 1 : 0;
     a.scale = scale;
-    Tensor k_tail = key.narrow(2, L - T, T), v_tail = value.narrow(2, L - T, T);
-    a.q = view4(query); a.k = view4(k_tail); a.v = view4(v_tail); a.o = view4(out);
+    a.q = view4(query); a.o = view4(out);
     a.k_cache = view4(key); a.v_cache = view4(value);
     a.cache_cap = static_cast<int>(L);
+    a.cache_read_only = 1;
     check(vb200_prefill_fwd(&a), "scaled_dot_product_attention");
     return out;
 }

@@ -3,6 +3,7 @@
 // arrays in, host arrays out; errors come back as -1 with the text in vbh_last_error().
 #include <vesper/generation/generator.h>
 #include <vesper/models/transformer.h>
+#include <vesper/nn/gqa_attention.h>
 
 #include <cstring>
 #include <string>
@@ -20,9 +21,76 @@ Tensor ids_to_device(const int32_t* ids, int64_t B, int64_t T) {
     t.copy_from_host(ids);
     return t;
 }
+// host fp32 <-> device tensor of the module's dtype
+Tensor act_to_device(const float* x, const std::vector<int64_t>& shape, DType dt) {
+    Tensor t = vesper::empty(shape, dt, Device::CUDA);
+    if (dt == DType::Float32) { t.copy_from_host(x); return t; }
+    std::vector<uint16_t> h(t.numel());
+    for (size_t i = 0; i < h.size(); ++i) h[i] = vesper::float_to_bf16(x[i]);
+    t.copy_from_host(h.data());
+    return t;
+}
+void act_to_host(const Tensor& y, float* out) {
+    Tensor c = y.is_contiguous() ? y : y.contiguous();
+    if (c.dtype() == DType::Float32) { c.copy_to_host(out); return; }
+    std::vector<uint16_t> h(c.numel());
+    c.copy_to_host(h.data());
+    for (size_t i = 0; i < h.size(); ++i) out[i] = vesper::bf16_to_float(h[i]);
+}
+struct AttnModule {
+    std::unique_ptr<vesper::nn::GroupedQueryAttention> gqa;
+    std::unique_ptr<vesper::nn::MultiHeadAttention> mha;
+    DType dt;
+};
 }  // namespace
 
 extern "C" {
+
+// ---- nn::GroupedQueryAttention / nn::MultiHeadAttention / nn::KVCache ----
+// kind 0: GroupedQueryAttention(embed_dim, num_heads, num_kv_heads, max_seq_len, rope_base, 0, bias);
+// kind 1: MultiHeadAttention(embed_dim, num_heads, 0, use_rope).  dtype 0 = Float32, 1 = BFloat16.
+void* vbh_attn_new(int kind, int64_t embed_dim, int64_t num_heads, int64_t num_kv_heads, int64_t max_seq_len, float rope_base,
+                   int bias, int use_rope, int dtype) {
+    try {
+        auto m = std::make_unique<AttnModule>();
+        m->dt = dtype == 0 ? DType::Float32 : DType::BFloat16;
+        if (kind == 0) m->gqa = std::make_unique<vesper::nn::GroupedQueryAttention>(embed_dim, num_heads, num_kv_heads, max_seq_len, rope_base, 0.0f, bias != 0, m->dt);
+        else m->mha = std::make_unique<vesper::nn::MultiHeadAttention>(static_cast<int>(embed_dim), static_cast<int>(num_heads), 0.0f, use_rope != 0, m->dt);
+        return m.release();
+    } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
+}
+void vbh_attn_free(void* m) { delete static_cast<AttnModule*>(m); }
+// host fp32 weights in the reference's layouts: input projection [out, in] (+ bias [out], nullable), output projection
+int vbh_attn_load(void* h, const float* w_in, const float* b_in, const float* w_out, const float* b_out) {
+    try {
+        auto* m = static_cast<AttnModule*>(h);
+        if (m->gqa) { m->gqa->wqkv().load_weight(w_in, b_in); m->gqa->wo().load_weight(w_out, b_out); }
+        else { m->mha->c_attn.load_weight(w_in, b_in); m->mha->c_proj.load_weight(w_out, b_out); }
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+void* vbh_kvcache_new(int64_t B, int64_t H, int64_t max_seq_len, int64_t D, int dtype) {
+    try {
+        return new vesper::nn::KVCache(static_cast<int>(B), static_cast<int>(H), static_cast<int>(max_seq_len), static_cast<int>(D), Device::CUDA,
+                                       dtype == 0 ? DType::Float32 : DType::BFloat16);
+    } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
+}
+void vbh_kvcache_free(void* c) { delete static_cast<vesper::nn::KVCache*>(c); }
+int vbh_kvcache_len(void* c) { return static_cast<vesper::nn::KVCache*>(c)->current_seq_len(); }
+// mode 0: forward(x); 1: forward(x, causal); 2: forward(x, cache, start_pos).  x, y: host fp32 [B, T, embed_dim].
+int vbh_attn_forward(void* h, const float* x_host, int64_t B, int64_t T, int64_t C, int mode, int causal, void* cache, int64_t start_pos,
+                     float* y_host) {
+    try {
+        auto* m = static_cast<AttnModule*>(h);
+        Tensor x = act_to_device(x_host, {B, T, C}, m->dt);
+        auto* kc = static_cast<vesper::nn::KVCache*>(cache);
+        Tensor y;
+        if (m->gqa) y = mode == 0 ? m->gqa->forward(x) : mode == 1 ? m->gqa->forward(x, causal != 0) : m->gqa->forward(x, kc, start_pos);
+        else y = mode == 0 ? m->mha->forward(x) : mode == 1 ? m->mha->forward(x, causal != 0) : m->mha->forward(x, kc, static_cast<int>(start_pos));
+        act_to_host(y, y_host);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
 
 const char* vbh_last_error() { return g_err.c_str(); }
 

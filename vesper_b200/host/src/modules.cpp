@@ -44,40 +44,60 @@ void require(const Tensor& t, DType dt, const char* who) {
     if (t.dtype() != dt) throw std::runtime_error(std::string(who) + ": unexpected dtype");
 }
 
+Tensor weight_from_host(const float* src, const std::vector<int64_t>& shape, DType dt) {
+    if (dt == DType::BFloat16) return bf16_from_host(src, shape);
+    Tensor t = empty(shape, DType::Float32, Device::CUDA);
+    t.copy_from_host(src);
+    return t;
+}
+
 Tensor run_linear(const Tensor& input, const Tensor& weight, const Tensor& bias, int64_t in_f, int64_t out_f, int epilogue, const char* who) {
-    require(input, DType::BFloat16, who);
+    require(input, weight.dtype(), who);
     const int64_t M = leading_rows(input, in_f, who);
     Tensor x = input.is_contiguous() ? input : input.contiguous();
     const int64_t out_cols = epilogue == VB200_EPI_SWIGLU ? out_f / 2 : out_f;
-    Tensor out = empty(with_last(input, out_cols), DType::BFloat16, Device::CUDA);
+    Tensor out = empty(with_last(input, out_cols), weight.dtype(), Device::CUDA);
+    if (weight.dtype() == DType::Float32) {
+        if (epilogue != VB200_EPI_BF16) throw std::runtime_error(std::string(who) + ": the Float32 path has no fused epilogue");
+        check(vb200_linear_f32(x.device_index(), current_stream(), x.data_ptr<float>(), in_f, weight.data_ptr<float>(), in_f,
+                               bias.defined() ? bias.data_ptr<float>() : nullptr, out.data_ptr<float>(), out_cols, static_cast<int>(M),
+                               static_cast<int>(out_f), static_cast<int>(in_f)), who);
+        return out;
+    }
     check(vb200_linear_bias(x.device_index(), current_stream(), x.data_ptr<char>(), in_f, weight.data_ptr<char>(), in_f,
                             bias.defined() ? bias.data_ptr<float>() : nullptr, out.data_ptr<char>(), out_cols, static_cast<int>(M),
                             static_cast<int>(out_f), static_cast<int>(in_f), epilogue, 0), who);
     return out;
 }
 
+void require_dtype(DType dt, const char* who) {
+    if (dt != DType::BFloat16 && dt != DType::Float32) throw std::runtime_error(std::string(who) + ": dtype must be BFloat16 or Float32");
+}
+
 }  // namespace
 
-Linear::Linear(int64_t in_features, int64_t out_features, bool use_bias, Device device)
-    : in_features_(in_features), out_features_(out_features), use_bias_(use_bias) {
+Linear::Linear(int64_t in_features, int64_t out_features, bool use_bias, Device device, DType dtype)
+    : in_features_(in_features), out_features_(out_features), use_bias_(use_bias), dtype_(dtype) {
     if (device != Device::CUDA) throw std::runtime_error("Linear: this library is the CUDA backend");
-    weight = zeros({out_features, in_features}, DType::BFloat16, Device::CUDA);
+    require_dtype(dtype, "Linear");
+    weight = zeros({out_features, in_features}, dtype, Device::CUDA);
     if (use_bias) bias = zeros({out_features}, DType::Float32, Device::CUDA);
 }
 void Linear::load_weight(const float* host_weight, const float* host_bias) {
-    weight = bf16_from_host(host_weight, {out_features_, in_features_});
+    weight = weight_from_host(host_weight, {out_features_, in_features_}, dtype_);
     if (use_bias_ && host_bias) bias.copy_from_host(host_bias);
 }
 Tensor Linear::forward(const Tensor& input) { return run_linear(input, weight, bias, in_features_, out_features_, VB200_EPI_BF16, "Linear"); }
 
-FusedQKVLinear::FusedQKVLinear(int64_t in_features, int64_t q_features, int64_t kv_features, bool use_bias, Device device)
-    : in_features_(in_features), q_features_(q_features), kv_features_(kv_features), use_bias_(use_bias) {
+FusedQKVLinear::FusedQKVLinear(int64_t in_features, int64_t q_features, int64_t kv_features, bool use_bias, Device device, DType dtype)
+    : in_features_(in_features), q_features_(q_features), kv_features_(kv_features), use_bias_(use_bias), dtype_(dtype) {
     if (device != Device::CUDA) throw std::runtime_error("FusedQKVLinear: this library is the CUDA backend");
-    weight = zeros({q_features + 2 * kv_features, in_features}, DType::BFloat16, Device::CUDA);
+    require_dtype(dtype, "FusedQKVLinear");
+    weight = zeros({q_features + 2 * kv_features, in_features}, dtype, Device::CUDA);
     if (use_bias) bias = zeros({q_features + 2 * kv_features}, DType::Float32, Device::CUDA);
 }
 void FusedQKVLinear::load_weight(const float* host_weight, const float* host_bias) {
-    weight = bf16_from_host(host_weight, {q_features_ + 2 * kv_features_, in_features_});
+    weight = weight_from_host(host_weight, {q_features_ + 2 * kv_features_, in_features_}, dtype_);
     if (use_bias_ && host_bias) bias.copy_from_host(host_bias);
 }
 Tensor FusedQKVLinear::forward(const Tensor& input) {

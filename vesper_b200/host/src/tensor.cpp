@@ -195,6 +195,15 @@ Tensor Tensor::index(const std::vector<IndexSelector>& selectors) const {
     return Tensor(storage_, shape, strides, off, dtype_);
 }
 
+Tensor Tensor::unflatten_last(int64_t outer, int64_t inner) const {
+    if (ndim() < 1 || strides_.back() != 1 || shape_.back() != outer * inner)
+        throw std::runtime_error("unflatten_last: the last dimension must be contiguous and equal outer * inner");
+    std::vector<int64_t> shape(shape_.begin(), shape_.end() - 1), strides(strides_.begin(), strides_.end() - 1);
+    shape.push_back(outer); shape.push_back(inner);
+    strides.push_back(inner); strides.push_back(1);
+    return Tensor(storage_, shape, strides, offset_, dtype_);
+}
+
 Tensor Tensor::narrow(int64_t dim, int64_t start, int64_t length) const {
     if (dim < 0) dim += ndim();
     std::vector<IndexSelector> sel(static_cast<size_t>(dim) + 1, Slice());

@@ -179,8 +179,8 @@ void TransformerLM::ensure_buffers(int64_t rows, int64_t batch) {
     b.qkv = empty({rows, qkv_n}, DType::BFloat16, Device::CUDA);
     b.attn = empty({rows, config_.n_heads * D}, DType::BFloat16, Device::CUDA);
     b.act = empty({rows, hid}, DType::BFloat16, Device::CUDA);
-    // attention workspace: the larger of the prompt pass's angle table and the split-KV partials of a
-    // decode step planned for the longest sequence the cache can hold
+    // attention workspace: the larger of the prompt pass's angle table and the split-KV partials of the
+    // most demanding decode step the cache capacity allows
     vb200_prefill_args pa{};
     pa.struct_size = sizeof(pa);
     pa.dtype = VB200_BF16;
@@ -193,8 +193,10 @@ void TransformerLM::ensure_buffers(int64_t rows, int64_t batch) {
     da.struct_size = sizeof(da);
     da.dtype = VB200_BF16;
     da.B = static_cast<int>(batch); da.Hq = pa.Hq; da.Hkv = pa.Hkv; da.D = pa.D;
-    da.cache_cap = static_cast<int>(config_.max_seq_len); da.max_len = static_cast<int>(config_.max_seq_len);
-    ws = std::max(ws, vb200_decode_workspace_bytes(&da));
+    da.cache_cap = static_cast<int>(config_.max_seq_len);
+    // the split plan is not monotone in the step's max_len (a shorter context can take more, smaller splits),
+    // and steps run both with a common length and with the device length array: size for the worst of them
+    ws = std::max(ws, vb200_decode_workspace_bytes_max(&da));
     b.attn_ws = empty({static_cast<int64_t>((ws + 255) / 256 * 64)}, DType::Float32, Device::CUDA);
     b.rows = rows;
     b.batch = batch;

@@ -12,7 +12,8 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 HOST_LIB_PATH = os.path.join(PKG, "lib", "libvesper_b200_host.so")
 
 HOST_EXPORTS = ["vbh_last_error", "vbh_model_new", "vbh_model_free", "vbh_model_set_param", "vbh_model_init_cache",
-                "vbh_model_forward_with_cache", "vbh_generate_greedy"]
+                "vbh_model_forward_with_cache", "vbh_generate_greedy", "vbh_attn_new", "vbh_attn_free", "vbh_attn_load",
+                "vbh_kvcache_new", "vbh_kvcache_free", "vbh_kvcache_len", "vbh_attn_forward"]
 
 _host = None
 _i64 = C.c_int64
@@ -38,6 +39,15 @@ def load_host():
     L.vbh_model_forward_with_cache.argtypes = [C.c_void_p, _i32p, _i64, _i64, _i64, C.c_int, _f32p]
     L.vbh_generate_greedy.argtypes = [C.c_void_p, _i32p, _i64, _i64, _i64, C.POINTER(_i64), _i64, _i64, C.c_int, _i32p, C.POINTER(C.c_double)]
     L.vbh_generate_greedy.restype = _i64
+    L.vbh_attn_new.argtypes = [C.c_int, _i64, _i64, _i64, _i64, C.c_float, C.c_int, C.c_int, C.c_int]
+    L.vbh_attn_new.restype = C.c_void_p
+    L.vbh_attn_free.argtypes = [C.c_void_p]
+    L.vbh_attn_load.argtypes = [C.c_void_p, _f32p, _f32p, _f32p, _f32p]
+    L.vbh_kvcache_new.argtypes = [_i64, _i64, _i64, _i64, C.c_int]
+    L.vbh_kvcache_new.restype = C.c_void_p
+    L.vbh_kvcache_free.argtypes = [C.c_void_p]
+    L.vbh_kvcache_len.argtypes = [C.c_void_p]
+    L.vbh_attn_forward.argtypes = [C.c_void_p, _f32p, _i64, _i64, _i64, C.c_int, C.c_int, C.c_void_p, _i64, _f32p]
     _host = L
     return L
 
@@ -108,3 +118,63 @@ class TransformerLM:
 
     def __del__(self):
         self.close()
+
+
+def _fp(a):
+    return None if a is None else a.ctypes.data_as(_f32p)
+
+
+class KVCache:
+    """nn::KVCache of the host layer ([B, H, max_seq_len, D] on the GPU; dtype "f32" or "bf16")."""
+
+    def __init__(self, B, H, max_seq_len, D, dtype="bf16"):
+        self.L = load_host()
+        self.h = self.L.vbh_kvcache_new(B, H, max_seq_len, D, 0 if dtype == "f32" else 1)
+        if not self.h:
+            raise RuntimeError(self.L.vbh_last_error().decode())
+
+    def __len__(self):
+        return self.L.vbh_kvcache_len(self.h)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.L.vbh_kvcache_free(self.h)
+            self.h = None
+
+
+class AttentionModule:
+    """nn::GroupedQueryAttention (kind "gqa") or nn::MultiHeadAttention (kind "mha") of the host layer, with the
+    reference's constructor arguments and forward overloads; host fp32 arrays in and out."""
+
+    def __init__(self, kind, embed_dim, num_heads, num_kv_heads=None, max_seq_len=4096, rope_base=10000.0, bias=False,
+                 use_rope=True, dtype="bf16"):
+        self.L = load_host()
+        self.C = embed_dim
+        self.h = self.L.vbh_attn_new(0 if kind == "gqa" else 1, embed_dim, num_heads, num_kv_heads or num_heads, max_seq_len, rope_base,
+                                     int(bias), int(use_rope), 0 if dtype == "f32" else 1)
+        if not self.h:
+            raise RuntimeError(self.L.vbh_last_error().decode())
+
+    def load(self, w_in, w_out, b_in=None, b_out=None):
+        arrs = [None if a is None else np.ascontiguousarray(a, np.float32) for a in (w_in, b_in, w_out, b_out)]
+        if self.L.vbh_attn_load(self.h, *[_fp(a) for a in arrs]) != 0:
+            raise RuntimeError(self.L.vbh_last_error().decode())
+
+    def _run(self, x, mode, causal, cache, start_pos):
+        x = np.ascontiguousarray(x, np.float32)
+        B, T, C_ = x.shape
+        y = np.empty_like(x)
+        if self.L.vbh_attn_forward(self.h, _fp(x), B, T, C_, mode, int(causal), cache.h if cache is not None else None, start_pos, _fp(y)) != 0:
+            raise RuntimeError(self.L.vbh_last_error().decode())
+        return y
+
+    def forward(self, x, causal=None):
+        return self._run(x, 0, False, None, 0) if causal is None else self._run(x, 1, causal, None, 0)
+
+    def forward_cached(self, cache, x, start_pos):
+        return self._run(x, 2, False, cache, start_pos)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.L.vbh_attn_free(self.h)
+            self.h = None
