@@ -499,7 +499,7 @@ def bench_sharded(cx, nsteps=50):
     if world > 1:
         try:
             exchange = PeerExchange(cx.dist, world, cx.rank, Bq * Hq, D, dev)
-        except Exception as e:                      # no peer mapping on this box: the all-gather path still runs
+        except Exception as e:                      # peer memory could not be mapped: the all-gather path still runs
             exchange_error = f"{type(e).__name__}: {e}"[:200]
 
     def step_gather():

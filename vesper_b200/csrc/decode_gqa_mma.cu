@@ -409,12 +409,13 @@ int launch_decode_gqa_mma_split(cudaStream_t s, const DecodeParams& p) {
     if (int rc = make_kv_map(&maps.k, p.dtype, p.k_cache, p.cache_cap, p.Hkv, p.B)) return rc;
     if (int rc = make_kv_map(&maps.v, p.dtype, p.v_cache, p.cache_cap, p.Hkv, p.B)) return rc;
     auto kernel = decode_gqa_mma_kernel<T, NREP, CW, kStages, MINB>;
-    static thread_local int configured_dev = -1;
+    static thread_local bool configured[64] = {};      // per device ordinal: the attribute belongs to the device's context
     int dev = 0;
     VB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_dev != dev) {
+    if (dev < 0 || dev >= 64) return set_detail(VB200_ERR_NO_DEVICE, "device ordinal out of range");
+    if (!configured[dev]) {
         VB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        configured_dev = dev;
+        configured[dev] = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(p.num_splits, p.Hkv, p.B);

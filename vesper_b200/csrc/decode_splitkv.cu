@@ -543,14 +543,15 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
         constexpr size_t kBaseSmem = decode_base_smem<T, NREP, CW, kStages>();
         constexpr size_t kRxRow = NREP * (D + 2) * sizeof(float);                       // one split's (acc, m, l) per head
         static_assert(2 * CW * NREP * 128 * 4 + 2 * 2 * CW * NREP * 4 <= 2 * kTile * 128 * sizeof(T), "merge buffers must fit in the first ring stage (the second may hold the cluster receive area)");
-        static thread_local int configured_dev = -1;
+        static thread_local bool configured[64] = {};      // per device ordinal: the attribute belongs to the device's context
         int dev = 0;
         VB200_CUDA_TRY(cudaGetDevice(&dev));
-        if (configured_dev != dev) {
+        if (dev < 0 || dev >= 64) return set_detail(VB200_ERR_NO_DEVICE, "device ordinal out of range");
+    if (!configured[dev]) {
             VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 static_cast<int>(kBaseSmem)));
             VB200_CUDA_TRY(cudaFuncSetAttribute(decode_splitkv_kernel<T, NREP, CW, kStages, MINB>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-            configured_dev = dev;
+            configured[dev] = true;
         }
         // Up to 16 one-tile splits per (batch, kv_head): they run as one thread-block cluster that merges its partials
         // through distributed shared memory and writes the final rows -- the combine kernel and the workspace round

@@ -168,13 +168,14 @@ size_t bwd_smem_bytes(int D) { return sizeof(float) * (4 * kT * (D + 1) + 2 * kT
 template <int DMAX>
 int launch_bwd_t(cudaStream_t s, const AttnBwdParams& p) {
     const size_t smem = bwd_smem_bytes(p.D);
-    static thread_local int configured_dev = -1;
+    static thread_local bool configured[64] = {};      // per device ordinal: the attribute belongs to the device's context
     int dev = 0;
     VB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_dev != dev) {
+    if (dev < 0 || dev >= 64) return set_detail(VB200_ERR_NO_DEVICE, "device ordinal out of range");
+    if (!configured[dev]) {
         VB200_CUDA_TRY(cudaFuncSetAttribute(bwd_dkdv_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bwd_smem_bytes(DMAX))));
         VB200_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bwd_smem_bytes(DMAX))));
-        configured_dev = dev;
+        configured[dev] = true;
     }
     const long long rows = static_cast<long long>(p.B) * p.H * p.N;
     bwd_delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, s>>>(p.d_out, p.out, p.delta, rows, p.D);

@@ -48,6 +48,7 @@ struct PrefillParams {
 };
 int launch_prefill_f32(cudaStream_t s, const PrefillParams& p);
 int launch_prefill_sm100(cudaStream_t s, const PrefillParams& p);
+int launch_prefill_pair_sm100(cudaStream_t s, const PrefillParams& p);   // head_dim 128: two SMs per work item (cta_group::2)
 
 // ---- decode_splitkv.cu ----
 struct DecodeParams {

@@ -563,14 +563,15 @@ int make_map_2d(CUtensorMap* m, const void* ptr, long long rows, long long K, lo
 }
 
 // Raises the dynamic shared memory limit of one kernel instantiation once per device and thread;
-// `configured_dev` is the caller's (per instantiation) thread-local marker.
+// `configured` is the caller's (per instantiation) thread-local array of 64 markers, one per device ordinal.
 template <typename Kernel>
-int set_smem_once(Kernel kernel, int bytes, int* configured_dev) {
+int set_smem_once(Kernel kernel, int bytes, bool* configured) {
     int dev = 0;
     VB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (*configured_dev != dev) {
+    if (dev < 0 || dev >= 64) return set_detail(VB200_ERR_NO_DEVICE, "device ordinal out of range");
+    if (!configured[dev]) {
         VB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-        *configured_dev = dev;
+        configured[dev] = true;
     }
     return VB200_OK;
 }
@@ -589,8 +590,8 @@ int launch_wide(cudaStream_t s, const LinearParams& p) {
     if (int rc = make_map_2d(&maps.a, p.x, p.M, p.K, p.ldx, kTileA)) return rc;
     if (int rc = make_map_2d(&maps.b, p.w, p.N, p.K, p.ldw, BN)) return rc;
     auto kernel = linear_wide_kernel<BN, EPI>;
-    static thread_local int configured_dev = -1;
-    if (int rc = set_smem_once(kernel, C::kSmemBytes, &configured_dev)) return rc;
+    static thread_local bool configured[64] = {};
+    if (int rc = set_smem_once(kernel, C::kSmemBytes, configured)) return rc;
     int sms = 0;
     if (int rc = sm_count(&sms)) return rc;
     const int tiles = ((p.M + kTileA - 1) / kTileA) * ((p.N + BN - 1) / BN);
@@ -626,8 +627,8 @@ int launch_skinny(cudaStream_t s, const LinearParams& p) {
     if (int rc = make_map_2d(&maps.a, p.w, p.N, p.K, p.ldw, kTileA)) return rc;
     if (int rc = make_map_2d(&maps.b, p.x, p.M, p.K, p.ldx, MT)) return rc;
     auto kernel = linear_skinny_kernel<MT, EPI>;
-    static thread_local int configured_dev = -1;
-    if (int rc = set_smem_once(kernel, C::kSmemBytes, &configured_dev)) return rc;
+    static thread_local bool configured[64] = {};
+    if (int rc = set_smem_once(kernel, C::kSmemBytes, configured)) return rc;
     int sms = 0;
     if (int rc = sm_count(&sms)) return rc;
     const int n_tiles = (p.N + kTileA - 1) / kTileA;

@@ -203,12 +203,13 @@ __global__ void __launch_bounds__(kThreads) prefill_f32_kernel(PrefillParams p) 
 int launch_prefill_f32(cudaStream_t s, const PrefillParams& p) {
     if (p.D % 4 != 0 || p.D > 128 || p.D < 4) return set_detail(VB200_ERR_UNSUPPORTED, "fp32 attention needs head_dim % 4 == 0 and <= 128");
     size_t smem = sizeof(float) * (static_cast<size_t>(kBM + 2 * kBN) * (p.D + 4) + kBM * (kBN + 4));
-    static thread_local int configured_dev = -1;
+    static thread_local bool configured[64] = {};      // per device ordinal: the attribute belongs to the device's context
     int dev = 0;
     VB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_dev != dev) {
+    if (dev < 0 || dev >= 64) return set_detail(VB200_ERR_NO_DEVICE, "device ordinal out of range");
+    if (!configured[dev]) {
         VB200_CUDA_TRY(cudaFuncSetAttribute(prefill_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024));
-        configured_dev = dev;
+        configured[dev] = true;
     }
     dim3 grid((p.T + kBM - 1) / kBM, p.Hq, p.B);
     prefill_f32_kernel<<<grid, kThreads, smem, s>>>(p);

@@ -24,6 +24,7 @@
 // Every wait is bounded (see mbar_wait); on expiry the CTA drains and returns
 // with the device status word set.
 #include <cstdio>
+#include <cstdlib>
 
 #include "kernels.h"
 
@@ -43,30 +44,12 @@ constexpr int kThreads = 384;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;
+constexpr int kEpiBatch = 2;         // TMEM loads (32 columns each) in flight per wait in the epilogue
 
-// tuning knobs (compile-time)
-#ifndef VB_REG_SOFTMAX
-#define VB_REG_SOFTMAX 216     // registers per thread of the two softmax warpgroups
-#endif
-#ifndef VB_REG_OTHER
-#define VB_REG_OTHER 72        // registers per thread of the producer / MMA / RoPE warpgroup
-#endif
-#ifndef VB_PACKED_MATH
-#define VB_PACKED_MATH 1       // fp32x2 FMA/add in the softmax
-#endif
-#ifndef VB_MAX3
-#define VB_MAX3 0              // 3-input max in the row maximum
-#endif
-static_assert(VB_REG_SOFTMAX * 256 + VB_REG_OTHER * 128 <= 168 * 384, "register budget");
-
-#ifdef VB_TIMING
-// Development aid: per-CTA cycle counters, [cta][item][slot], written when the buffer is set.
-__device__ long long* g_timing_buf = nullptr;
-#define VB_T(slot, value)                                                                   \
-    do { if (g_timing_buf && item_no < 16) g_timing_buf[(blockIdx.x * 16 + item_no) * 16 + (slot)] = (value); } while (0)
-#else
-#define VB_T(slot, value) do { } while (0)
-#endif
+// Register split after setmaxnreg: the two softmax warpgroups (one thread per row holds a 128-column score tile)
+// take 216 registers per thread, the producer / MMA / RoPE warpgroup 72.
+constexpr int kRegSoftmax = 216, kRegOther = 72;
+static_assert(kRegSoftmax * 256 + kRegOther * 128 <= 168 * 384, "register budget");
 
 struct __align__(8) Barriers {
     uint64_t q_full[kQBufs], q_rot[kQBufs], q_free[kQBufs];
@@ -89,10 +72,6 @@ struct Cfg {
     static constexpr int kSmemBytes = (kQBufs + kStages) * kTileBytes + 1024 /*alignment slack*/ + 256 /*Barriers*/;
 };
 
-#ifndef VB_HEAD_PAIRS
-#define VB_HEAD_PAIRS 1        // pair the tiles of two heads of a group (equal work) instead of two row tiles of one head
-#endif
-
 // One unit of work: two 128-row query tiles that read the same K/V blocks.  With an even number of
 // query heads per KV head the two tiles are the SAME rows of two heads of one group: both visit the
 // same number of key blocks, so neither softmax warpgroup idles in the last iteration (adjacent row
@@ -106,7 +85,7 @@ struct Item {
 };
 
 __host__ __device__ __forceinline__ bool pair_by_heads(const PrefillParams& p) {
-    return VB_HEAD_PAIRS && ((p.Hq / p.Hkv) % 2 == 0);
+    return (p.Hq / p.Hkv) % 2 == 0;
 }
 // number of (batch, head or head pair) columns and of row steps of the item grid
 __host__ __device__ __forceinline__ int item_cols(const PrefillParams& p) { return pair_by_heads(p) ? p.B * (p.Hq / 2) : p.B * p.Hq; }
@@ -202,7 +181,7 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
 
     if (warp >= 8) {
         // the data-movement / issue / RoPE warpgroup needs few registers; the softmax warpgroups take them
-        reg_dec<VB_REG_OTHER>();
+        reg_dec<kRegOther>();
         if (warp == kProducerWarp) {
             // =========================== TMA producer ===========================
             if (lane == 0) {
@@ -276,18 +255,13 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 int kv_item = 0, q_seq = 0;
                 int blk0 = 0, blk1 = 0;          // running count of score tiles per query tile (barrier phases)
                 bool ok = true;
-                int item_no = -1;
                 for (int round = 0; round < n_rounds && ok; ++round) {
                     const int idx = item_of_round(round, n_items);
                     if (idx < 0) continue;
-                    ++item_no;
                     const Item w = get_item(p, idx, n_bh, n_pairs);
                     int qbuf[2] = {0, 0};
                     const int k0_slot = kv_item % kStages;
-                    long long tm0 = clock64();
-                    VB_T(0, tm0);
                     ok = mbar_wait(&bar->kv_full[k0_slot], (kv_item / kStages) & 1, abort_flag, 0x200);
-                    VB_T(1, clock64() - tm0);
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
                         if (w.nblk[t] == 0 || !ok) continue;
@@ -295,9 +269,7 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                         const int ph = (q_seq / kQBufs) & 1;
                         ++q_seq;
                         // S of this tile is free: every PV of the previous item was issued before this point
-                        long long tq0 = clock64();
                         ok = mbar_wait(rope ? &bar->q_rot[qbuf[t]] : &bar->q_full[qbuf[t]], ph, abort_flag, 0x210 + t);
-                        VB_T(2 + t, clock64() - tq0);
                         if (!ok) continue;
                         tc_fence_after();
                         issue_qk(t, qbuf[t], k0_slot);
@@ -338,8 +310,6 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                         if (j + 1 < w.nmax) umma_commit(&bar->kv_empty[k_slot]);
                     }
                     kv_item += 2 * w.nmax;
-                    VB_T(4, clock64() - tm0);
-                    VB_T(5, w.nmax);
                 }
                 // everything issued so far has to retire before TMEM is released
                 umma_commit(&bar->mma_done);
@@ -359,21 +329,16 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
             for (int e = 0; e < 4; ++e) sincosf(2.0f * p.inv_freq.v[(c * 4 + e) & (kMaxHalfDim - 1)], &step_s[e], &step_c[e]);
             int q_seq = 0;
             bool ok = true;
-            int item_no = -1;
             for (int round = 0; round < n_rounds && ok; ++round) {
                 const int idx = item_of_round(round, n_items);
                 if (idx < 0) continue;
-                ++item_no;
                 const Item w = get_item(p, idx, n_bh, n_pairs);
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     if (w.nblk[t] == 0 || !ok) continue;
                     const int b = q_seq % kQBufs, ph = (q_seq / kQBufs) & 1;
                     ++q_seq;
-                    long long tr0 = clock64();
                     ok = mbar_wait_warp(&bar->q_full[b], ph, abort_flag, 0x700 + b);
-                    long long tr1 = clock64();
-                    if (tid == kRopeWarp0 * 32) { VB_T(6 + 4 * t, tr0); VB_T(7 + 4 * t, tr1 - tr0); }
                     if (!ok) continue;
                     if (c < D / 8) {
                         unsigned char* qtile = q_smem + b * C::kTileBytes + (c >> 3) * C::kHalfBytes;
@@ -442,13 +407,12 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                     }
                     fence_proxy_async_smem();        // generic-proxy writes -> visible to the tensor core's smem reads
                     mbar_arrive(&bar->q_rot[b]);
-                    if (tid == kRopeWarp0 * 32) { VB_T(8 + 4 * t, clock64() - tr1); VB_T(9 + 4 * t, clock64()); }
                 }
             }
         }
     } else {
         // =========================== softmax / correction / epilogue ===========================
-        reg_inc<VB_REG_SOFTMAX>();
+        reg_inc<kRegSoftmax>();
         const int t = warp >> 2;                     // tile of this warpgroup
         const int r = tid & 127;                     // row inside the tile = TMEM lane
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -457,14 +421,11 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
         const float scale_log2 = p.scale * kLog2e;
         int g = 0;                                   // running count of score tiles of this query tile
         bool ok = true;
-        int item_no = -1;
 
         for (int round = 0; round < n_rounds && ok; ++round) {
             const int idx = item_of_round(round, n_items);
             if (idx < 0) continue;
-            ++item_no;
             const Item w = get_item(p, idx, n_bh, n_pairs);
-            long long t_wait = 0, t_comp = 0, t_epi = 0;
             const int n = t ? w.nblk[1] : w.nblk[0];
             if (n == 0) continue;
             const int tile_r0 = t ? w.r0[1] : w.r0[0];
@@ -472,15 +433,8 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
 
             float m_ref = -INFINITY, l_sum = 0.f;
             for (int j = 0; j < n; ++j, ++g) {
-#ifdef VB_TIMING
-                long long ta = clock64();
-#endif
                 ok = mbar_wait_warp(&bar->s_full[t], g & 1, abort_flag, 0x800 + t);
                 if (!ok) break;
-#ifdef VB_TIMING
-                long long tb_ = clock64();
-                t_wait += tb_ - ta;
-#endif
                 tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
@@ -505,11 +459,7 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-#if VB_MAX3
-                        mx8[(i >> 1) & 7] = fmax3(mx8[(i >> 1) & 7], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
-#else
                         mx8[(i >> 1) & 7] = fmaxf(mx8[(i >> 1) & 7], fmaxf(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
-#endif
                     }
                 const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
                 const float m_cand = mx * scale_log2;
@@ -547,17 +497,10 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                         const int c = 2 * half + cc;
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
-#if VB_PACKED_MATH
                             // packed fp32x2: one FMA and one add per pair of columns
                             const float2 e = __ffma2_rn(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nm2);
                             const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
                             rs[(i >> 1) & 3] = __fadd2_rn(rs[(i >> 1) & 3], pp);
-#else
-                            const float2 pp = make_float2(fast_exp2(fmaf(__uint_as_float(s[c][i]), sc2.x, nm2.x)),
-                                                          fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), sc2.x, nm2.x)));
-                            rs[(i >> 1) & 3].x += pp.x;
-                            rs[(i >> 1) & 3].y += pp.y;
-#endif
                             pk[cc * 16 + (i >> 1)] = Elem<T>::pack2(pp.x, pp.y);
                         }
                     }
@@ -567,14 +510,8 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(&bar->p_ready[t]);
-#ifdef VB_TIMING
-                t_comp += clock64() - tb_;
-#endif
             }
             if (!ok) break;
-#ifdef VB_TIMING
-            long long te0 = clock64();
-#endif
 
             // ---- epilogue of this item: O / l -> global, LSE ----
             ok = mbar_wait_warp(&bar->o_done[t], (g - 1) & 1, abort_flag, 0xA00 + t);
@@ -583,24 +520,17 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
             const float inv_l = 1.0f / l_sum;
             const int hq_t = t ? w.hq1 : w.hq;
             T* orow = static_cast<T*>(p.o.ptr) + w.b * p.o.sb + hq_t * p.o.sh + static_cast<long long>(row) * p.o.ss;
-#ifndef VB_EPI_WIDE
-#define VB_EPI_WIDE 1          // 1: several TMEM loads in flight per wait and 32-byte global stores in the epilogue (3 % faster at S = 2048)
-#endif
-#ifndef VB_EPI_BATCH
-#define VB_EPI_BATCH 2         // TMEM loads (32 columns each) per wait
-#endif
-#if VB_EPI_WIDE
             const bool o32 = (reinterpret_cast<uintptr_t>(orow) & 31) == 0;     // every segment offset below is a multiple of 32 bytes
 #pragma unroll
-            for (int c = 0; c < D / 32; c += VB_EPI_BATCH) {
-                uint32_t o[VB_EPI_BATCH][32];
+            for (int c = 0; c < D / 32; c += kEpiBatch) {
+                uint32_t o[kEpiBatch][32];
 #pragma unroll
-                for (int h2 = 0; h2 < VB_EPI_BATCH; ++h2)
+                for (int h2 = 0; h2 < kEpiBatch; ++h2)
                     if (c + h2 < D / 32) tmem_ld32(o_addr + (c + h2) * 32, o[h2]);
                 tmem_ld_wait();
                 if (row < p.T) {
 #pragma unroll
-                    for (int h2 = 0; h2 < VB_EPI_BATCH; ++h2) {
+                    for (int h2 = 0; h2 < kEpiBatch; ++h2) {
                         if (c + h2 >= D / 32) break;
 #pragma unroll
                         for (int v = 0; v < 2; ++v) {
@@ -621,35 +551,11 @@ prefill_sm100_kernel(const __grid_constant__ TmaMaps maps, PrefillParams p) {
                     }
                 }
             }
-#else
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t o[32];
-                tmem_ld32(o_addr + c * 32, o);
-                tmem_ld_wait();
-                if (row < p.T) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint4 out;
-                        out.x = Elem<T>::pack2(__uint_as_float(o[8 * v + 0]) * inv_l, __uint_as_float(o[8 * v + 1]) * inv_l);
-                        out.y = Elem<T>::pack2(__uint_as_float(o[8 * v + 2]) * inv_l, __uint_as_float(o[8 * v + 3]) * inv_l);
-                        out.z = Elem<T>::pack2(__uint_as_float(o[8 * v + 4]) * inv_l, __uint_as_float(o[8 * v + 5]) * inv_l);
-                        out.w = Elem<T>::pack2(__uint_as_float(o[8 * v + 6]) * inv_l, __uint_as_float(o[8 * v + 7]) * inv_l);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = out;
-                    }
-                }
-            }
-#endif
             // O has been read out: the next item's first PV (issued only after this thread's next
             // p_ready arrival) may overwrite it
             tc_fence_before();
             if (p.lse != nullptr && row < p.T)
                 p.lse[(static_cast<long long>(w.b) * p.Hq + hq_t) * p.T + row] = (m_ref + fast_log2(l_sum)) * kLn2;
-#ifdef VB_TIMING
-            t_epi = clock64() - te0;
-            if ((tid & 127) == 0) { VB_T(14 - 4 * t, t_wait); VB_T(15 - 4 * t, t_comp); if (t == 1) VB_T(9, t_epi); }
-#endif
-            (void)t_wait; (void)t_comp; (void)t_epi;
         }
     }
 
@@ -705,12 +611,13 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
     if (int rc = make_map(&maps.q, p.dtype, p.q, p.T, p.Hq, p.B, D)) return rc;
     if (int rc = make_map(&maps.k, p.dtype, p.k, p.Skv, p.Hkv, p.B, D)) return rc;
     if (int rc = make_map(&maps.v, p.dtype, p.v, p.Skv, p.Hkv, p.B, D)) return rc;
-    static thread_local int configured_dev = -1;
+    static thread_local bool configured[64] = {};      // per device ordinal: the attribute belongs to the device's context
     int dev = 0;
     VB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_dev != dev) {
+    if (dev < 0 || dev >= 64) return set_detail(VB200_ERR_NO_DEVICE, "device ordinal out of range");
+    if (!configured[dev]) {
         VB200_CUDA_TRY(cudaFuncSetAttribute(prefill_sm100_kernel<T, D, kExactRope>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
-        configured_dev = dev;
+        configured[dev] = true;
     }
     const int n_items = item_rows(p) * item_cols(p);
     int sms = 0;
@@ -727,15 +634,28 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
 
 }  // namespace
 
-#ifdef VB_TIMING
-extern "C" int vb200_debug_set_timing_buffer(void* buf) {
-    long long* b = static_cast<long long*>(buf);
-    return cudaMemcpyToSymbol(g_timing_buf, &b, sizeof(b)) == cudaSuccess ? 0 : -5;
+
+// Which of the two tensor-core kernels runs a head_dim-128 call: the two-SM kernel (prefill_pair_sm100.cu) works on
+// four query tiles per item, so it is chosen when the call fills them -- four query heads per KV head, or enough
+// rows for the two / four row tiles the other pairings need; short calls stay on the single-CTA kernel below.
+// VB200_PREFILL_KERNEL=single|pair in the environment overrides the choice (read once; for A/B measurements).
+static bool use_pair_kernel(const PrefillParams& p) {
+    static const int forced = []() {
+        const char* e = getenv("VB200_PREFILL_KERNEL");
+        if (!e) return -1;
+        return (e[0] == 'p' || e[0] == 'P') ? 1 : 0;
+    }();
+    if (p.D != 128) return false;
+    if (forced >= 0) return forced == 1;
+    const int n_rep = p.Hq / p.Hkv;
+    if (n_rep % 4 == 0) return true;
+    if (n_rep % 2 == 0) return p.T > kBlockM;
+    return p.T > 3 * kBlockM;
 }
-#endif
 
 int launch_prefill_sm100(cudaStream_t s, const PrefillParams& p) {
     if (p.D != 128 && p.D != 64) return set_detail(VB200_ERR_UNSUPPORTED, "bf16/fp16 attention supports head_dim 64 and 128");
+    if (use_pair_kernel(p)) return launch_prefill_pair_sm100(s, p);
     // past position 16384 the fp32 angle pos*f of the reference is itself coarse (~6e-8*pos) and only a
     // per-row table read reproduces it
     const bool exact = p.q_rope_table != nullptr && p.start_pos + p.T > 16384;

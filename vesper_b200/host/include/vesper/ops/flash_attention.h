@@ -29,7 +29,7 @@ void flash_attention_cuda_dispatch(const Tensor& q, const Tensor& k, const Tenso
 // (src/ops/flash_attention.cpp:373-378); dropout is not part of the CUDA path (dropout_p must be 0).
 std::tuple<Tensor, Tensor, Tensor> flash_attention_backward(const Tensor& grad_output, const Tensor& q, const Tensor& k,
                                                             const Tensor& v, const Tensor& output, const Tensor& lse,
-                                                            float scale, bool is_causal, float dropout_p = 0.0f,
+                                                            float scale, bool is_causal = true, float dropout_p = 0.0f,
                                                             const Tensor& dropout_mask = Tensor());
 void flash_attention_backward_cuda_dispatch(const Tensor& grad_output, const Tensor& q, const Tensor& k, const Tensor& v,
                                             const Tensor& output, const Tensor& lse, Tensor& grad_q, Tensor& grad_k,
