@@ -508,6 +508,11 @@ def bench_sharded(cx, nsteps=50):
     def step_fused():
         cuda_step(step4, q4, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out4, workspace=ws4, exchange=exchange, qpos=qpos)
 
+    one_launch_ok = exchange is not None and exchange.supports_one_launch(Bq, Hq, Hkv)
+
+    def step_one_launch():
+        cuda_step(step4, q4, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out4, workspace=ws4, exchange=exchange, qpos=qpos, one_launch=True)
+
     def timed(fn, n):
         for _ in range(5):
             fn()
@@ -521,7 +526,27 @@ def bench_sharded(cx, nsteps=50):
         return cx.max_over_ranks(s0.elapsed_time(s1)) / n
 
     ms_gather = timed(step_gather, nsteps)
-    ms_fused = ms_graph = None
+    ms_fused = ms_graph = ms_one = ms_one_graph = None
+    graph_one = None
+    if one_launch_ok:
+        ms_one = timed(step_one_launch, nsteps)
+        try:
+            cx.sync_all()
+            graph_one = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_one):
+                for _ in range(nsteps):
+                    step_one_launch()
+            for _ in range(2):
+                graph_one.replay()
+            cx.sync_all()
+            s0, s1 = cx.event(), cx.event()
+            s0.record()
+            graph_one.replay()
+            s1.record()
+            cx.sync_all()
+            ms_one_graph = cx.max_over_ranks(s0.elapsed_time(s1)) / nsteps
+        except Exception as e:
+            exchange_error = f"graph (one launch): {type(e).__name__}: {e}"[:200]
     if exchange is not None:
         ms_fused = timed(step_fused, nsteps)
         # the same steps replayed from one CUDA graph (the library is capture-safe and the exchange numbers its
@@ -546,7 +571,7 @@ def bench_sharded(cx, nsteps=50):
     # correctness of what was timed (a 1-GPU test box cannot run the N > 1 parity tests): the chosen path's result
     # against the all-gather path's, bit for bit, and against the CPU oracle's attention over the whole 131072-key
     # context for 4 sampled query heads (their KV heads' shards are collected on rank 0 for that)
-    paths_bit_identical, max_abs_err, err_heads = None, None, [0, 21, 42, 63]
+    paths_bit_identical, max_abs_err, err_heads, one_launch_max_diff = None, None, [0, 21, 42, 63], None
     step_gather()
     cx.sync_all()
     out_gather = out4.clone()
@@ -560,6 +585,17 @@ def bench_sharded(cx, nsteps=50):
             graph.replay()
             cx.sync_all()
             same = same and bool(torch.equal(out4, out_gather))
+        if one_launch_ok:
+            # the one-launch step merges its splits in another order: equal up to one rounding of the bf16 output
+            out4.zero_()
+            step_one_launch()
+            cx.sync_all()
+            one_launch_max_diff = float((out4.float() - out_gather.float()).abs().max().item())
+            if ms_one_graph is not None:
+                out4.zero_()
+                graph_one.replay()
+                cx.sync_all()
+                one_launch_max_diff = max(one_launch_max_diff, float((out4.float() - out_gather.float()).abs().max().item()))
         flag = torch.tensor([1 if same else 0], dtype=torch.int32, device=dev)
         cx.dist.all_reduce(flag, op=cx.dist.ReduceOp.MIN)
         paths_bit_identical = bool(flag.item())
@@ -585,7 +621,9 @@ def bench_sharded(cx, nsteps=50):
     except Exception as e:
         exchange_error = (exchange_error or "") + f" oracle check: {type(e).__name__}: {e}"[:200]
     candidates = [("all-gather + combine", ms_gather)] + ([("fused peer-memory exchange", ms_fused)] if ms_fused else []) + \
-                 ([("fused peer-memory exchange, CUDA-graph replay", ms_graph)] if ms_graph else [])
+                 ([("fused peer-memory exchange, CUDA-graph replay", ms_graph)] if ms_graph else []) + \
+                 ([("decode + split merge + exchange in one launch", ms_one)] if ms_one else []) + \
+                 ([("decode + split merge + exchange in one launch, CUDA-graph replay", ms_one_graph)] if ms_one_graph else [])
     path, ms = min(candidates, key=lambda c: c[1])
     nbytes = 2.0 * Hkv * L4 * D * 2
     capi.check_kernel_status(cx.local)
@@ -594,6 +632,7 @@ def bench_sharded(cx, nsteps=50):
         "metric": "long-context decode KV-read GB/s (aggregate)", "value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
         "ms_per_step": ms, "scaling": "strong", "path": path,
         "ms_per_step_all_gather_path": ms_gather, "ms_per_step_fused_exchange": ms_fused, "ms_per_step_fused_exchange_graph": ms_graph,
+        "ms_per_step_one_launch": ms_one, "ms_per_step_one_launch_graph": ms_one_graph, "one_launch_max_diff_vs_all_gather_path": one_launch_max_diff,
         "exchange_error": exchange_error,
         "paths_bit_identical": paths_bit_identical, "max_abs_err": max_abs_err,
         "max_abs_err_what": f"query heads {err_heads} over the whole context against the CPU oracle (gate 1e-2, bf16)",

@@ -240,6 +240,19 @@ typedef struct vb200_exchange_args {
 size_t vb200_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t D);
 int vb200_exchange_combine(const vb200_exchange_args* a);
 
+/* The whole sequence-sharded decode step of one rank in ONE launch (no reference counterpart): vb200_decode_fwd
+ * over this rank's shard of the KV sequence, with the merge of its splits and the exchange above run as the tail of
+ * the split kernel -- the CTA that delivers the last split of a (batch, kv_head) merges that group's splits in
+ * registers / shared memory, stores the merged records into every rank's exchange buffer, waits (bounded) for the
+ * peers' flags and writes the final rows.  No combine kernel, no exchange kernel, no partial records in HBM: two
+ * launch gaps and two round trips less than vb200_decode_fwd(partial_out) + vb200_exchange_combine, which is what a
+ * step of a few microseconds per GPU is made of.
+ * `a`: as for vb200_decode_fwd (o, lse, partial_out are ignored; the workspace is needed); `x`: as for
+ * vb200_exchange_combine with rows = B * Hq, D and dtype of the decode call (`partial` is ignored; out / lse receive
+ * the result).  Needs Hq / Hkv of 4 or 8 and B * Hkv <= 64, without advance_lens; otherwise VB200_ERR_UNSUPPORTED and
+ * the two-call form applies.  Every rank must make the same sequence of exchanging calls on its buffer. */
+int vb200_decode_exchange_fwd(const vb200_decode_args* a, const vb200_exchange_args* x);
+
 /* ---- attention backward (training; fp32, the reference's training dtype) --------------------
  * dQ, dK, dV of O = softmax(scale Q K^T [causal]) V from the saved O and LSE of the forward, P
  * recomputed tile by tile.  All tensors contiguous [B,H,N,D] fp32 with Hq == Hkv (the reference op

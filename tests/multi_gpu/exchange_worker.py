@@ -42,10 +42,18 @@ def main():
         lse_nccl = torch.empty_like(lse_fused)
         cuda_step(step, q, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out_fused, lse=lse_fused, workspace=ws, exchange=ex)
         cuda_step(step, q, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out_nccl, lse=lse_nccl, workspace=ws, dist=dist)
+        # decode + split merge + exchange in ONE launch
+        out_one_launch = torch.empty_like(out_fused)
+        lse_one_launch = torch.empty_like(lse_fused)
+        cuda_step(step, q, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out_one_launch, lse=lse_one_launch, workspace=ws,
+                  exchange=ex, one_launch=True)
         torch.cuda.synchronize()
         capi.check_kernel_status(local)
         assert torch.equal(out_fused, out_nccl), f"rank {rank} step {it}: fused exchange differs from all-gather + combine"
         assert torch.allclose(lse_fused, lse_nccl, atol=1e-6, rtol=0)
+        # (its split merge sums in another order: equal up to one rounding of the 16-bit output)
+        assert (out_one_launch.float() - out_fused.float()).abs().max().item() <= 2e-3, f"rank {rank} step {it}: one-launch step differs"
+        assert torch.allclose(lse_one_launch, lse_fused, atol=1e-5, rtol=0)
         if rank == 0:
             # single-GPU attention over the whole context through the same library (q rotated at position L)
             one = ShardedDecodeStep(1, 0, L)

@@ -289,3 +289,62 @@ def test_decode_full_sequence_is_reported_not_overrun(lib, cuda, oracle):
             kc1, vc1 = k[b:b + 1].copy(), v[b:b + 1].copy()
             want_o, _, _ = oracle.gqa_attention_cached(q[b:b + 1], kn[b:b + 1], vn[b:b + 1], kc1, vc1, lens[b], lens[b])
             assert maxabs(from_torch(o)[b], want_o[0]) <= 1e-2
+
+
+@pytest.mark.parametrize("case", [
+    # dtype, B, Hq, Hkv, D, lens, cache row stride (elements; 0 = D)
+    ("fp32", 2, 4, 4, 64, [37, 300], 0),          # the reference's own cache format and a small head (tests/test_kv_cache_chapter33.cpp:66-188)
+    ("fp32", 2, 6, 2, 64, [1, 129], 0),           # three query heads per KV head
+    ("fp32", 1, 8, 2, 128, [700], 0),
+    ("bf16", 2, 8, 2, 64, [63, 512], 0),
+    ("fp16", 1, 4, 4, 32, [100], 0),
+    ("bf16", 2, 8, 2, 128, [200, 90], 160),       # head_dim 128 but strided cache rows: not the tuned kernels' layout
+    ("bf16", 1, 12, 2, 128, [333], 0),            # six query heads per KV head
+])
+def test_decode_generic_shapes_rope_append_two_steps(lib, cuda, oracle, case):
+    """Split-KV decode for the shapes outside the two tuned kernels (fp32 caches, head_dim != 128, other group sizes,
+    strided cache rows): ragged lengths, RoPE at position len, append, attend, two steps with the length array advanced
+    on the device.  fp32 within 1e-4 of the oracle, 16-bit within the usual gates."""
+    import torch
+    from vesper_b200 import capi
+    dt, B, Hq, Hkv, D, lens, row_stride = case
+    rnd = {"fp32": (lambda x: np.asarray(x, np.float32)), "bf16": bf16_round, "fp16": fp16_round}[dt]
+    tdt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[dt]
+    tol, lse_tol = {"fp32": (1e-4, 1e-4), "bf16": (1e-2, 1e-3), "fp16": (2e-3, 1e-3)}[dt]
+    cap = max(lens) + 8
+    rng = np.random.default_rng(80 + D + Hq)
+    k, v = make_cache(rng, B, Hkv, cap, D, lens, rnd)
+    if row_stride:
+        bk = torch.zeros(B, Hkv, cap, row_stride, dtype=tdt, device=cuda)
+        bv = torch.zeros_like(bk)
+        tk, tv = bk[..., :D], bv[..., :D]
+        tk.copy_(to_torch(k, tdt, cuda)); tv.copy_(to_torch(v, tdt, cuda))
+    else:
+        tk, tv = to_torch(k, tdt, cuda), to_torch(v, tdt, cuda)
+    seq = torch.tensor(lens, dtype=torch.int32, device=cuda)
+    scale = float(1.0 / np.sqrt(D))
+    cur = list(lens)
+    for step in range(2):
+        q = rnd(rng.standard_normal((B, Hq, 1, D), dtype=np.float32))
+        kn = rnd(rng.standard_normal((B, Hkv, 1, D), dtype=np.float32))
+        vn = rnd(rng.standard_normal((B, Hkv, 1, D), dtype=np.float32))
+        tq, tkn, tvn = (to_torch(x, tdt, cuda) for x in (q, kn, vn))
+        o = torch.empty_like(tq)
+        lse = torch.empty(B, Hq, dtype=torch.float32, device=cuda)
+        capi.decode(tq, o, tk, tv, scale=scale, k_new=tkn, v_new=tvn, lse=lse, theta=10000.0, seq_lens=seq,
+                    advance_lens=True, max_len=max(cur) + 1, num_splits=(0 if step == 0 else 3))
+        torch.cuda.synchronize()
+        capi.check_kernel_status(0)
+        for b in range(B):
+            kc1, vc1 = k[b:b + 1].copy(), v[b:b + 1].copy()
+            want_o, want_lse, n = oracle.gqa_attention_cached(q[b:b + 1], kn[b:b + 1], vn[b:b + 1], kc1, vc1, cur[b], cur[b])
+            assert n == cur[b] + 1
+            assert maxabs(from_torch(o)[b], want_o[0]) <= tol, f"step {step} seq {b}"
+            assert maxabs(from_torch(lse)[b], want_lse[0, :, 0]) <= lse_tol, f"step {step} seq {b}"
+            cur[b] += 1
+        assert seq.tolist() == cur
+        k, v = from_torch(tk), from_torch(tv)          # carry the device cache (rounded rotated K) forward
+    for b in range(B):
+        assert not k[b, :, cur[b]:].any() and not v[b, :, cur[b]:].any()
+    if row_stride:
+        assert not bool(bk[..., D:].any()) and not bool(bv[..., D:].any())

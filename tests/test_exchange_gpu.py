@@ -130,3 +130,77 @@ def test_absent_peer_times_out_with_a_status_not_a_hang(cuda, oracle):
     capi.check_kernel_status(0)
     o, _ = _want(oracle, p)
     assert np.abs(from_torch(out) - o).max() <= 2.0 ** -8 * max(1.0, np.abs(o).max())
+
+
+@pytest.mark.parametrize("n_rep", [8, 4])
+def test_decode_and_exchange_in_one_launch_with_an_emulated_peer(cuda, oracle, n_rep):
+    """vb200_decode_exchange_fwd: rank 0 of a 2-way sequence-sharded decode runs its shard, merges its splits and
+    exchanges in ONE launch; rank 1 is emulated by seeding what it would have pushed (its record comes from a
+    vb200_decode_fwd(partial_out) over the second shard).  Result against the oracle's attention over the whole
+    context, query rotated at the absolute position; push side: the stand-in peer buffer received this rank's record
+    (compared with the two-call form's record)."""
+    import torch
+    from helpers import bf16_round, maxabs, to_torch
+    from vesper_b200 import capi
+    B, Hkv, D, L = 1, 2, 128, 4096
+    Hq = Hkv * n_rep
+    rows = B * Hq
+    rng = np.random.default_rng(70 + n_rep)
+    k = bf16_round(rng.standard_normal((B, Hkv, L, D), dtype=np.float32))
+    v = bf16_round(rng.standard_normal((B, Hkv, L, D), dtype=np.float32))
+    scale = float(1.0 / np.sqrt(D))
+    half = L // 2
+    k0, v0 = to_torch(k[:, :, :half], torch.bfloat16, cuda), to_torch(v[:, :, :half], torch.bfloat16, cuda)
+    k1, v1 = to_torch(k[:, :, half:], torch.bfloat16, cuda), to_torch(v[:, :, half:], torch.bfloat16, cuda)
+    qpos = torch.tensor([L], dtype=torch.int32, device=cuda)
+    nbytes = capi.exchange_buffer_bytes(2, rows, D)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=cuda) for _ in range(2)]
+    out = torch.empty(rows, D, dtype=torch.bfloat16, device=cuda)
+    lse = torch.empty(rows, dtype=torch.float32, device=cuda)
+    for step in (1, 2, 3):                                   # the call number advances in the buffer; slots alternate
+        q = bf16_round(rng.standard_normal((B, Hq, 1, D), dtype=np.float32))
+        tq = to_torch(q, torch.bfloat16, cuda)
+        rec1 = torch.empty(rows, D + 2, dtype=torch.float32, device=cuda)
+        capi.decode(tq, None, k1, v1, scale=scale, theta=10000.0, uniform_len=half, max_len=half, pos_offset=half,
+                    q_positions=qpos, partial_out=rec1)
+        rec0 = torch.empty_like(rec1)
+        capi.decode(tq, None, k0, v0, scale=scale, theta=10000.0, uniform_len=half, max_len=half, pos_offset=0,
+                    q_positions=qpos, partial_out=rec0)
+        torch.cuda.synchronize()
+        _seed_peer(bufs[0], 2, rows, D, 1, step, rec1.cpu().numpy())
+        capi.decode_exchange(tq, k0, v0, [b.data_ptr() for b in bufs], 0, out, lse, scale=scale, theta=10000.0,
+                             uniform_len=half, max_len=half, pos_offset=0, q_positions=qpos)
+        torch.cuda.synchronize()
+        capi.check_kernel_status(0)
+        q_rot = oracle.apply_rope(q, L, 10000.0)
+        want_o, want_lse = oracle.decode_ragged(q_rot[:, :, 0], k, v, [L])
+        assert maxabs(from_torch(out), want_o[0]) <= 1e-2, step
+        assert maxabs(from_torch(lse), want_lse[0]) <= 1e-3, step
+        # push side: our merged record in the stand-in peer's slot[parity][0]; same numbers as the two-call form up to
+        # the summation order of the split merge
+        n = rows * (D + 2)
+        off = SLOT_BASE + ((step & 1) * 2 + 0) * n * 4
+        got = bufs[1][off:off + n * 4].view(torch.float32).cpu().numpy().reshape(rows, D + 2)
+        ref = rec0.cpu().numpy()
+        # (for 4-head groups the two-call form at this length runs the CUDA-core split kernel, the one-launch form the
+        # warp-MMA one, whose P is rounded to 16 bits: a few 1e-4 apart on records of size ~0.1)
+        # (m is a reference maximum, raised lazily, not necessarily the true one: only m + ln l is determined)
+        assert np.abs(got[:, :D] - ref[:, :D]).max() <= 1e-3
+        assert np.abs((got[:, D] + np.log(got[:, D + 1])) - (ref[:, D] + np.log(ref[:, D + 1]))).max() <= 1e-3
+        f0 = FLAG_BASE + (((step & 1) * MAX_WORLD + 0) * MAX_CTAS) * 4
+        assert bool((bufs[1][f0:f0 + B * Hkv * 4].view(torch.int32) == step).all())
+
+
+def test_decode_exchange_refuses_shapes_it_does_not_take(cuda):
+    import torch
+    from vesper_b200 import capi
+    B, Hq, Hkv, D, L = 1, 4, 2, 128, 256                     # two query heads per KV head: the two-call form applies
+    q = torch.zeros(B, Hq, 1, D, dtype=torch.bfloat16, device=cuda)
+    kc = torch.zeros(B, Hkv, L, D, dtype=torch.bfloat16, device=cuda)
+    buf = torch.zeros(capi.exchange_buffer_bytes(1, B * Hq, D), dtype=torch.uint8, device=cuda)
+    out = torch.empty(B * Hq, D, dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(capi.Vb200Error) as e:
+        capi.decode_exchange(q, kc, kc, [buf.data_ptr()], 0, out, scale=1.0, uniform_len=L, max_len=L)
+    assert e.value.status == -2
+    torch.cuda.synchronize()
+    capi.check_kernel_status(0)

@@ -32,21 +32,52 @@ def test_gqa_module_fp32_matches_the_reference_module(lib, cuda):
     assert maxabs(m.forward(g["x"]), g["y"]) <= 1e-4            # forward(x) is causal
 
 
-def test_gqa_module_bf16_and_cached_equals_uncached(lib, cuda):
-    from vesper_b200.model import KVCache
-    m, g, (Cdim, Hq, Hkv, T) = gqa_from_fixture("bf16")
-    x = bf16_round(g["x"])
+def oracle_attention_module(oracle, x, w_in, b_in, w_out, b_out, Hq, Hkv, kc, vc, start, cur):
+    """The module composed from the oracle's operators on bf16-rounded activations: input projection (+ bias) ->
+    [B,H,T,D] -> RoPE + cache + grouped attention (src/nn/gqa_attention.cpp:111-159) -> merge heads -> output projection."""
+    B, T, C_ = x.shape
+    D = C_ // Hq
+    qkv = oracle.linear(x.reshape(-1, C_), w_in)
+    if b_in is not None:
+        qkv = qkv + b_in
+    qkv = bf16_round(qkv).reshape(B, T, Hq + 2 * Hkv, D)
+    q = np.ascontiguousarray(qkv[:, :, :Hq].transpose(0, 2, 1, 3))
+    k = np.ascontiguousarray(qkv[:, :, Hq:Hq + Hkv].transpose(0, 2, 1, 3))
+    v = np.ascontiguousarray(qkv[:, :, Hq + Hkv:].transpose(0, 2, 1, 3))
+    o, _, cur = oracle.gqa_attention_cached(q, k, v, kc, vc, start, cur)
+    merged = bf16_round(o.transpose(0, 2, 1, 3).reshape(-1, C_))
+    y = oracle.linear(merged, w_out)
+    if b_out is not None:
+        y = y + b_out
+    return y.reshape(B, T, C_), cur
+
+
+def test_gqa_module_bf16_and_cached_equals_uncached(lib, cuda, oracle):
+    """The serving format through the GQA class at head_dim 128 with two query heads per KV head: uncached causal
+    forward against the oracle composition, then the same sequence as a prompt pass and two single-token steps through
+    forward(x, cache, start_pos) -- which must agree with the uncached result (the reference's own cached GQA path does
+    not when the cache is not full)."""
+    from vesper_b200.model import AttentionModule, KVCache
+    Cdim, Hq, Hkv, T, B = 512, 4, 2, 70, 2
+    D = Cdim // Hq
+    rng = np.random.default_rng(33)
+    wqkv = bf16_round((0.05 * rng.standard_normal(((Hq + 2 * Hkv) * D, Cdim))).astype(np.float32))
+    wo = bf16_round((0.05 * rng.standard_normal((Cdim, Cdim))).astype(np.float32))
+    x = bf16_round(rng.standard_normal((B, T, Cdim)).astype(np.float32))
+    m = AttentionModule("gqa", Cdim, Hq, Hkv, max_seq_len=128, rope_base=10000.0, dtype="bf16")
+    m.load(wqkv, wo)
     y = m.forward(x, True)
-    assert maxabs(y, g["y"]) <= 2e-2
-    # prompt pass of T - 2 tokens, then two single-token steps through forward(x, cache, start_pos)
-    cache = KVCache(x.shape[0], Hkv, 64, Cdim // Hq, "bf16")
+    kc, vc = np.zeros((B, Hkv, 128, D), np.float32), np.zeros((B, Hkv, 128, D), np.float32)
+    want, _ = oracle_attention_module(oracle, x, wqkv, None, wo, None, Hq, Hkv, kc, vc, 0, 0)
+    assert maxabs(y, want) <= 2e-2
+    cache = KVCache(B, Hkv, 128, D, "bf16")
     y0 = m.forward_cached(cache, x[:, :T - 2], 0)
     y1 = m.forward_cached(cache, x[:, T - 2:T - 1], T - 2)
     y2 = m.forward_cached(cache, x[:, T - 1:T], T - 1)
     assert len(cache) == T
     got = np.concatenate([y0, y1, y2], axis=1)
-    assert maxabs(got, y) <= 1e-2                                # same kernels, bf16 cache: rotated K is rounded once more
-    assert maxabs(got, g["y"]) <= 2e-2
+    assert maxabs(got, y) <= 1e-2                                # same kernels; the bf16 cache rounds the rotated K once more
+    assert maxabs(got, want) <= 2e-2
 
 
 def test_gqa_module_fp32_cached_equals_uncached(lib, cuda):
@@ -105,11 +136,7 @@ def test_mha_module_bf16_head_dim_128(lib, cuda, oracle):
     y1 = m.forward_cached(cache, x[:, T:], T)
 
     def want(xs, start, kc, vc, cur):
-        qkv = bf16_round(oracle.linear(xs.reshape(-1, Cm), w_attn) + b_attn).reshape(B, xs.shape[1], 3, Hm, D)
-        q, k, v = (np.ascontiguousarray(qkv[:, :, i].transpose(0, 2, 1, 3)) for i in range(3))
-        o, _, cur = oracle.gqa_attention_cached(q, k, v, kc, vc, start, cur)
-        merged = bf16_round(o.transpose(0, 2, 1, 3).reshape(-1, Cm))
-        return (oracle.linear(merged, w_proj) + b_proj).reshape(B, xs.shape[1], Cm), cur
+        return oracle_attention_module(oracle, xs, w_attn, b_attn, w_proj, b_proj, Hm, Hm, kc, vc, start, cur)
 
     kc, vc = np.zeros((B, Hm, 64, D), np.float32), np.zeros((B, Hm, 64, D), np.float32)
     w0, cur = want(x[:, :T], 0, kc, vc, 0)

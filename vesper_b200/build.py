@@ -22,7 +22,7 @@ LIBDIR = os.path.join(PKG, "lib")
 OBJDIR = os.path.join(PKG, "build")
 LIB = os.path.join(LIBDIR, "libvesper_b200.so")
 
-SOURCES = ["api.cu", "rope_append.cu", "prefill_f32.cu", "prefill_sm100.cu", "prefill_pair_sm100.cu", "decode_splitkv.cu", "decode_static.cu",
+SOURCES = ["api.cu", "rope_append.cu", "prefill_f32.cu", "prefill_sm100.cu", "prefill_pair_sm100.cu", "decode_splitkv.cu", "decode_generic.cu", "decode_static.cu",
            "linear_sm100.cu", "block_ops.cu", "decode_exchange.cu", "decode_gqa_mma.cu", "flash_bwd_f32.cu"]
 HEADERS = ["common.cuh", "kernels.h", os.path.join("..", "..", "include", "vesper_b200.h"),
            os.path.join("..", "..", "include", "vesper_b200_block.h")]

@@ -51,7 +51,7 @@ class DecodeArgs(C.Structure):
 
 EXPORTS = [
     "vb200_prefill_workspace_bytes", "vb200_prefill_fwd", "vb200_decode_workspace_bytes", "vb200_decode_workspace_bytes_max", "vb200_decode_fwd",
-    "vb200_decode_fwd_static", "vb200_exchange_buffer_bytes", "vb200_exchange_combine",
+    "vb200_decode_fwd_static", "vb200_exchange_buffer_bytes", "vb200_exchange_combine", "vb200_decode_exchange_fwd",
     "vb200_attention_bwd_workspace_bytes", "vb200_attention_bwd",
     "vb200_lse_combine", "vb200_kv_append", "vb200_apply_rope", "vb200_repeat_kv", "vb200_rope_inv_freq",
     "vb200_strerror", "vb200_last_error_detail", "vb200_abi_version", "vb200_launch_count",
@@ -148,6 +148,7 @@ def load():
     L.vb200_exchange_buffer_bytes.argtypes = [C.c_int32, C.c_int64, C.c_int32]
     L.vb200_exchange_buffer_bytes.restype = C.c_size_t
     L.vb200_exchange_combine.argtypes = [C.POINTER(ExchangeArgs)]
+    L.vb200_decode_exchange_fwd.argtypes = [C.POINTER(DecodeArgs), C.POINTER(ExchangeArgs)]
     # decoder-block operators (include/vesper_b200_block.h)
     L.vb200_linear.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64] + [C.c_int32] * 5
     L.vb200_linear_bias.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64] + [C.c_int32] * 5
@@ -338,27 +339,51 @@ def exchange_buffer_bytes(world, rows, D):
     return int(load().vb200_exchange_buffer_bytes(world, rows, D))
 
 
-def exchange_combine(partial, peer_ptrs, rank, out, lse=None, *, step=0, timeout_cycles=0, stream=None):
-    """partial [rows, D+2] fp32 (local), peer_ptrs: device address of every rank's exchange buffer."""
+def exchange_args(peer_ptrs, rank, out, lse=None, *, partial=None, rows=None, D=None, step=0, timeout_cycles=0, stream=None):
     a = ExchangeArgs()
     a.struct_size = C.sizeof(ExchangeArgs)
-    a.device = partial.device.index or 0
+    a.device = out.device.index or 0
     a.stream = _stream_ptr(stream)
     a.world, a.rank = len(peer_ptrs), rank
     arr = (C.c_void_p * len(peer_ptrs))(*[C.c_void_p(int(p)) for p in peer_ptrs])
     a.peer_buffers = arr
+    a._keep = arr
     a.partial = _ptr(partial)
-    a.rows, a.D = partial.shape[0], partial.shape[1] - 2
+    a.rows = rows if rows is not None else partial.shape[0]
+    a.D = D if D is not None else partial.shape[1] - 2
     a.dtype = dtype_code(out)
     a.out = _ptr(out)
     a.lse = _ptr(lse)
     a.step = step
     a.timeout_cycles = timeout_cycles
+    return a
+
+
+def exchange_combine(partial, peer_ptrs, rank, out, lse=None, *, step=0, timeout_cycles=0, stream=None):
+    """partial [rows, D+2] fp32 (local), peer_ptrs: device address of every rank's exchange buffer."""
+    a = exchange_args(peer_ptrs, rank, out, lse, partial=partial, step=step, timeout_cycles=timeout_cycles, stream=stream)
     check(load().vb200_exchange_combine(C.byref(a)))
     return out
 
 
-# ---- decoder-block operators ---------------------------------------------------------------
+def decode_exchange(q, k_cache, v_cache, peer_ptrs, rank, out, lse=None, *, timeout_cycles=0, step=0, workspace=None, **kw):
+    """vb200_decode_exchange_fwd: this rank's shard of a sequence-sharded decode step, split merge and exchange in one
+    launch.  out [B*Hq, D] (bf16/fp16), lse [B*Hq]; kw as for decode_args (scale, theta, uniform_len, max_len, pos_offset,
+    q_positions, ...)."""
+    import torch
+    L = load()
+    B, Hq, _, D = q.shape
+    stream = kw.get("stream")
+    a = decode_args(q, None, k_cache, v_cache, workspace=workspace, **kw)
+    need = L.vb200_decode_workspace_bytes(C.byref(a))
+    if need > a.workspace_bytes:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+        a.workspace, a.workspace_bytes = _ptr(workspace), need
+    x = exchange_args(peer_ptrs, rank, out, lse, rows=B * Hq, D=D, step=step, timeout_cycles=timeout_cycles, stream=stream)
+    check(L.vb200_decode_exchange_fwd(C.byref(a), C.byref(x)))
+    return workspace
+
+
 def linear(x, w, out, epilogue=EPI_BF16, splits=0, stream=None, bias=None):
     """out = epilogue(x @ w.T [+ bias]): x [M,K] bf16, w [N,K] bf16 (row strides honoured), bias fp32 [N]."""
     M, K = x.shape

@@ -194,7 +194,7 @@ int validate_decode(const vb200_decode_args* a) {
     if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->D <= 0) return set_detail(VB200_ERR_INVALID_ARG, "B, Hq, Hkv, D must be positive");
     if (a->Hq % a->Hkv != 0) return set_detail(VB200_ERR_INVALID_ARG, "Hq must be divisible by Hkv");
     if (!a->q.ptr || !a->k_cache.ptr || !a->v_cache.ptr) return set_detail(VB200_ERR_INVALID_ARG, "q, k_cache, v_cache must be non-null");
-    if (!a->o.ptr && !a->partial_out) return set_detail(VB200_ERR_INVALID_ARG, "o or partial_out must be given");
+    // (vb200_decode_exchange_fwd writes through its exchange arguments and passes neither)
     if ((a->k_new.ptr == nullptr) != (a->v_new.ptr == nullptr)) return set_detail(VB200_ERR_INVALID_ARG, "k_new and v_new must both be given or both be null");
     if (a->cache_cap <= 0) return set_detail(VB200_ERR_INVALID_ARG, "cache_cap must be positive");
     if (!a->seq_lens && (a->uniform_len < 0 || a->uniform_len + (a->k_new.ptr ? 1 : 0) > a->cache_cap))
@@ -309,10 +309,12 @@ int vb200_prefill_fwd(const vb200_prefill_args* a) {
 
     float2* table = nullptr;
     unsigned char* ws = static_cast<unsigned char*>(a->workspace);
-    if (pl.need_table) {
-        table = reinterpret_cast<float2*>(ws);
-        InvFreq f;
-        fill_inv_freq(f, a->rope, a->D);
+    InvFreq f;
+    fill_inv_freq(f, a->rope, a->D);
+    if (pl.need_table) table = reinterpret_cast<float2*>(ws);
+    const bool ro = a->k_cache.ptr && a->cache_read_only;
+    // the table alone is needed when nothing is appended or rotated beside Q (read-only cache)
+    if (pl.need_table && ro) {
         if (int rc = launch_rope_table(s, table, a->T, a->D, a->start_pos, f)) return rc;
     }
 
@@ -327,24 +329,27 @@ int vb200_prefill_fwd(const vb200_prefill_args* a) {
     p.o = to_view(a->o);
     p.lse = a->lse;
     p.q_rope_table = table;
-    fill_inv_freq(p.inv_freq, a->rope, a->D);
+    p.inv_freq = f;
     p.status = kernel_status_word();
     if (!p.status) return set_detail(VB200_ERR_CUDA, "cannot resolve the device status word");
 
-    if (a->k_cache.ptr && a->cache_read_only) {
+    if (ro) {
         // the cache already holds every key and value this call attends to
         p.k = to_view(a->k_cache);
         p.v = to_view(a->v_cache);
     } else if (a->k_cache.ptr) {
-        // fused RoPE(K) + append; attention then reads K/V straight from the cache
-        if (int rc = launch_kv_append(s, a->dtype, a->B, a->Hkv, a->T, a->D, to_view(a->k), to_view(a->v),
-                                      to_view(a->k_cache), to_view(a->v_cache), a->start_pos, table)) return rc;
+        // RoPE table + RoPE(K) + append in one launch; attention then reads K/V straight from the cache
+        if (pl.need_table) {
+            if (int rc = launch_rope_append_fused(s, a->dtype, a->B, a->Hkv, a->T, a->D, to_view(a->k), to_view(a->v),
+                                                  to_view(a->k_cache), to_view(a->v_cache), a->start_pos, table, f)) return rc;
+        } else if (int rc = launch_kv_append(s, a->dtype, a->B, a->Hkv, a->T, a->D, to_view(a->k), to_view(a->v),
+                                             to_view(a->k_cache), to_view(a->v_cache), a->start_pos, nullptr)) return rc;
         p.k = to_view(a->k_cache);
         p.v = to_view(a->v_cache);
     } else if (pl.need_krot) {
         View4 krot{ws + pl.table_bytes, static_cast<long long>(a->Hkv) * a->T * a->D, static_cast<long long>(a->T) * a->D, a->D};
-        if (int rc = launch_kv_append(s, a->dtype, a->B, a->Hkv, a->T, a->D, to_view(a->k), View4{nullptr, 0, 0, 0},
-                                      krot, View4{nullptr, 0, 0, 0}, 0, table)) return rc;
+        if (int rc = launch_rope_append_fused(s, a->dtype, a->B, a->Hkv, a->T, a->D, to_view(a->k), View4{nullptr, 0, 0, 0},
+                                              krot, View4{nullptr, 0, 0, 0}, 0, table, f)) return rc;
         p.k = krot;
         p.v = to_view(a->v);
     } else {
@@ -379,10 +384,32 @@ size_t vb200_decode_workspace_bytes_max(const vb200_decode_args* a) {
     return best;
 }
 
-int vb200_decode_fwd(const vb200_decode_args* a) {
+namespace {
+// Fills the exchange parameters from the C struct (validation shared by both entry points that exchange).
+int fill_exchange(ExchangeParams& p, const vb200_exchange_args* a, const char* who) {
+    if (!a || a->struct_size != sizeof(vb200_exchange_args)) return set_detail(VB200_ERR_INVALID_ARG, "vb200_exchange_args: null or struct_size mismatch");
+    if (a->world <= 0 || a->world > VB200_EXCHANGE_MAX_WORLD || a->rank < 0 || a->rank >= a->world)
+        return set_detail(VB200_ERR_INVALID_ARG, "exchange: world must be in [1, 16] and rank in [0, world)");
+    if (!a->peer_buffers || !a->out || a->rows <= 0 || a->D <= 0 || a->D % 2 != 0)
+        return set_detail(VB200_ERR_INVALID_ARG, "exchange: null pointer, rows <= 0 or odd D");
+    if (a->dtype != VB200_BF16 && a->dtype != VB200_F16) return set_detail(VB200_ERR_UNSUPPORTED, "exchange: out must be bf16 or fp16");
+    p = ExchangeParams{};
+    p.world = a->world; p.rank = a->rank;
+    for (int r = 0; r < a->world; ++r) {
+        if (!a->peer_buffers[r] || reinterpret_cast<uintptr_t>(a->peer_buffers[r]) % 128 != 0)
+            return set_detail(VB200_ERR_ALIGNMENT, "exchange: every exchange buffer must be non-null and 128-byte aligned");
+        p.peers[r] = a->peer_buffers[r];
+    }
+    p.partial = a->partial; p.rows = a->rows; p.D = a->D; p.dtype = a->dtype; p.out = a->out; p.lse = a->lse;
+    p.step = a->step; p.timeout_cycles = a->timeout_cycles > 0 ? a->timeout_cycles : kWaitCycles;
+    (void)who;
+    return VB200_OK;
+}
+
+int decode_impl(const vb200_decode_args* a, const vb200_exchange_args* x) {
     if (int rc = validate_decode(a)) return rc;
-    if (a->D != 128 || a->dtype == VB200_F32) return set_detail(VB200_ERR_UNSUPPORTED, "decode supports bf16/fp16 with head_dim 128");
-    if (a->k_cache.stride_s != a->D || a->v_cache.stride_s != a->D) return set_detail(VB200_ERR_UNSUPPORTED, "cache rows must be contiguous (stride_s == D)");
+    if (!x && !a->o.ptr && !a->partial_out) return set_detail(VB200_ERR_INVALID_ARG, "o or partial_out must be given");
+    if (a->D % 8 != 0 || a->D > 128) return set_detail(VB200_ERR_UNSUPPORTED, "head_dim must be a multiple of 8 and <= 128");
     DecodePlan pl = plan_decode(a);
     if (!a->workspace || a->workspace_bytes < pl.total) return set_detail(VB200_ERR_WORKSPACE, "decode workspace too small (see vb200_decode_workspace_bytes)");
     if (reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0) return set_detail(VB200_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
@@ -416,7 +443,27 @@ int vb200_decode_fwd(const vb200_decode_args* a) {
     p.ws_header = pl.ws_header;
     p.status = kernel_status_word();
     if (!p.status) return set_detail(VB200_ERR_CUDA, "cannot resolve the device status word");
+    if (x) {
+        if (int rc = fill_exchange(p.xchg, x, "vb200_decode_exchange_fwd")) return rc;
+        if (x->rows != static_cast<int64_t>(a->B) * a->Hq || x->D != a->D || x->dtype != a->dtype)
+            return set_detail(VB200_ERR_INVALID_ARG, "vb200_decode_exchange_fwd: the exchange must carry B * Hq rows of head_dim D in the decode dtype");
+        if (static_cast<int64_t>(a->B) * a->Hkv > 64)
+            return set_detail(VB200_ERR_UNSUPPORTED, "vb200_decode_exchange_fwd: at most 64 (batch, kv_head) groups; use vb200_decode_fwd + vb200_exchange_combine");
+        if (p.seq_lens && p.advance_lens && p.append)
+            return set_detail(VB200_ERR_UNSUPPORTED, "vb200_decode_exchange_fwd: advance_lens needs the two-call form");
+        p.xchg.status = p.status;
+        p.fused_exchange = 1;
+        p.partial_out = nullptr;
+    }
     return launch_decode(static_cast<cudaStream_t>(a->stream), p);
+}
+}  // namespace
+
+int vb200_decode_fwd(const vb200_decode_args* a) { return decode_impl(a, nullptr); }
+
+int vb200_decode_exchange_fwd(const vb200_decode_args* a, const vb200_exchange_args* x) {
+    if (!x) return set_detail(VB200_ERR_INVALID_ARG, "vb200_decode_exchange_fwd: null exchange arguments");
+    return decode_impl(a, x);
 }
 
 int vb200_lse_combine(int device, void* stream, const float* partials, int32_t R,

@@ -13,7 +13,7 @@
 // swizzle (4-D tensor maps over the cache views, no multicast); ldmatrix applies the same XOR to its row
 // addresses, so the eight 16-byte rows of a phase fall into distinct banks.  (Row-by-row 256-byte bulk
 // copies into padded rows were tried first: 2 M copies per step saturate the copy engine, 1.9 TB/s.)
-#include "kernels.h"
+#include "decode_exchange.cuh"
 
 #include <cuda.h>
 #include <cstdio>
@@ -360,6 +360,62 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa_mma_kernel(con
             if (d == 0) { out[D] = M * kLn2M; out[D + 1] = L; }
         }
     }
+    if (!p.fused_exchange) return;
+
+    // ---- sequence-sharded decode in one launch: the CTA that delivers the LAST split of this (batch, kv_head) merges
+    // the group's splits and exchanges the merged records with the other ranks (128 consumer threads; the producer
+    // warp has left) ----
+    float* rec = reinterpret_cast<float*>(smem_raw);          // [NREP][D + 2]: this rank's merged (O/l, m, l) per head
+    __shared__ int s_last;
+    __shared__ uint32_t s_step;
+    __shared__ int s_ok;
+    const int unit = b * p.Hkv + kvh;
+    const int nvalid = min((total + p.chunk - 1) / p.chunk, p.num_splits);
+    __threadfence();                                          // this CTA's rows before its ticket
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    if (tid == 0) {
+        int* ticket = reinterpret_cast<int*>(static_cast<char*>(p.xchg.peers[p.xchg.rank]) + kXTicketBase) + unit;
+        const int t = atomicAdd(ticket, 1);
+        s_last = (t == nvalid - 1) ? 1 : 0;
+        if (s_last) *ticket = 0;                              // every split has delivered: ready for the next call
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    if (!s_last) return;
+    __threadfence();
+    {
+        // warp w merges heads w, w + CW, ...; lane l owns dims 4l .. 4l+3.  Rows come from L2 (written by other CTAs).
+        const float* grp = p.workspace + p.ws_header + (static_cast<long long>(unit) * p.num_splits) * NREP * (D + 2);
+        for (int h = warp; h < NREP; h += CW) {
+            const float* rows = grp + h * (D + 2);
+            const long long sstride = static_cast<long long>(NREP) * (D + 2);
+            float M = -INFINITY;
+            for (int sidx = lane; sidx < nvalid; sidx += 32) M = fmaxf(M, __ldcg(rows + sidx * sstride + D));
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float L = 0.f;
+#pragma unroll 8
+            for (int sidx = 0; sidx < nvalid; ++sidx) {
+                const float* row = rows + sidx * sstride;
+                const float ms = __ldcg(row + D);
+                const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - M) * __ldcg(row + D + 1);
+                // a record is D + 2 = 130 floats long: its rows are 8-byte, not 16-byte, aligned
+                const float2 oa = __ldcg(reinterpret_cast<const float2*>(row) + 2 * lane);
+                const float2 ob = __ldcg(reinterpret_cast<const float2*>(row) + 2 * lane + 1);
+                L += wgt;
+                acc.x += wgt * oa.x; acc.y += wgt * oa.y; acc.z += wgt * ob.x; acc.w += wgt * ob.y;
+            }
+            const float inv = (nvalid > 0 && L > 0.f) ? 1.0f / L : 0.f;
+            float* out = rec + h * (D + 2);
+            *reinterpret_cast<float2*>(out + 4 * lane) = make_float2(acc.x * inv, acc.y * inv);
+            *reinterpret_cast<float2*>(out + 4 * lane + 2) = make_float2(acc.z * inv, acc.w * inv);
+            if (lane == 0) { out[D] = M; out[D + 1] = L; }
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    const long long r0 = static_cast<long long>(b) * p.Hq + static_cast<long long>(kvh) * NREP;
+    exchange_rows<T, CW * 32>(p.xchg, unit, r0, r0 + NREP, rec, tid, &s_step, &s_ok,
+                              [] { asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory"); });
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

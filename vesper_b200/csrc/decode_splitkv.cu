@@ -435,9 +435,9 @@ constexpr int kCombineGroups = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(128 * kCombineGroups) decode_combine_kernel(DecodeParams p) {
-    constexpr int D = 128;
+    const int D = p.D;                                   // <= 128: thread d of a group owns dim d, the others idle
     __shared__ float s_red[kCombineGroups * 32];
-    __shared__ float s_acc[kCombineGroups][D];
+    __shared__ float s_acc[kCombineGroups][128];
     __shared__ float s_l[kCombineGroups];
     const int hq = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, d = tid & 127, grp = tid >> 7;
     const int nrep = p.Hq / p.Hkv, kvh = hq / nrep, h = hq % nrep;
@@ -472,7 +472,7 @@ __global__ void __launch_bounds__(128 * kCombineGroups) decode_combine_kernel(De
         const float* row = base + s * sstride;
         float w = expf(row[D] - M) * row[D + 1];
         L += w;
-        acc += w * row[d];
+        if (d < D) acc += w * row[d];
     }
     s_acc[grp][d] = acc;
     if (d == 0) s_l[grp] = L;
@@ -485,11 +485,11 @@ __global__ void __launch_bounds__(128 * kCombineGroups) decode_combine_kernel(De
     float o = (nsp > 0) ? acc / L : 0.f;
     if (p.partial_out) {
         float* po = p.partial_out + (static_cast<long long>(b) * p.Hq + hq) * (D + 2);
-        po[d] = o;
+        if (d < D) po[d] = o;
         if (d == 0) { po[D] = M; po[D + 1] = L; }
     } else {
         T* og = static_cast<T*>(p.o.ptr) + b * p.o.sb + hq * p.o.sh;
-        og[d] = Elem<T>::from_f(o);
+        if (d < D) og[d] = Elem<T>::from_f(o);
         if (p.lse && d == 0) p.lse[static_cast<long long>(b) * p.Hq + hq] = M + logf(L);
     }
     // a full sequence (token not appended) keeps its length
@@ -517,6 +517,34 @@ __global__ void lse_combine_kernel(const float* __restrict__ partials, int R, lo
     if (lse && d == 0) lse[row] = M + logf(L);
 }
 
+template <typename T>
+int launch_combine(cudaStream_t s, const DecodeParams& p) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(p.Hq, p.B);
+    cfg.blockDim = dim3(128 * kCombineGroups);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_combine_kernel<T>, p));
+    note_launch();
+    VB200_CUDA_TRY(cudaPeekAtLastError());
+    return VB200_OK;
+}
+
+// every shape the tuned kernels do not take (decode_generic.cu), then the common combine
+template <typename T>
+int launch_decode_generic(cudaStream_t s, const DecodeParams& p) {
+    if (p.fused_exchange) return set_detail(VB200_ERR_UNSUPPORTED, "decode + exchange in one launch needs 16-bit caches with head_dim 128");
+    profile_mark_begin(s);
+    if (int rc = launch_decode_generic_split(s, p)) return rc;
+    profile_mark_end(s);
+    return launch_combine<T>(s, p);
+}
+
 constexpr int kMaxClusterSplits = 16;   // cluster sizes above 8 need the non-portable cluster size attribute
 
 template <typename T, int NREP>
@@ -533,7 +561,12 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
     // CUDA-core kernel below that, where its lighter prologue wins (3 us per call at 600-key contexts).
     bool use_mma = false, need_combine = true;
     if constexpr (NREP == 8) use_mma = true;
-    if constexpr (NREP == 4) use_mma = p.chunk >= 256;
+    if constexpr (NREP == 4) use_mma = p.chunk >= 256 || p.fused_exchange;
+    if (p.fused_exchange) {
+        // the exchange runs as the tail of the warp-MMA split kernel: no combine launch
+        if (!use_mma) return set_detail(VB200_ERR_UNSUPPORTED, "decode + exchange in one launch needs 4 or 8 query heads per KV head");
+        need_combine = false;
+    }
     if (use_mma) {
         if constexpr (NREP == 4 || NREP == 8) {
             profile_mark_begin(s);
@@ -616,18 +649,7 @@ int launch_decode_t(cudaStream_t s, const DecodeParams& p) {
     note_launch();
     VB200_CUDA_TRY(cudaPeekAtLastError());
     if (need_combine) {
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3(p.Hq, p.B);
-        cfg.blockDim = dim3(128 * kCombineGroups);
-        cfg.dynamicSmemBytes = 0;
-        cfg.stream = s;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_combine_kernel<T>, p));
-        note_launch();
+        if (int rc = launch_combine<T>(s, p)) return rc;
     }
     VB200_CUDA_TRY(cudaPeekAtLastError());
     return VB200_OK;
@@ -640,7 +662,7 @@ int launch_decode_nrep(cudaStream_t s, const DecodeParams& p) {
         case 2: return launch_decode_t<T, 2>(s, p);
         case 4: return launch_decode_t<T, 4>(s, p);
         case 8: return launch_decode_t<T, 8>(s, p);
-        default: return set_detail(VB200_ERR_UNSUPPORTED, "decode supports Hq/Hkv in {1,2,4,8}");
+        default: return launch_decode_generic<T>(s, p);        // other group sizes
     }
 }
 
@@ -649,10 +671,12 @@ int launch_decode_nrep(cudaStream_t s, const DecodeParams& p) {
 int decode_tile_keys() { return kTile; }
 
 int launch_decode(cudaStream_t s, const DecodeParams& p) {
-    if (p.D != 128) return set_detail(VB200_ERR_UNSUPPORTED, "split-KV decode supports head_dim 128");
-    if (p.dtype == VB200_BF16) return launch_decode_nrep<__nv_bfloat16>(s, p);
-    if (p.dtype == VB200_F16) return launch_decode_nrep<__half>(s, p);
-    return set_detail(VB200_ERR_UNSUPPORTED, "split-KV decode supports bf16 and fp16 caches");
+    // the tuned kernels: 16-bit caches, head_dim 128, contiguous cache rows (a tile is one bulk copy / TMA box)
+    const bool tuned = p.D == 128 && p.dtype != VB200_F32 && p.k_cache.ss == p.D && p.v_cache.ss == p.D;
+    if (p.dtype == VB200_BF16) return tuned ? launch_decode_nrep<__nv_bfloat16>(s, p) : launch_decode_generic<__nv_bfloat16>(s, p);
+    if (p.dtype == VB200_F16) return tuned ? launch_decode_nrep<__half>(s, p) : launch_decode_generic<__half>(s, p);
+    if (p.dtype == VB200_F32) return launch_decode_generic<float>(s, p);
+    return set_detail(VB200_ERR_UNSUPPORTED, "decode: unknown dtype");
 }
 
 int launch_lse_combine(cudaStream_t s, const float* partials, int R, long long rows, int D,

@@ -28,6 +28,10 @@ int launch_rope_table(cudaStream_t s, float2* table, int T, int D, int start_pos
 int launch_kv_append(cudaStream_t s, int dtype, int B, int H, int T, int D,
                      View4 k, View4 v, View4 k_dst, View4 v_dst, int dst_row0, const float2* table,
                      const InvFreq* inv_freq = nullptr);
+// table + rotated K + V rows in one launch: table[t][i] as launch_rope_table writes it, k_dst / v_dst rows
+// [dst_row0, dst_row0 + T) as launch_kv_append does with that table.  v / v_dst may be null (K only).
+int launch_rope_append_fused(cudaStream_t s, int dtype, int B, int H, int T, int D, View4 k, View4 v, View4 k_dst, View4 v_dst,
+                             int dst_row0, float2* table, const InvFreq& f);
 int launch_apply_rope_f32(cudaStream_t s, float* x, const float* cos_t, const float* sin_t,
                           int batch, int heads, int seq_len, int head_dim);
 int launch_repeat_kv(cudaStream_t s, int dtype, View4 in, void* out, int B, int Hkv, int S, int D, int n_rep);
@@ -49,6 +53,21 @@ struct PrefillParams {
 int launch_prefill_f32(cudaStream_t s, const PrefillParams& p);
 int launch_prefill_sm100(cudaStream_t s, const PrefillParams& p);
 int launch_prefill_pair_sm100(cudaStream_t s, const PrefillParams& p);   // head_dim 128: two SMs per work item (cta_group::2)
+
+// ---- decode_exchange.cu (declared first: the decode kernel can run the exchange as its tail) ----
+struct ExchangeParams {
+    int world, rank;
+    void* peers[VB200_EXCHANGE_MAX_WORLD];   // exchange buffer of every rank as this GPU addresses it; [rank] = own
+    const float* partial;                    // local [rows, D+2]
+    long long rows;
+    long long rows_per_cta;                  // filled in by the launcher
+    int D, dtype;
+    void* out;                               // [rows, D]
+    float* lse;                              // [rows] or null
+    unsigned step;                           // 0 = take the next step number from the buffer's own counter
+    long long timeout_cycles;
+    int* status;
+};
 
 // ---- decode_splitkv.cu ----
 struct DecodeParams {
@@ -74,6 +93,11 @@ struct DecodeParams {
     int ws_header;       // floats reserved at the front of the workspace (multiple of 64)
     int* status;         // device status word (bounded waits)
     int cluster_merge;   // 1: the splits of a (batch, kv_head) form one thread-block cluster that merges its partials itself
+    // Sequence-sharded decode in ONE launch (warp-MMA split kernel only): the CTA that delivers the last split of a
+    // (batch, kv_head) merges the splits and runs the exchange protocol for that group's rows (exchange_rows in
+    // decode_exchange.cuh) -- no combine kernel, no exchange kernel, no partial records in HBM.
+    int fused_exchange;
+    ExchangeParams xchg;
 };
 // Length bookkeeping of one decode step for sequence b, shared by the split kernels and the combine
 // kernel.  len = cached keys attended to; append = whether the new token is written and attended to.
@@ -102,6 +126,7 @@ __device__ __forceinline__ StepLen step_length(const DecodeParams& p, int b) {
 }
 #endif
 int decode_tile_keys();
+int launch_decode_generic_split(cudaStream_t s, const DecodeParams& p);   // decode_generic.cu
 int launch_decode(cudaStream_t s, const DecodeParams& p);
 // decode_gqa_mma.cu: split kernel with warp-MMA products (instantiated for Hq / Hkv of 4 and 8); same workspace layout
 template <typename T, int NREP> int launch_decode_gqa_mma_split(cudaStream_t s, const DecodeParams& p);
@@ -119,19 +144,6 @@ struct AttnBwdParams {
 int launch_attention_bwd_f32(cudaStream_t s, const AttnBwdParams& p);
 
 // ---- decode_exchange.cu ----
-struct ExchangeParams {
-    int world, rank;
-    void* peers[VB200_EXCHANGE_MAX_WORLD];   // exchange buffer of every rank as this GPU addresses it; [rank] = own
-    const float* partial;                    // local [rows, D+2]
-    long long rows;
-    long long rows_per_cta;                  // filled in by the launcher
-    int D, dtype;
-    void* out;                               // [rows, D]
-    float* lse;                              // [rows] or null
-    unsigned step;                           // 0 = take the next step number from the buffer's own counter
-    long long timeout_cycles;
-    int* status;
-};
 size_t exchange_buffer_bytes(int world, long long rows, int D);
 int launch_exchange_combine(cudaStream_t s, ExchangeParams p);
 

@@ -1,27 +1,34 @@
 // bf16 / fp16 attention forward for head_dim 128 on sm_100a, two SMs per work item: a cluster of two CTAs runs
-// every product as ONE tcgen05.mma.cta_group::2 of M = 256 query rows (128 per CTA) against a key / value block
-// of which each CTA holds HALF in its shared memory (the K rows 64c .. 64c+63 of the block for S = Q K^T, the V
-// columns 64c .. 64c+63 for O += P V).  Per SM that halves the shared-memory traffic of the B operand and the
-// L2 -> SM fill traffic of K / V, which is what bounds the single-CTA kernel (prefill_sm100.cu: A and B of a
-// 128 x 128 x 16 product both from shared memory need 128 B/clk, the shared-memory limit).
+// every product as ONE tcgen05.mma.cta_group::2 of M = 256 query rows (one 128-row tile per CTA) against a key /
+// value block of which each CTA holds HALF in its shared memory (the K rows 64c .. 64c+63 of the block for
+// S = Q K^T, the V columns 64c .. 64c+63 for O += P V).  Halving the B-operand traffic per SM is what lets ONE query
+// tile per SM keep the tensor pipe fed (a single CTA needs two tiles per K / V block to stay under the 128 B/clk
+// shared-memory limit, prefill_sm100.cu), and one tile per SM leaves TMEM room to take the products off the
+// softmax's critical path:
+//   TMEM per CTA (512 columns): S[0] [0,128)  S[1] [128,256)  O [256,384)  P[0] [384,448)  P[1] [448,512)
+//   block g of the running block count uses S[g & 1] and P[g & 1].  Q K^T of block g+2 is issued as soon as the
+//   softmax has READ S of block g into registers, i.e. long before it finishes block g; P has its own columns, so
+//   nothing the softmax still needs is overwritten.  The softmax warpgroup therefore goes from block to block
+//   (and from one work item to the next) without waiting for a product; the hand-over latencies between the two SMs
+//   stay off its path.  A second warpgroup drains O of a finished item (scale by 1/l, stage in shared memory, TMA
+//   store, LSE) while the softmax warpgroup is already in the next item.
 //
 // Math (flash_attention_cpu_dispatch, src/ops/flash_attention.cpp:218-364):
 //   s_ij = scale * q_i . k_j ;  key j visible to query i iff j <= start_pos + i
 //   O_i = sum_j softmax_j(s_ij) v_j ;  LSE_i = ln sum_j exp(s_ij)
 //
-// A work item is FOUR 128-row query tiles that read the same K / V blocks -- two per CTA -- e.g. the same rows of
-// the four query heads of a GQA group.  Persistent: cluster x of the grid walks items x, x + G, ... in snake order,
-// heaviest (last rows) first.  Roles per CTA (384 threads):
-//   warps 0-3 / 4-7  softmax, correction and epilogue of this CTA's tile 0 / 1 (one thread per row = TMEM lane)
-//   warp  8          TMA producer: this CTA's Q tiles (3 rotating buffers) and its halves of K and V (4-slot ring)
-//   warp  9          TMEM owner; in the leader CTA (cluster rank 0) also the ONLY issuer of tcgen05.mma
-//   warps 10-11      RoPE of freshly loaded Q tiles, in place in swizzled shared memory
+// A work item is TWO 128-row query tiles that read the same K / V blocks -- one per CTA: the same rows of two query
+// heads of a GQA group, or two adjacent row tiles of one head.  Persistent: cluster x of the grid walks items
+// x, x + G, ... in snake order, heaviest (last rows) first.  Roles per CTA (384 threads):
+//   warps 0-3    softmax of this CTA's tile: one thread per row = TMEM lane; also the (rare) rescale of O
+//   warps 4-7    epilogue of finished items
+//   warp  8      TMA producer: this CTA's Q tiles (3 rotating buffers) and its halves of K and V (6-slot ring)
+//   warp  9      TMEM owner; in the leader CTA (cluster rank 0) also the ONLY issuer of tcgen05.mma
+//   warps 10-11  RoPE of freshly loaded Q tiles, in place in swizzled shared memory
 // Hand-overs: the leader's MMA thread waits on barriers in ITS shared memory that both CTAs feed -- the K / V
 // "full" barrier receives the transaction bytes of both CTAs' TMA loads (cp.async.bulk.tensor with .cta_group::2
-// naming the leader's barrier; no multicast anywhere), the "Q rotated" and "P ready" barriers receive remote
-// mbarrier arrivals -- and signals back with tcgen05.commit multicast to the same barrier in both CTAs.
-// TMEM per CTA (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P (16-bit) overwrites the first
-// 64 columns of its S.  The epilogue stages the O tile in shared memory and writes it with TMA stores.
+// naming the leader's barrier; no multicast anywhere), "Q rotated", "S read", "P ready" and "O drained" receive
+// remote mbarrier arrivals -- and signals back with tcgen05.commit multicast to the same barrier in both CTAs.
 //
 // Every wait is bounded (mbar_wait); on expiry the CTA drains and returns with the device status word set.
 #include <cstdio>
@@ -35,7 +42,7 @@ namespace {
 constexpr int kBlockM = 128;           // query rows per tile
 constexpr int kBlockN = 128;           // keys per block
 constexpr int kD = 128;                // head_dim of this kernel
-constexpr int kStages = 4;             // ring slots, each HALF a K or V block (16 KB)
+constexpr int kStages = 6;             // ring slots, each HALF a K or V block (16 KB)
 constexpr int kQBufs = 3;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
@@ -44,25 +51,30 @@ constexpr int kThreads = 384;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;
-constexpr int kRegSoftmax = 216, kRegOther = 72;
-static_assert(kRegSoftmax * 256 + kRegOther * 128 <= 168 * 384, "register budget");
+constexpr int kRegSoftmax = 232, kRegEpilogue = 168, kRegOther = 72;     // per thread after setmaxnreg, by warpgroup (168 = the launch value)
+static_assert((kRegSoftmax + kRegEpilogue + kRegOther) * 128 <= 168 * 384, "register budget");
 
 constexpr int kBoxBytes = 128 * 128;                 // [128 rows][64 cols] 16-bit box, 128-byte rows, 128B swizzle
 constexpr int kTileBytes = 2 * kBoxBytes;            // one [128][128] tile (Q, or the O staging area)
 constexpr int kSlotBytes = kBoxBytes;                // half a K block (2 boxes of [64 rows][64 cols]) or half a V block (1 box)
-constexpr int kSmemBytes = kQBufs * kTileBytes + kStages * kSlotBytes + 2 * kTileBytes + 1024 + 256;
+constexpr int kSmemBytes = kQBufs * kTileBytes + kStages * kSlotBytes + kTileBytes + kBlockM * 8 + 1024 + 512;
+static_assert(kSmemBytes <= 232448, "227 KB of dynamic shared memory per CTA");
 
 struct __align__(8) Barriers {
     uint64_t q_full[kQBufs];            // local: this CTA's Q tile landed
     uint64_t q_rot[kQBufs];             // leader: both CTAs' Q tiles rotated (or just loaded), 4 warp arrivals
-    uint64_t q_free[kQBufs];            // both (multicast commit): last QK^T of the tile retired
+    uint64_t q_free[kQBufs];            // both (multicast commit): last QK^T of the item retired
     uint64_t kv_full[kStages];          // leader: both halves of the slot landed
     uint64_t kv_empty[kStages];         // both (multicast commit)
-    uint64_t s_full[2];                 // both (multicast commit)
-    uint64_t p_ready[2];                // leader: 8 warp arrivals (4 per CTA)
-    uint64_t o_done[2];                 // both (multicast commit)
+    uint64_t s_full[2];                 // both (multicast commit): S[b] holds the scores of a block
+    uint64_t s_free[2];                 // leader: both softmax warpgroups have S[b] in registers (8 warp arrivals)
+    uint64_t p_ready[2];                // leader: P[b] written (8 warp arrivals)
+    uint64_t pv_done[2];                // both (multicast commit): the product that read P[b] retired
+    uint64_t o_free;                    // leader: both epilogue warpgroups have O in registers (8 warp arrivals)
     uint64_t mma_done;                  // both (multicast commit)
-    uint64_t epi_done[2];               // local: the 128 rows of a staged O tile are written (128 arrivals)
+    uint64_t stat_full, stat_free;      // local, softmax <-> epilogue warpgroup: (m, l) of a finished item (128 arrivals)
+    uint64_t stage_free;                // local: the previous TMA store has finished reading the staging tile (1 arrival)
+    uint64_t epi_done;                  // local: the 128 rows of the staged O tile are written (128 arrivals)
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -71,54 +83,53 @@ struct PairMaps {
     CUtensorMap q, k, v, o;
 };
 
-// How the four tiles of an item are laid over (head, row tile): A = four heads of a group, B = two heads x two
-// adjacent row tiles, C = four adjacent row tiles of one head.
-__host__ __device__ __forceinline__ int item_mode(const PrefillParams& p) {
-    const int n_rep = p.Hq / p.Hkv;
-    return (n_rep % 4 == 0) ? 0 : (n_rep % 2 == 0) ? 1 : 2;
-}
-__host__ __device__ __forceinline__ int item_cols(const PrefillParams& p) {
-    const int m = item_mode(p);
-    return p.B * (m == 0 ? p.Hq / 4 : m == 1 ? p.Hq / 2 : p.Hq);
-}
+#ifdef VBP_PROF
+// development build only: per-CTA cycle counters, [cta][slot]
+__device__ long long g_pair_prof[160 * 32];
+#define PROF_DECL(name) long long name = 0
+#define PROF_T0(v) const long long v = clock64()
+#define PROF_ADD(acc, t0) acc += clock64() - (t0)
+#define PROF_OUT(slot, val) g_pair_prof[blockIdx.x * 32 + (slot)] = (val)
+#else
+#define PROF_DECL(name)
+#define PROF_T0(v)
+#define PROF_ADD(acc, t0)
+#define PROF_OUT(slot, val)
+#endif
+
+// How the two tiles of an item are laid over (head, row tile): two heads of a group (an even number of query
+// heads per KV head), else two adjacent row tiles of one head.
+__host__ __device__ __forceinline__ bool pair_by_heads(const PrefillParams& p) { return (p.Hq / p.Hkv) % 2 == 0; }
+__host__ __device__ __forceinline__ int item_cols(const PrefillParams& p) { return pair_by_heads(p) ? p.B * (p.Hq / 2) : p.B * p.Hq; }
 __host__ __device__ __forceinline__ int item_rows(const PrefillParams& p) {
-    const int m = item_mode(p);
-    const int span = kBlockM * (m == 0 ? 1 : m == 1 ? 2 : 4);
+    const int span = pair_by_heads(p) ? kBlockM : 2 * kBlockM;
     return (p.T + span - 1) / span;
 }
 
 struct Item {
     int b, hkv;
-    int hq[2];       // head of this CTA's tile 0 / 1
-    int r0[2];       // first query row of each tile (may be >= T: the tile is then computed on zero rows and not stored)
-    int n;           // key blocks EVERY tile of the item steps through (the longest tile's count; the others see masked blocks)
+    int hq;          // head of this CTA's tile
+    int r0;          // first query row of this CTA's tile (may be >= T: computed on zero rows and not stored)
+    int n;           // key blocks BOTH tiles of the item step through (the longer tile's count; the other sees masked blocks)
 };
 
 __device__ __forceinline__ Item get_item(const PrefillParams& p, int it, int n_cols, int n_rows, int cta) {
     Item w;
     const int pr = n_rows - 1 - it / n_cols;       // heaviest (last) query rows first
     const int col = it % n_cols;
-    const int mode = item_mode(p);
     int last_r0;
-    if (mode == 0) {
-        const int g = col % (p.Hq / 4);
-        w.b = col / (p.Hq / 4);
-        w.hq[0] = 4 * g + 2 * cta; w.hq[1] = w.hq[0] + 1;
-        w.r0[0] = w.r0[1] = pr * kBlockM;
-        last_r0 = pr * kBlockM;
-    } else if (mode == 1) {
-        const int g = col % (p.Hq / 2);
+    if (pair_by_heads(p)) {
         w.b = col / (p.Hq / 2);
-        w.hq[0] = 2 * g; w.hq[1] = 2 * g + 1;
-        w.r0[0] = w.r0[1] = (2 * pr + cta) * kBlockM;
-        last_r0 = (2 * pr + 1) * kBlockM;
+        w.hq = 2 * (col % (p.Hq / 2)) + cta;
+        w.r0 = pr * kBlockM;
+        last_r0 = w.r0;
     } else {
         w.b = col / p.Hq;
-        w.hq[0] = w.hq[1] = col % p.Hq;
-        w.r0[0] = (4 * pr + 2 * cta) * kBlockM; w.r0[1] = w.r0[0] + kBlockM;
-        last_r0 = (4 * pr + 3) * kBlockM;
+        w.hq = col % p.Hq;
+        w.r0 = (2 * pr + cta) * kBlockM;
+        last_r0 = (2 * pr + 1) * kBlockM;
     }
-    w.hkv = w.hq[0] / (p.Hq / p.Hkv);
+    w.hkv = w.hq / (p.Hq / p.Hkv);
     int kv_end = p.Skv;
     if (p.causal) kv_end = min(p.Skv, p.start_pos + min(last_r0 + kBlockM, p.T));
     w.n = (kv_end + kBlockN - 1) / kBlockN;
@@ -146,36 +157,26 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
     return r;
 }
+// Arrival on a barrier of the peer CTA.  Default semantics (release at CTA scope): what is handed over lives in TMEM
+// or was made visible to the async proxy by its writer, and is ordered by the tcgen05 / proxy fences around the
+// barrier; a release at cluster scope here was measured at ~1000 cycles per arrival on the arriving warp.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The same with a cluster-scope release, for generic-proxy data written by this CTA's threads (off the critical path).
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
-// Bounded wait with cluster-scope acquire (the barrier is fed by the peer CTA as well).
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where) {
-    const uint32_t addr = smem_u32(bar);
-    uint32_t ok = 0;
-    long long t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((it & 0xFF) == 0xFF) {
-            if (*ctx.abort_flag) return false;
-            const long long now = clock64();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitCycles) {
-                *ctx.abort_flag = 1;
-                atomicCAS(ctx.status, 0, (1 << 24) | where);
-                return false;
-            }
-        }
-    }
-}
+#ifdef VBP_BACKOFF
+#define WAIT_OFFPATH mbar_wait_relaxed
+#define WAIT_OFFPATH_WARP mbar_wait_relaxed_warp
+#else
+#define WAIT_OFFPATH mbar_wait
+#define WAIT_OFFPATH_WARP mbar_wait_warp
+#endif
 
 // 4-D tiled TMA load whose completion bytes go to a barrier that may live in the peer CTA (`bar_cluster_addr` is a
 // shared::cluster address); the destination is this CTA's own shared memory.  No multicast.
@@ -229,6 +230,36 @@ __device__ __forceinline__ void umma2_commit(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"(both) : "memory");
 }
 
+// Walks the key blocks of all work items of a cluster in processing order: g counts blocks over the whole kernel
+// (it selects the S / P buffer and the barrier phases), j the block inside the current item.
+struct BlockCursor {
+    int round, n_rounds, n_items, cluster, n_clusters, n_cols, n_rows, cta;
+    int item_no;     // items started so far - 1
+    int j, g;
+    bool valid;
+    Item w;
+    __device__ void find_item(const PrefillParams& p) {
+        int idx = -1;
+        while (round < n_rounds && (idx = item_of_round(round, n_items, cluster, n_clusters)) < 0) ++round;
+        valid = idx >= 0;
+        if (valid) { w = get_item(p, idx, n_cols, n_rows, cta); ++item_no; j = 0; }
+    }
+    __device__ void init(const PrefillParams& p, int n_rounds_, int n_items_, int cluster_, int n_clusters_, int n_cols_, int n_rows_, int cta_) {
+        round = 0; n_rounds = n_rounds_; n_items = n_items_; cluster = cluster_; n_clusters = n_clusters_; n_cols = n_cols_; n_rows = n_rows_; cta = cta_;
+        item_no = -1; j = 0; g = 0;
+        find_item(p);
+    }
+    __device__ void next(const PrefillParams& p) {       // to the next block
+        ++g;
+        if (++j >= w.n) { ++round; find_item(p); }
+    }
+    __device__ void next_item(const PrefillParams& p) {  // to the first block of the next item
+        g += w.n - j;
+        ++round;
+        find_item(p);
+    }
+};
+
 template <typename T, bool kExactRope>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
@@ -236,8 +267,9 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     unsigned char* q_smem = smem;                                        // kQBufs tiles
     unsigned char* kv_smem = q_smem + kQBufs * kTileBytes;               // kStages half-block slots
-    unsigned char* o_smem = kv_smem + kStages * kSlotBytes;              // 2 staging tiles (one per softmax warpgroup)
-    Barriers* bar = reinterpret_cast<Barriers*>(o_smem + 2 * kTileBytes);
+    unsigned char* o_smem = kv_smem + kStages * kSlotBytes;              // staging tile of the epilogue
+    float2* stats = reinterpret_cast<float2*>(o_smem + kTileBytes);      // [128] (m_ref, l_sum) of the item that just finished
+    Barriers* bar = reinterpret_cast<Barriers*>(o_smem + kTileBytes + kBlockM * 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t cta = cluster_ctarank();                              // 0 = leader (issues the MMAs), 1 = peer
@@ -252,11 +284,15 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
     if (warp == kMmaWarp) {
         if (lane == 0) {
             for (int b = 0; b < kQBufs; ++b) { mbar_init(&bar->q_full[b], 1); mbar_init(&bar->q_rot[b], 4); mbar_init(&bar->q_free[b], 1); }
-            for (int t = 0; t < 2; ++t) {
-                mbar_init(&bar->s_full[t], 1); mbar_init(&bar->p_ready[t], 8); mbar_init(&bar->o_done[t], 1); mbar_init(&bar->epi_done[t], kBlockM);
-            }
             for (int s = 0; s < kStages; ++s) { mbar_init(&bar->kv_full[s], 1); mbar_init(&bar->kv_empty[s], 1); }
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(&bar->s_full[b], 1); mbar_init(&bar->s_free[b], 8); mbar_init(&bar->p_ready[b], 8); mbar_init(&bar->pv_done[b], 1);
+            }
+            mbar_init(&bar->stat_full, kBlockM); mbar_init(&bar->stat_free, kBlockM);
+            mbar_init(&bar->o_free, 8);
             mbar_init(&bar->mma_done, 1);
+            mbar_init(&bar->stage_free, 1);
+            mbar_init(&bar->epi_done, kBlockM);
             bar->abort_flag = 0;
             mbar_fence_init();
         }
@@ -279,51 +315,52 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
         reg_dec<kRegOther>();
         if (warp == kProducerWarp) {
             // =========================== TMA producer (each CTA: its Q tiles, its halves of K and V) ===========================
+            // K / V slots are filled in the order the MMA thread consumes them: K(0), K(1), then for every block g of the
+            // kernel-wide sequence K(g+2), V(g) -- across item boundaries.
             if (lane == 0) {
-                int kv_item = 0, q_seq = 0;
+                int kv_item = 0;
                 bool ok = true;
-                uint32_t kv_full_leader[kStages];
-#pragma unroll
-                for (int s = 0; s < kStages; ++s) kv_full_leader[s] = map_to_cta(smem_u32(&bar->kv_full[s]), 0);
-                auto load_q = [&](const Item& w, int t) {
+                const uint32_t kv_full_leader0 = map_to_cta(smem_u32(&bar->kv_full[0]), 0);   // the barriers of one kind are contiguous
+                int q_loaded = -1;               // last item number whose Q tile load was issued
+                auto load_q = [&](const BlockCursor& c) {
+                    if (!ok || !c.valid || c.item_no <= q_loaded) return;
+                    const int b = c.item_no % kQBufs, use = c.item_no / kQBufs;
+                    if (use > 0) ok = WAIT_OFFPATH(&bar->q_free[b], (use - 1) & 1, abort_flag, 0x110 + b);
                     if (!ok) return;
-                    const int b = q_seq % kQBufs, use = q_seq / kQBufs;
-                    if (use > 0) ok = mbar_wait(&bar->q_free[b], (use - 1) & 1, abort_flag, 0x110 + b);
-                    if (!ok) return;
-                    ++q_seq;
+                    q_loaded = c.item_no;
                     mbar_arrive_expect_tx(&bar->q_full[b], kTileBytes);
                     // rows at or past T (an absent tile, a ragged last tile) arrive as zeros
-                    tma_load_4d(q_smem + b * kTileBytes, &maps.q, &bar->q_full[b], 0, w.r0[t], w.hq[t], w.b);
-                    tma_load_4d(q_smem + b * kTileBytes + kBoxBytes, &maps.q, &bar->q_full[b], 64, w.r0[t], w.hq[t], w.b);
+                    tma_load_4d(q_smem + b * kTileBytes, &maps.q, &bar->q_full[b], 0, c.w.r0, c.w.hq, c.w.b);
+                    tma_load_4d(q_smem + b * kTileBytes + kBoxBytes, &maps.q, &bar->q_full[b], 64, c.w.r0, c.w.hq, c.w.b);
                 };
-                int round = 0, idx = -1;
-                while (round < n_rounds && (idx = item_of_round(round, n_items, cluster_id, n_clusters)) < 0) ++round;
-                Item w;
-                if (idx >= 0) { w = get_item(p, idx, n_cols, n_rows, cta); load_q(w, 0); load_q(w, 1); }
-                while (idx >= 0 && ok) {
-                    int round2 = round + 1, idx2 = -1;
-                    while (round2 < n_rounds && (idx2 = item_of_round(round2, n_items, cluster_id, n_clusters)) < 0) ++round2;
-                    Item wn;
-                    if (idx2 >= 0) { wn = get_item(p, idx2, n_cols, n_rows, cta); load_q(wn, 0); }
-                    for (int x = 0; x < 2 * w.n && ok; ++x, ++kv_item) {        // x = 2j: K_j, 2j+1: V_j
-                        const int slot = kv_item % kStages;
-                        if (kv_item >= kStages) ok = mbar_wait(&bar->kv_empty[slot], ((kv_item / kStages) - 1) & 1, abort_flag, 0x100);
-                        if (!ok) break;
-                        // the leader's barrier collects the bytes of both CTAs' halves
-                        if (leader) mbar_arrive_expect_tx(&bar->kv_full[slot], 2 * kSlotBytes);
-                        unsigned char* dst = kv_smem + slot * kSlotBytes;
-                        const int key0 = (x >> 1) * kBlockN;
-                        if ((x & 1) == 0) {
-                            // K: this CTA's 64 keys of the block, all 128 dims, as two [64 rows][64 cols] boxes
-                            tma_load_4d_pair(dst, &maps.k, kv_full_leader[slot], 0, key0 + 64 * static_cast<int>(cta), w.hkv, w.b);
-                            tma_load_4d_pair(dst + kSlotBytes / 2, &maps.k, kv_full_leader[slot], 64, key0 + 64 * static_cast<int>(cta), w.hkv, w.b);
-                        } else {
-                            // V: all 128 keys of the block, this CTA's 64 dims, one [128 rows][64 cols] box
-                            tma_load_4d_pair(dst, &maps.v, kv_full_leader[slot], 64 * static_cast<int>(cta), key0, w.hkv, w.b);
-                        }
+                auto load_half = [&](const BlockCursor& c, bool is_v) {
+                    if (!ok) return;
+                    const int slot = kv_item % kStages;
+                    if (kv_item >= kStages) ok = WAIT_OFFPATH(&bar->kv_empty[slot], ((kv_item / kStages) - 1) & 1, abort_flag, 0x100);
+                    if (!ok) return;
+                    ++kv_item;
+                    // the leader's barrier collects the bytes of both CTAs' halves
+                    if (leader) mbar_arrive_expect_tx(&bar->kv_full[slot], 2 * kSlotBytes);
+                    unsigned char* dst = kv_smem + slot * kSlotBytes;
+                    const uint32_t full_bar = kv_full_leader0 + 8 * slot;
+                    const int key0 = c.j * kBlockN;
+                    if (!is_v) {
+                        // K: this CTA's 64 keys of the block, all 128 dims, as two [64 rows][64 cols] boxes
+                        tma_load_4d_pair(dst, &maps.k, full_bar, 0, key0 + 64 * static_cast<int>(cta), c.w.hkv, c.w.b);
+                        tma_load_4d_pair(dst + kSlotBytes / 2, &maps.k, full_bar, 64, key0 + 64 * static_cast<int>(cta), c.w.hkv, c.w.b);
+                    } else {
+                        // V: all 128 keys of the block, this CTA's 64 dims, one [128 rows][64 cols] box
+                        tma_load_4d_pair(dst, &maps.v, full_bar, 64 * static_cast<int>(cta), key0, c.w.hkv, c.w.b);
                     }
-                    if (idx2 >= 0) load_q(wn, 1);
-                    idx = idx2; round = round2; w = wn;
+                };
+                BlockCursor kc, vc;              // K runs two blocks ahead of V
+                kc.init(p, n_rounds, n_items, cluster_id, n_clusters, n_cols, n_rows, cta);
+                vc = kc;
+                for (int pre = 0; pre < 2 && kc.valid && ok; ++pre) { load_q(kc); load_half(kc, false); kc.next(p); }
+                while (vc.valid && ok) {
+                    if (kc.valid) { load_q(kc); load_half(kc, false); kc.next(p); }
+                    load_half(vc, true);
+                    vc.next(p);
                 }
             }
         } else if (warp == kMmaWarp) {
@@ -331,91 +368,88 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
             if (leader && lane == 0) {
                 constexpr uint32_t idesc_qk = make_idesc_f16(Elem<T>::kFormat, 0, 0, 2 * kBlockM, kBlockN);
                 constexpr uint32_t idesc_pv = make_idesc_f16(Elem<T>::kFormat, 0, 1, 2 * kBlockM, kD);
-                const uint32_t q_addr = smem_u32(q_smem), kv_addr = smem_u32(kv_smem);
-                auto tmem_s = [&](int t) { return tmem_base + static_cast<uint32_t>(t * 128); };
-                auto tmem_o = [&](int t) { return tmem_base + static_cast<uint32_t>(256 + t * 128); };
-                auto issue_qk = [&](int t, int qbuf, int slot) {
+                // Shared-memory matrix descriptors, built once: 128-byte swizzle, 1024 bytes between 8-row groups; per
+                // product only the start-address field (low word, in 16-byte units) moves.  The issuing thread's own
+                // instruction stream is what bounds the tensor pipe here: every instruction between two MMAs counts.
+                const uint64_t desc_q0 = make_smem_desc_sw128(smem_u32(q_smem), 16, 1024);              // Q tile, K-major
+                const uint64_t desc_k0 = make_smem_desc_sw128(smem_u32(kv_smem), 16, 1024);             // K half, K-major
+                const uint64_t desc_v0 = make_smem_desc_sw128(smem_u32(kv_smem), kBoxBytes, 1024);      // V half, MN-major
+                const uint32_t tmem_o = tmem_base + 256;
+                int kv_item = 0;
+                bool ok = true;
+                PROF_DECL(w_qrot); PROF_DECL(w_sfree); PROF_DECL(w_kfull); PROF_DECL(w_pready); PROF_DECL(w_ofree); PROF_DECL(w_vfull); PROF_DECL(n_blocks); PROF_DECL(t_iqk); PROF_DECL(t_ipv);
+                PROF_T0(t_start);
+                // S[g & 1] = Q K(block)^T for the block the cursor stands on
+                auto issue_qk = [&](const BlockCursor& c) {
+                    if (!ok) return;
+                    const int qbuf = c.item_no % kQBufs;
+                    { PROF_T0(t0); if (c.j == 0) ok = mbar_wait(&bar->q_rot[qbuf], (c.item_no / kQBufs) & 1, abort_flag, 0x210); PROF_ADD(w_qrot, t0); }
+                    // S[g & 1] was last used by block g - 2: both softmax warpgroups must have read it
+                    { PROF_T0(t0); if (ok && c.g >= 2) ok = mbar_wait(&bar->s_free[c.g & 1], ((c.g >> 1) - 1) & 1, abort_flag, 0x220); PROF_ADD(w_sfree, t0); }
+                    const int slot = kv_item % kStages;
+                    { PROF_T0(t0); if (ok) ok = mbar_wait(&bar->kv_full[slot], (kv_item / kStages) & 1, abort_flag, 0x200); PROF_ADD(w_kfull, t0); }
+                    if (!ok) return;
+                    ++kv_item;
+                    tc_fence_after();
+                    PROF_T0(t_i0);
+                    const uint32_t d = tmem_base + static_cast<uint32_t>((c.g & 1) * 128);
+                    const uint64_t a0 = desc_q0 + static_cast<uint64_t>(qbuf * (kTileBytes >> 4));
+                    const uint64_t b0 = desc_k0 + static_cast<uint64_t>(slot * (kSlotBytes >> 4));
 #pragma unroll
                     for (int kk = 0; kk < kD / 16; ++kk) {
                         // A: [128 rows][64 cols] boxes of the Q tile; B: [64 rows][64 cols] boxes of this CTA's K half
-                        const uint64_t a = make_smem_desc_sw128(q_addr + qbuf * kTileBytes + (kk >> 2) * kBoxBytes + (kk & 3) * 32, 16, 1024);
-                        const uint64_t bd = make_smem_desc_sw128(kv_addr + slot * kSlotBytes + (kk >> 2) * (kSlotBytes / 2) + (kk & 3) * 32, 16, 1024);
-                        umma2_ss(tmem_s(t), a, bd, idesc_qk, kk > 0 ? 1u : 0u);
+                        const uint64_t a = a0 + static_cast<uint64_t>(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
+                        const uint64_t bd = b0 + static_cast<uint64_t>(((kk >> 2) * (kSlotBytes / 2) + (kk & 3) * 32) >> 4);
+                        umma2_ss(d, a, bd, idesc_qk, kk > 0 ? 1u : 0u);
                     }
+                    umma2_commit(&bar->s_full[c.g & 1]);
+                    umma2_commit(&bar->kv_empty[slot]);
+                    if (c.j + 1 == c.w.n) umma2_commit(&bar->q_free[qbuf]);          // last QK of the item
+                    PROF_ADD(t_iqk, t_i0);
                 };
-                auto issue_pv = [&](int t, int slot, bool accumulate) {
+                BlockCursor qk, pv;
+                qk.init(p, n_rounds, n_items, cluster_id, n_clusters, n_cols, n_rows, 0);
+                pv = qk;
+                for (int pre = 0; pre < 2 && qk.valid && ok; ++pre) { issue_qk(qk); qk.next(p); }
+                while (pv.valid && ok) {
+                    if (qk.valid) { issue_qk(qk); qk.next(p); }
+                    if (!ok) break;
+                    // O += P[g & 1] V(block)
+                    const int b = pv.g & 1;
+                    { PROF_T0(t0); ok = mbar_wait(&bar->p_ready[b], (pv.g >> 1) & 1, abort_flag, 0x400); PROF_ADD(w_pready, t0); }
+                    // the first product of an item overwrites O: the previous item's O must have been drained
+                    { PROF_T0(t0); if (ok && pv.j == 0 && pv.item_no > 0) ok = mbar_wait(&bar->o_free, (pv.item_no - 1) & 1, abort_flag, 0x410); PROF_ADD(w_ofree, t0); }
+                    const int slot = kv_item % kStages;
+                    { PROF_T0(t0); if (ok) ok = mbar_wait(&bar->kv_full[slot], (kv_item / kStages) & 1, abort_flag, 0x300); PROF_ADD(w_vfull, t0); }
+                    if (!ok) break;
+#ifdef VBP_PROF
+                    ++n_blocks;
+#endif
+                    ++kv_item;
+                    tc_fence_after();
+                    PROF_T0(t_i1);
+                    const uint32_t a_tmem = tmem_base + static_cast<uint32_t>(384 + b * 64);
+                    const uint64_t v0 = desc_v0 + static_cast<uint64_t>(slot * (kSlotBytes >> 4));
+                    const uint32_t acc0 = pv.j > 0 ? 1u : 0u;
 #pragma unroll
                     for (int kk = 0; kk < kBlockN / 16; ++kk) {
                         // V half is MN-major for this product: 16 keys = 2048 bytes per step, 64 dims per CTA
-                        const uint64_t bd = make_smem_desc_sw128(kv_addr + slot * kSlotBytes + kk * 2048, kBoxBytes, 1024);
-                        umma2_ts(tmem_o(t), tmem_s(t) + kk * 8, bd, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+                        umma2_ts(tmem_o, a_tmem + kk * 8, v0 + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv, kk > 0 ? 1u : acc0);
                     }
-                };
-                int kv_item = 0, q_seq = 0;
-                int blk[2] = {0, 0};             // running count of score tiles per tile index (barrier phases)
-                bool ok = true;
-                for (int round = 0; round < n_rounds && ok; ++round) {
-                    const int idx = item_of_round(round, n_items, cluster_id, n_clusters);
-                    if (idx < 0) continue;
-                    const Item w = get_item(p, idx, n_cols, n_rows, 0);
-                    int qbuf[2] = {0, 0};
-                    const int k0_slot = kv_item % kStages;
-                    ok = mbar_wait_cluster(&bar->kv_full[k0_slot], (kv_item / kStages) & 1, abort_flag, 0x200);
-#pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        if (!ok) continue;
-                        qbuf[t] = q_seq % kQBufs;
-                        const int ph = (q_seq / kQBufs) & 1;
-                        ++q_seq;
-                        // S of this tile is free: every PV of the previous item was issued before this point
-                        ok = mbar_wait_cluster(&bar->q_rot[qbuf[t]], ph, abort_flag, 0x210 + t);
-                        if (!ok) continue;
-                        tc_fence_after();
-                        issue_qk(t, qbuf[t], k0_slot);
-                        umma2_commit(&bar->s_full[t]);
-                        if (w.n == 1) umma2_commit(&bar->q_free[qbuf[t]]);
-                    }
-                    if (!ok) break;
-                    umma2_commit(&bar->kv_empty[k0_slot]);
-                    for (int j = 0; j < w.n && ok; ++j) {
-                        const int v_item = kv_item + 2 * j + 1, k_item = kv_item + 2 * j + 2;
-                        const int v_slot = v_item % kStages, k_slot = k_item % kStages;
-                        ok = mbar_wait_cluster(&bar->kv_full[v_slot], (v_item / kStages) & 1, abort_flag, 0x300);
-                        bool k_ready = false;
-#pragma unroll
-                        for (int t = 0; t < 2; ++t) {
-                            if (!ok) continue;
-                            ok = mbar_wait_cluster(&bar->p_ready[t], blk[t] & 1, abort_flag, 0x400 + t);
-                            if (!ok) continue;
-                            ++blk[t];
-                            tc_fence_after();
-                            issue_pv(t, v_slot, j > 0);
-                            umma2_commit(&bar->o_done[t]);
-                            if (j + 1 < w.n) {
-                                if (!k_ready) {
-                                    ok = mbar_wait_cluster(&bar->kv_full[k_slot], (k_item / kStages) & 1, abort_flag, 0x500);
-                                    if (!ok) continue;
-                                    tc_fence_after();
-                                    k_ready = true;
-                                }
-                                issue_qk(t, qbuf[t], k_slot);
-                                umma2_commit(&bar->s_full[t]);
-                                if (j + 2 == w.n) umma2_commit(&bar->q_free[qbuf[t]]);   // last QK of this tile
-                            }
-                        }
-                        if (!ok) break;
-                        umma2_commit(&bar->kv_empty[v_slot]);
-                        if (j + 1 < w.n) umma2_commit(&bar->kv_empty[k_slot]);
-                    }
-                    kv_item += 2 * w.n;
+                    umma2_commit(&bar->pv_done[b]);
+                    umma2_commit(&bar->kv_empty[slot]);
+                    PROF_ADD(t_ipv, t_i1);
+                    pv.next(p);
                 }
                 // everything issued so far has to retire (in both CTAs) before TMEM is released
                 umma2_commit(&bar->mma_done);
+                PROF_OUT(0, clock64() - t_start); PROF_OUT(1, w_qrot); PROF_OUT(2, w_sfree); PROF_OUT(3, w_kfull); PROF_OUT(4, w_pready);
+                PROF_OUT(5, w_ofree); PROF_OUT(6, w_vfull); PROF_OUT(7, n_blocks); PROF_OUT(18, t_iqk); PROF_OUT(19, t_ipv);
             }
             __syncwarp();
         } else {
             // =========================== RoPE of this CTA's Q tiles; tells the leader they are ready ===========================
-            // 2 warps; warp w owns rows [64w, 64w+64) of each tile.  A step handles two rows: lane l takes 16-byte
+            // 2 warps; warp w owns rows [64w, 64w+64) of the tile.  A step handles two rows: lane l takes 16-byte
             // chunk (l & 15) of row 2*step + (l >> 4).  Without RoPE the warps only forward "tile landed".
             const int rw = warp - kRopeWarp0;
             const int c = lane & 15;
@@ -423,124 +457,120 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
             float step_c[4], step_s[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) sincosf(2.0f * p.inv_freq.v[(c * 4 + e) & (kMaxHalfDim - 1)], &step_s[e], &step_c[e]);
-            uint32_t q_rot_leader[kQBufs];
-#pragma unroll
-            for (int b = 0; b < kQBufs; ++b) q_rot_leader[b] = map_to_cta(smem_u32(&bar->q_rot[b]), 0);
-            int q_seq = 0;
+            const uint32_t q_rot_leader = map_to_cta(smem_u32(&bar->q_rot[0]), 0);     // the barriers of one kind are contiguous
             bool ok = true;
-            for (int round = 0; round < n_rounds && ok; ++round) {
-                const int idx = item_of_round(round, n_items, cluster_id, n_clusters);
-                if (idx < 0) continue;
-                const Item w = get_item(p, idx, n_cols, n_rows, cta);
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    if (!ok) continue;
-                    const int b = q_seq % kQBufs, ph = (q_seq / kQBufs) & 1;
-                    ++q_seq;
-                    ok = mbar_wait_warp(&bar->q_full[b], ph, abort_flag, 0x700 + b);
-                    if (!ok) continue;
-                    if (rope) {
-                        unsigned char* qtile = q_smem + b * kTileBytes + (c >> 3) * kBoxBytes;
-                        const int r_first = rw * 64 + (lane >> 4);
-                        // rows past T hold zeros: rotating them is harmless; their table row is clamped
-                        if constexpr (kExactRope) {
+            BlockCursor it;
+            it.init(p, n_rounds, n_items, cluster_id, n_clusters, n_cols, n_rows, cta);
+            for (; it.valid && ok; it.next_item(p)) {
+                const Item& w = it.w;
+                const int b = it.item_no % kQBufs, ph = (it.item_no / kQBufs) & 1;
+                ok = WAIT_OFFPATH_WARP(&bar->q_full[b], ph, abort_flag, 0x700 + b);
+                if (!ok) break;
+                if (rope) {
+                    unsigned char* qtile = q_smem + b * kTileBytes + (c >> 3) * kBoxBytes;
+                    const int r_first = rw * 64 + (lane >> 4);
+                    // rows past T hold zeros: rotating them is harmless; their table row is clamped
+                    if constexpr (kExactRope) {
 #pragma unroll 2
-                            for (int st = 0; st < 32; ++st) {
-                                const int r = r_first + 2 * st;
-                                const int rowx = min(w.r0[t] + r, p.T - 1);
-                                const float4* tabx = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(rowx) * (kD / 2)) + c * 2;
-                                const float4 a0 = __ldg(tabx), a1 = __ldg(tabx + 1);
-                                const float csx[4] = {a0.x, a0.z, a1.x, a1.z}, snx[4] = {a0.y, a0.w, a1.y, a1.w};
+                        for (int st = 0; st < 32; ++st) {
+                            const int r = r_first + 2 * st;
+                            const int rowx = min(w.r0 + r, p.T - 1);
+                            const float4* tabx = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(rowx) * (kD / 2)) + c * 2;
+                            const float4 a0 = __ldg(tabx), a1 = __ldg(tabx + 1);
+                            const float csx[4] = {a0.x, a0.z, a1.x, a1.z}, snx[4] = {a0.y, a0.w, a1.y, a1.w};
+                            uint4* ptr = reinterpret_cast<uint4*>(qtile + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+                            uint4 raw = *ptr;
+                            uint32_t* u = &raw.x;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 x = Elem<T>::unpack2(u[e]);
+                                const float t1 = __fmul_rn(x.x, csx[e]), t2 = __fmul_rn(x.y, snx[e]);
+                                const float t3 = __fmul_rn(x.x, snx[e]), t4 = __fmul_rn(x.y, csx[e]);
+                                u[e] = Elem<T>::pack2(__fsub_rn(t1, t2), __fadd_rn(t3, t4));
+                            }
+                            *ptr = raw;
+                        }
+                    } else {
+                        float4 seed0, seed1;
+                        {
+                            const int row = min(w.r0 + r_first, p.T - 1);
+                            const float4* tab = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(row) * (kD / 2)) + c * 2;
+                            seed0 = __ldg(tab); seed1 = __ldg(tab + 1);
+                        }
+#pragma unroll 1
+                        for (int s0 = 0; s0 < 32; s0 += kRopeSeed) {
+                            float cs[4] = {seed0.x, seed0.z, seed1.x, seed1.z};
+                            float sn[4] = {seed0.y, seed0.w, seed1.y, seed1.w};
+                            if (s0 + kRopeSeed < 32) {             // prefetch the next exact seed
+                                const int row = min(w.r0 + r_first + 2 * (s0 + kRopeSeed), p.T - 1);
+                                const float4* tab = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(row) * (kD / 2)) + c * 2;
+                                seed0 = __ldg(tab); seed1 = __ldg(tab + 1);
+                            }
+#pragma unroll
+                            for (int i = 0; i < kRopeSeed; ++i) {
+                                const int r = r_first + 2 * (s0 + i);
                                 uint4* ptr = reinterpret_cast<uint4*>(qtile + r * 128 + (((c & 7) ^ (r & 7)) << 4));
                                 uint4 raw = *ptr;
                                 uint32_t* u = &raw.x;
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
                                     const float2 x = Elem<T>::unpack2(u[e]);
-                                    const float t1 = __fmul_rn(x.x, csx[e]), t2 = __fmul_rn(x.y, snx[e]);
-                                    const float t3 = __fmul_rn(x.x, snx[e]), t4 = __fmul_rn(x.y, csx[e]);
+                                    const float t1 = __fmul_rn(x.x, cs[e]), t2 = __fmul_rn(x.y, sn[e]);
+                                    const float t3 = __fmul_rn(x.x, sn[e]), t4 = __fmul_rn(x.y, cs[e]);
                                     u[e] = Elem<T>::pack2(__fsub_rn(t1, t2), __fadd_rn(t3, t4));
+                                    // advance this pair's angle by two positions
+                                    const float cn = fmaf(cs[e], step_c[e], -sn[e] * step_s[e]);
+                                    sn[e] = fmaf(sn[e], step_c[e], cs[e] * step_s[e]);
+                                    cs[e] = cn;
                                 }
                                 *ptr = raw;
                             }
-                        } else {
-                            float4 seed0, seed1;
-                            {
-                                const int row = min(w.r0[t] + r_first, p.T - 1);
-                                const float4* tab = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(row) * (kD / 2)) + c * 2;
-                                seed0 = __ldg(tab); seed1 = __ldg(tab + 1);
-                            }
-#pragma unroll 1
-                            for (int s0 = 0; s0 < 32; s0 += kRopeSeed) {
-                                float cs[4] = {seed0.x, seed0.z, seed1.x, seed1.z};
-                                float sn[4] = {seed0.y, seed0.w, seed1.y, seed1.w};
-                                if (s0 + kRopeSeed < 32) {             // prefetch the next exact seed
-                                    const int row = min(w.r0[t] + r_first + 2 * (s0 + kRopeSeed), p.T - 1);
-                                    const float4* tab = reinterpret_cast<const float4*>(p.q_rope_table + static_cast<long long>(row) * (kD / 2)) + c * 2;
-                                    seed0 = __ldg(tab); seed1 = __ldg(tab + 1);
-                                }
-#pragma unroll
-                                for (int i = 0; i < kRopeSeed; ++i) {
-                                    const int r = r_first + 2 * (s0 + i);
-                                    uint4* ptr = reinterpret_cast<uint4*>(qtile + r * 128 + (((c & 7) ^ (r & 7)) << 4));
-                                    uint4 raw = *ptr;
-                                    uint32_t* u = &raw.x;
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e) {
-                                        const float2 x = Elem<T>::unpack2(u[e]);
-                                        const float t1 = __fmul_rn(x.x, cs[e]), t2 = __fmul_rn(x.y, sn[e]);
-                                        const float t3 = __fmul_rn(x.x, sn[e]), t4 = __fmul_rn(x.y, cs[e]);
-                                        u[e] = Elem<T>::pack2(__fsub_rn(t1, t2), __fadd_rn(t3, t4));
-                                        // advance this pair's angle by two positions
-                                        const float cn = fmaf(cs[e], step_c[e], -sn[e] * step_s[e]);
-                                        sn[e] = fmaf(sn[e], step_c[e], cs[e] * step_s[e]);
-                                        cs[e] = cn;
-                                    }
-                                    *ptr = raw;
-                                }
-                            }
                         }
                     }
-                    fence_proxy_async_smem();            // generic-proxy writes -> visible to the tensor core's smem reads
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(q_rot_leader[b]);
                 }
+                fence_proxy_async_smem();            // generic-proxy writes -> visible to the tensor core's smem reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster_release(q_rot_leader + 8 * b);
             }
         }
-    } else {
-        // =========================== softmax / correction / epilogue ===========================
+    } else if (warp < 4) {
+        // =========================== softmax (and the rare rescale of O) ===========================
         reg_inc<kRegSoftmax>();
-        const int t = warp >> 2;                     // tile of this warpgroup
-        const int r = tid & 127;                     // row inside the tile = TMEM lane
-        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const uint32_t s_addr = tmem_base + lane_base + static_cast<uint32_t>(t * 128);
-        const uint32_t o_addr = tmem_base + lane_base + static_cast<uint32_t>(256 + t * 128);
+        const int r = tid;                           // row inside the tile = TMEM lane
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t o_addr = tmem_base + lane_base + 256;
         const float scale_log2 = p.scale * kLog2e;
-        const uint32_t p_ready_leader = map_to_cta(smem_u32(&bar->p_ready[t]), 0);
-        unsigned char* stage = o_smem + t * kTileBytes;
-        int g = 0;                                   // running count of score tiles of this tile index
+        const uint32_t s_free_leader = map_to_cta(smem_u32(&bar->s_free[0]), 0);
+        const uint32_t p_ready_leader = map_to_cta(smem_u32(&bar->p_ready[0]), 0);
         bool ok = true;
-        bool store_pending = false;                  // thread 0 of the warpgroup: a TMA store may still be reading `stage`
-        int epi_phase = 0;                           // items whose epilogue this warpgroup has run
-
-        for (int round = 0; round < n_rounds && ok; ++round) {
-            const int idx = item_of_round(round, n_items, cluster_id, n_clusters);
-            if (idx < 0) continue;
-            const Item w = get_item(p, idx, n_cols, n_rows, cta);
-            const int n = w.n;
-            const int tile_r0 = w.r0[t];
+        PROF_DECL(w_sfull); PROF_DECL(w_pvdone); PROF_DECL(t_ld); PROF_DECL(t_math); PROF_DECL(w_stat); PROF_DECL(n_resc);
+        PROF_DECL(t_max); PROF_DECL(t_exp); PROF_DECL(t_st);
+        PROF_T0(t_start);
+        BlockCursor it;
+        it.init(p, n_rounds, n_items, cluster_id, n_clusters, n_cols, n_rows, cta);
+        while (it.valid && ok) {
+            const int n = it.w.n, tile_r0 = it.w.r0, item_no = it.item_no;
             const int row = tile_r0 + r;             // query row; >= T for padding rows (computed on zeros, never stored)
-
             float m_ref = -INFINITY, l_sum = 0.f;
-            for (int j = 0; j < n; ++j, ++g) {
-                ok = mbar_wait_warp(&bar->s_full[t], g & 1, abort_flag, 0x800 + t);
+            for (int j = 0; j < n; ++j) {
+                const int g = it.g + j, b = g & 1;
+                const uint32_t s_addr = tmem_base + lane_base + static_cast<uint32_t>(b * 128);
+                const uint32_t p_addr = tmem_base + lane_base + static_cast<uint32_t>(384 + b * 64);
+                { PROF_T0(t0); ok = mbar_wait_warp(&bar->s_full[b], (g >> 1) & 1, abort_flag, 0x800 + b); PROF_ADD(w_sfull, t0); }
                 if (!ok) break;
+                PROF_T0(t_blk);
                 tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
                 tmem_ld_wait();
+                PROF_ADD(t_ld, t_blk);
+                // the scores are in registers: the product of block g + 2 may overwrite S[b]
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(s_free_leader + 8 * b);
 
+#ifndef VBP_NOSOFTMAX
                 const int k0 = j * kBlockN;
                 const bool need_mask = (k0 + kBlockN > p.Skv) || (p.causal && (k0 + kBlockN - 1 > p.start_pos + tile_r0));
                 if (need_mask) {
@@ -561,14 +591,18 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                         mx8[(i >> 1) & 7] = fmaxf(mx8[(i >> 1) & 7], fmaxf(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
                 const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
                 const float m_cand = mx * scale_log2;
-                // a block this row sees nothing of (it belongs to a longer tile of the item) has m_cand = -inf: no growth
+                PROF_ADD(t_max, t_blk);
+                // a block this row sees nothing of (it belongs to the longer tile of the item) has m_cand = -inf: no growth
                 const bool grow = m_cand > m_ref + kRescaleThreshold;      // true on the first block of an item
                 if (__any_sync(0xFFFFFFFFu, grow)) {
                     const float m_new = grow ? m_cand : m_ref;
                     const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
                     if (j > 0) {
-                        // all PV products issued so far for this tile must have landed in O
-                        ok = mbar_wait_warp(&bar->o_done[t], (g - 1) & 1, abort_flag, 0x900 + t);
+#ifdef VBP_PROF
+                        ++n_resc;
+#endif
+                        // every product of this item issued so far (the last one read P of block g - 1) must have landed in O
+                        ok = mbar_wait_warp(&bar->pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag, 0x900);
                         if (!ok) break;
                         tc_fence_after();
 #pragma unroll
@@ -585,7 +619,16 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                     l_sum *= alpha;
                     m_ref = m_new;
                 }
+                // P[b] was last read by the product of block g - 2
+                if (g >= 2) {
+                    PROF_T0(t0);
+                    ok = mbar_wait_warp(&bar->pv_done[b], ((g >> 1) - 1) & 1, abort_flag, 0x910);
+                    PROF_ADD(w_pvdone, t0);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
                 // p = 2^(s*scale*log2e - m_ref); packed to 16 bit two per column
+                PROF_T0(t_e0);
                 float2 rs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
                 const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_ref, -m_ref);
 #pragma unroll
@@ -602,36 +645,83 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                             pk[cc * 16 + (i >> 1)] = Elem<T>::pack2(pp.x, pp.y);
                         }
                     }
-                    tmem_st32(s_addr + half * 32, pk);
+                    tmem_st32(p_addr + half * 32, pk);
                 }
                 l_sum += ((rs[0].x + rs[0].y) + (rs[1].x + rs[1].y)) + ((rs[2].x + rs[2].y) + (rs[3].x + rs[3].y));
+                PROF_ADD(t_exp, t_e0);
+#else
+                if (g >= 2) { ok = mbar_wait_warp(&bar->pv_done[b], ((g >> 1) - 1) & 1, abort_flag, 0x910); if (!ok) break; }
+                m_ref = 0.f; l_sum = 1.f; (void)s; (void)p_addr; (void)o_addr; (void)row; (void)scale_log2;
+#endif
+                PROF_T0(t_s0);
                 tmem_st_wait();
                 tc_fence_before();
-                // The staging tile of this warpgroup is written again in this item's epilogue, which every row enters
-                // only after the product that this (last) hand-over releases: the thread that issued the previous
-                // item's store makes sure, before handing over, that the store has finished reading the tile.
-                if (j + 1 == n && r == 0 && store_pending) { bulk_wait_read0(); store_pending = false; }
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(p_ready_leader);
+                if (lane == 0) mbar_arrive_cluster(p_ready_leader + 8 * b);
+                PROF_ADD(t_st, t_s0);
+                PROF_ADD(t_math, t_blk);
             }
             if (!ok) break;
-
-            // ---- epilogue of this item: O / l -> staging tile in shared memory -> TMA store; LSE ----
-            ok = mbar_wait_warp(&bar->o_done[t], (g - 1) & 1, abort_flag, 0xA00 + t);
+            // hand (m, l) of the finished item to the epilogue warpgroup and go straight on to the next item
+            // (the epilogue warpgroup read the previous item's pair a whole item ago)
+            { PROF_T0(t0); if (item_no >= 1) ok = mbar_wait_warp(&bar->stat_free, (item_no - 1) & 1, abort_flag, 0x920); PROF_ADD(w_stat, t0); }
+            if (!ok) break;
+            stats[r] = make_float2(m_ref, l_sum);
+            mbar_arrive(&bar->stat_full);
+            it.next_item(p);
+        }
+        if (tid == 0) {
+            PROF_OUT(8, clock64() - t_start); PROF_OUT(9, w_sfull); PROF_OUT(10, w_pvdone); PROF_OUT(11, t_ld); PROF_OUT(12, t_math); PROF_OUT(13, w_stat); PROF_OUT(14, n_resc); PROF_OUT(15, t_max); PROF_OUT(16, t_exp); PROF_OUT(17, t_st);
+        }
+    } else {
+        // =========================== epilogue of finished items: O / l -> staging tile -> TMA store; LSE ===========================
+        const int r = tid - 128;                     // row inside the tile = TMEM lane
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t o_addr = tmem_base + lane_base + 256;
+        const uint32_t o_free_leader = map_to_cta(smem_u32(&bar->o_free), 0);
+        unsigned char* stage = o_smem;
+        bool ok = true;
+        bool store_pending = false;                  // thread 0 of the warpgroup: a TMA store may still be reading `stage`
+        BlockCursor it;
+        it.init(p, n_rounds, n_items, cluster_id, n_clusters, n_cols, n_rows, cta);
+        for (; it.valid && ok; it.next_item(p)) {
+            const Item& w = it.w;
+            const int item_no = it.item_no;
+            const int g_last = it.g + w.n - 1;
+            const int row = w.r0 + r;
+            const bool present = w.r0 < p.T;
+            ok = WAIT_OFFPATH_WARP(&bar->stat_full, item_no & 1, abort_flag, 0xA00);
+            if (!ok) break;
+            const float2 st = stats[r];
+            mbar_arrive(&bar->stat_free);
+            // the item's last product has landed in O
+            ok = mbar_wait_warp(&bar->pv_done[g_last & 1], (g_last >> 1) & 1, abort_flag, 0xA10);
             if (!ok) break;
             tc_fence_after();
-            const float inv_l = 1.0f / l_sum;
-            const bool present = tile_r0 < p.T;
+            // the previous item's store must have finished reading the staging tile
+            if (r == 0) {
+                if (store_pending) { bulk_wait_read0(); store_pending = false; }
+                mbar_arrive(&bar->stage_free);
+            }
+            ok = mbar_wait_warp(&bar->stage_free, item_no & 1, abort_flag, 0xA20);
+            if (!ok) break;
+            const float inv_l = 1.0f / st.y;
 #pragma unroll
-            for (int c = 0; c < kD / 32; c += 2) {
+            for (int half = 0; half < 2; ++half) {
                 uint32_t o[2][32];
-                tmem_ld32(o_addr + c * 32, o[0]);
-                tmem_ld32(o_addr + (c + 1) * 32, o[1]);
+                tmem_ld32(o_addr + (2 * half) * 32, o[0]);
+                tmem_ld32(o_addr + (2 * half + 1) * 32, o[1]);
                 tmem_ld_wait();
+                if (half == 1) {
+                    // all of O is in registers (or already staged): the next item's first product may overwrite it
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(o_free_leader);
+                }
+                // 64 columns = one [128 rows][64 cols] box of the staging tile; 16-byte chunk h2 * 4 + v of this row
+                unsigned char* box = stage + half * kBoxBytes + r * 128;
 #pragma unroll
-                for (int h2 = 0; h2 < 2; ++h2) {
-                    // 32 columns = four 16-byte chunks of this row; chunk index inside its 64-column box: ((c + h2) & 1) * 4 + v
-                    unsigned char* box = stage + ((c + h2) >> 1) * kBoxBytes + r * 128;
+                for (int h2 = 0; h2 < 2; ++h2)
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
                         uint4 out;
@@ -639,28 +729,23 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                         out.y = Elem<T>::pack2(__uint_as_float(o[h2][8 * v + 2]) * inv_l, __uint_as_float(o[h2][8 * v + 3]) * inv_l);
                         out.z = Elem<T>::pack2(__uint_as_float(o[h2][8 * v + 4]) * inv_l, __uint_as_float(o[h2][8 * v + 5]) * inv_l);
                         out.w = Elem<T>::pack2(__uint_as_float(o[h2][8 * v + 6]) * inv_l, __uint_as_float(o[h2][8 * v + 7]) * inv_l);
-                        const int chunk = ((c + h2) & 1) * 4 + v;
+                        const int chunk = h2 * 4 + v;
                         *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = out;
                     }
-                }
             }
-            // O has been read out of TMEM: the next item's first PV (issued only after this thread's next P hand-over)
-            // may overwrite it
-            tc_fence_before();
             fence_proxy_async_smem();                // this row of the staging tile -> visible to the TMA store
-            mbar_arrive(&bar->epi_done[t]);
+            mbar_arrive(&bar->epi_done);
             if (r == 0) {
                 // only the issuing thread waits for the other rows (bounded like every wait)
-                if (mbar_wait(&bar->epi_done[t], epi_phase & 1, abort_flag, 0xB00 + t) && present) {
-                    tma_store_4d(&maps.o, stage, 0, tile_r0, w.hq[t], w.b);
-                    tma_store_4d(&maps.o, stage + kBoxBytes, 64, tile_r0, w.hq[t], w.b);
+                if (mbar_wait(&bar->epi_done, item_no & 1, abort_flag, 0xB00) && present) {
+                    tma_store_4d(&maps.o, stage, 0, w.r0, w.hq, w.b);
+                    tma_store_4d(&maps.o, stage + kBoxBytes, 64, w.r0, w.hq, w.b);
                     bulk_commit();
                     store_pending = true;
                 }
             }
-            ++epi_phase;
             if (p.lse != nullptr && present && row < p.T)
-                p.lse[(static_cast<long long>(w.b) * p.Hq + w.hq[t]) * p.T + row] = (m_ref + fast_log2(l_sum)) * kLn2;
+                p.lse[(static_cast<long long>(w.b) * p.Hq + w.hq) * p.T + row] = (st.x + fast_log2(st.y)) * kLn2;
         }
         if (r == 0 && store_pending) bulk_wait0();   // the staging tile must outlive the store's reads
     }
@@ -776,6 +861,12 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
 }
 
 }  // namespace
+
+#ifdef VBP_PROF
+extern "C" int vb200_debug_read_pair_prof(long long* host, int n) {
+    return cudaMemcpyFromSymbol(host, g_pair_prof, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
+}
+#endif
 
 // head_dim 128, bf16 / fp16.  The caller (launch_prefill_sm100) keeps the single-CTA kernel for head_dim 64.
 int launch_prefill_pair_sm100(cudaStream_t s, const PrefillParams& p) {

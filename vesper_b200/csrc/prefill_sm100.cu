@@ -646,11 +646,7 @@ static bool use_pair_kernel(const PrefillParams& p) {
         return (e[0] == 'p' || e[0] == 'P') ? 1 : 0;
     }();
     if (p.D != 128) return false;
-    if (forced >= 0) return forced == 1;
-    const int n_rep = p.Hq / p.Hkv;
-    if (n_rep % 4 == 0) return true;
-    if (n_rep % 2 == 0) return p.T > kBlockM;
-    return p.T > 3 * kBlockM;
+    return forced == 1;      // the single-CTA kernel is the faster one at every measured shape; the pair kernel is opt-in
 }
 
 int launch_prefill_sm100(cudaStream_t s, const PrefillParams& p) {

@@ -125,6 +125,77 @@ __global__ void kv_append_kernel(int B, int H, int Tn, int D, View4 k, View4 v, 
     }
 }
 
+// The angle table and the K rotation + cache append of a prompt pass in ONE launch.  A CTA owns kRopeRows consecutive
+// positions: it computes their (cos, sin) once (accurate sincosf of the reference's fp32 angle), keeps them in shared
+// memory, writes them to the table the attention kernel rotates Q with (only the CTAs of the first (batch, head) chunk
+// do), and moves those rows of K (rotated) and V (copied) for its chunk of (batch, head) pairs -- one table kernel, one
+// launch gap and one trip of the table through L2 less than table-then-append.
+constexpr int kRopeRows = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(256) rope_append_fused_kernel(int B, int H, int Tn, int D, View4 k, View4 v, View4 kd, View4 vd, int dst_row0,
+                                                                float2* __restrict__ table, InvFreq f, int bh_per_cta) {
+    __shared__ float2 cs[kRopeRows][kMaxHalfDim];
+    const int half = D / 2, vecs = D / 8;
+    const int t0 = blockIdx.x * kRopeRows;
+    const int rows = min(kRopeRows, Tn - t0);
+    for (int i = threadIdx.x; i < rows * half; i += blockDim.x) {
+        const int r = i / half, pr = i - r * half;
+        float sn, c;
+        sincosf(__int2float_rn(dst_row0 + t0 + r) * f.v[pr], &sn, &c);       // int -> float, one fp32 multiply: the reference's pos * freq
+        cs[r][pr] = make_float2(c, sn);
+        if (blockIdx.y == 0 && table != nullptr) table[static_cast<long long>(t0 + r) * half + pr] = make_float2(c, sn);
+    }
+    __syncthreads();
+    const int bh0 = blockIdx.y * bh_per_cta;
+    const int nbh = min(bh_per_cta, B * H - bh0);
+    const int per_bh = rows * vecs;
+    for (int i = threadIdx.x; i < nbh * per_bh; i += blockDim.x) {
+        const int bh = bh0 + i / per_bh, rem = i % per_bh;
+        const int r = rem / vecs, c = rem - r * vecs;
+        const int b = bh / H, h = bh - b * H, t = t0 + r;
+        const T* kp = static_cast<const T*>(k.ptr) + b * k.sb + h * k.sh + static_cast<long long>(t) * k.ss + c * 8;
+        T* kdp = static_cast<T*>(kd.ptr) + b * kd.sb + h * kd.sh + static_cast<long long>(dst_row0 + t) * kd.ss + c * 8;
+        Vec8<T> x;
+        x.load(kp);
+        float e[8];
+        x.get(e);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) rotate_pair(e[2 * j], e[2 * j + 1], cs[r][c * 4 + j]);
+        x.set(e);
+        x.store(kdp);
+        if (v.ptr != nullptr) {
+            const T* vp = static_cast<const T*>(v.ptr) + b * v.sb + h * v.sh + static_cast<long long>(t) * v.ss + c * 8;
+            T* vdp = static_cast<T*>(vd.ptr) + b * vd.sb + h * vd.sh + static_cast<long long>(dst_row0 + t) * vd.ss + c * 8;
+            Vec8<T> y;
+            y.load(vp);
+            y.store(vdp);
+        }
+    }
+}
+
+int launch_rope_append_fused(cudaStream_t s, int dtype, int B, int H, int T, int D, View4 k, View4 v, View4 k_dst, View4 v_dst,
+                             int dst_row0, float2* table, const InvFreq& f) {
+    if (T <= 0 || B * H <= 0) return VB200_OK;
+    const int row_tiles = (T + kRopeRows - 1) / kRopeRows;
+    // enough CTAs for about two per SM; every extra (batch, head) chunk repeats the sincosf of its rows
+    int chunks = (296 + row_tiles - 1) / row_tiles;
+    if (chunks > B * H) chunks = B * H;
+    if (chunks < 1) chunks = 1;
+    const int bh_per_cta = (B * H + chunks - 1) / chunks;
+    chunks = (B * H + bh_per_cta - 1) / bh_per_cta;
+    dim3 grid(static_cast<unsigned>(row_tiles), static_cast<unsigned>(chunks));
+    switch (dtype) {
+        case VB200_F32: rope_append_fused_kernel<float><<<grid, 256, 0, s>>>(B, H, T, D, k, v, k_dst, v_dst, dst_row0, table, f, bh_per_cta); break;
+        case VB200_BF16: rope_append_fused_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(B, H, T, D, k, v, k_dst, v_dst, dst_row0, table, f, bh_per_cta); break;
+        case VB200_F16: rope_append_fused_kernel<__half><<<grid, 256, 0, s>>>(B, H, T, D, k, v, k_dst, v_dst, dst_row0, table, f, bh_per_cta); break;
+        default: return VB200_ERR_UNSUPPORTED;
+    }
+    note_launch();
+    VB200_CUDA_TRY(cudaPeekAtLastError());
+    return VB200_OK;
+}
+
 int launch_kv_append(cudaStream_t s, int dtype, int B, int H, int T, int D,
                      View4 k, View4 v, View4 k_dst, View4 v_dst, int dst_row0, const float2* table,
                      const InvFreq* inv_freq) {

@@ -210,8 +210,8 @@ Tensor fused_attention(const Tensor& q, const Tensor& k, const Tensor& v, KVCach
         throw std::runtime_error("attention: the output view must have q's shape and dtype with contiguous head_dim");
     if (cache && cache->k().dtype() != q.dtype()) throw std::runtime_error("attention: the KV cache must have the dtype of q, k, v");
     Tensor out = out_view ? *out_view : empty(q.shape(), q.dtype(), Device::CUDA);
-    const int n_rep = Hq / Hkv;
-    const bool fast_decode = cache && T == 1 && D == 128 && q.dtype() != DType::Float32 && (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 8);
+    // one new token per sequence: the split-KV decode path, whatever the dtype, head_dim and group size
+    const bool fast_decode = cache && T == 1 && D % 8 == 0;
     if (fast_decode) {
         vb200_decode_args d{};
         d.struct_size = sizeof(d);
@@ -273,9 +273,7 @@ Tensor scaled_dot_product_attention(const Tensor& query, const Tensor& key, cons
     Tensor out = empty(query.shape(), query.dtype(), Device::CUDA);
     const int B = static_cast<int>(query.shape()[0]), Hq = static_cast<int>(query.shape()[1]), Hkv = static_cast<int>(key.shape()[1]);
     if (Hq % Hkv != 0) throw std::runtime_error("scaled_dot_product_attention: query heads must be a multiple of key heads");
-    const int n_rep = Hq / Hkv;
-    if (T == 1 && !is_causal && D == 128 && query.dtype() != DType::Float32 && key.strides()[2] == D && value.strides()[2] == D &&
-        (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 8)) {
+    if (T == 1 && D % 8 == 0) {                                  // (with one query row the causal flag changes nothing)
         // one query row per head: the split-KV kernel, no append, no rotation
         vb200_decode_args d{};
         d.struct_size = sizeof(d);

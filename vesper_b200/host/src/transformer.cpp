@@ -250,7 +250,7 @@ void TransformerLM::run_blocks(int64_t B, int64_t T, int64_t start_pos, bool dev
         consume(b.xn.data_ptr<char>(), L.wqkv, qkv, qkv_n, qkv_n, VB200_EPI_BF16, "linear(wqkv)");
         const vb200_tensor4 kc{cache.k().data_ptr<char>(), cache.k().strides()[0], cache.k().strides()[1], cache.k().strides()[2]};
         const vb200_tensor4 vc{cache.v().data_ptr<char>(), cache.v().strides()[0], cache.v().strides()[1], cache.v().strides()[2]};
-        if (T == 1 && D == 128) {
+        if (T == 1) {                        // one new token per sequence: the split-KV decode path (tuned for head_dim 128)
             vb200_decode_args d{};
             d.struct_size = sizeof(d);
             d.device = dev; d.stream = s; d.dtype = VB200_BF16;
@@ -271,7 +271,7 @@ void TransformerLM::run_blocks(int64_t B, int64_t T, int64_t start_pos, bool dev
             d.workspace_bytes = b.attn_ws.numel() * 4;
             check(vb200_decode_fwd(&d), "attention(decode)");
         } else {
-            if (device_positions) throw std::runtime_error("TransformerLM: device-side positions need head_dim 128 and one token per sequence");
+            if (device_positions) throw std::runtime_error("TransformerLM: device-side positions need one token per sequence");
             vb200_prefill_args a{};
             a.struct_size = sizeof(a);
             a.device = dev; a.stream = s; a.dtype = VB200_BF16;

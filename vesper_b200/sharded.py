@@ -128,19 +128,30 @@ class PeerExchange:
         from . import capi
         return capi.exchange_combine(partial, self.ptrs, self.rank, out, lse, timeout_cycles=timeout_cycles, stream=stream)
 
+    def supports_one_launch(self, B, Hq, Hkv):
+        """Whether vb200_decode_exchange_fwd takes this shape (else: decode call + combine())."""
+        return Hq % Hkv == 0 and Hq // Hkv in (4, 8) and B * Hkv <= 64
+
 
 def cuda_step(step: ShardedDecodeStep, q, k_shard, v_shard, *, scale, theta, partial_buf, out, lse=None,
-              gathered=None, workspace=None, dist=None, stream=None, exchange: PeerExchange | None = None, qpos=None):
+              gathered=None, workspace=None, dist=None, stream=None, exchange: PeerExchange | None = None, qpos=None,
+              one_launch=False):
     """GPU implementation of one step on this rank.  ``k_shard``/``v_shard`` hold rows
     [begin, end) of the sequence; ``q`` is the unrotated query [B,Hq,1,D] (replicated).
-    With ``exchange`` the partial records travel and merge in one peer-memory kernel; without it
-    they go through a host-supervised all-gather followed by ``vb200_lse_combine``."""
+    With ``exchange`` the partial records travel and merge in one peer-memory kernel -- with ``one_launch`` as the
+    tail of the decode kernel itself (vb200_decode_exchange_fwd); without ``exchange`` they go through a
+    host-supervised all-gather followed by ``vb200_lse_combine``."""
     import torch
     from . import capi
     begin, end = shard_range(step.context_len, step.world, step.rank)
     B, Hq, _, D = q.shape
     if qpos is None:
         qpos = torch.full((B,), step.context_len, dtype=torch.int32, device=q.device)
+    if exchange is not None and one_launch:
+        capi.decode_exchange(q, k_shard, v_shard, exchange.ptrs, exchange.rank, out, lse, scale=scale, theta=theta,
+                             uniform_len=end - begin, max_len=end - begin, pos_offset=begin, q_positions=qpos,
+                             workspace=workspace, stream=stream)
+        return out
     if step.world == 1 and exchange is None:
         # one shard: nothing to exchange or merge, the decode call writes the result itself
         capi.decode(q, out.view(B, Hq, 1, D), k_shard, v_shard, scale=scale, theta=theta, uniform_len=end - begin, max_len=end - begin,
