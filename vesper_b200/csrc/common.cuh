@@ -169,38 +169,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     }
 }
 
-// The same wait for roles that are off the critical path (a producer ahead of its consumers, an epilogue waiting for
-// a whole work item): between polls the thread sleeps, so that its warp leaves the issue slots of its SM
-// sub-partition to the warps that compute.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where, unsigned sleep_ns = 200) {
-    uint32_t addr = smem_u32(bar);
-    uint32_t ok = 0;
-    long long t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-        if (ok) return true;
-        __nanosleep(sleep_ns);
-        if ((it & 0x3F) == 0x3F) {
-            if (*ctx.abort_flag) return false;
-            long long now = clock64();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitCycles) {
-                *ctx.abort_flag = 1;
-                atomicCAS(ctx.status, 0, (1 << 24) | where);
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ bool mbar_wait_relaxed_warp(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where, unsigned sleep_ns = 200) {
-    bool ok = mbar_wait_relaxed(bar, parity, ctx, where, sleep_ns);
-    return __all_sync(0xFFFFFFFFu, ok);
-}
-
 // Same, for code that follows the wait with warp-collective instructions
 // (tcgen05.ld/st are .sync.aligned): the outcome is made warp-uniform.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where) {

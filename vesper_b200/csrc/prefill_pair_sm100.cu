@@ -31,6 +31,12 @@
 // remote mbarrier arrivals -- and signals back with tcgen05.commit multicast to the same barrier in both CTAs.
 //
 // Every wait is bounded (mbar_wait); on expiry the CTA drains and returns with the device status word set.
+//
+// Status: correct (same parity suite as the single-CTA kernel) and selectable with VB200_PREFILL_KERNEL=pair, but
+// NOT the default: with one query tile per SM there is one softmax warpgroup per SM, and one warp per SM
+// sub-partition cannot overlap its row-maximum and exponential phases (about 1450 cycles per 128x128 block at best,
+// against 1100 for two warpgroups that interleave on the MUFU), so the kernel is softmax-bound at a lower rate than
+// the single-CTA kernel, whose two tiles per SM keep two softmax warpgroups busy.
 #include <cstdio>
 
 #include "kernels.h"
@@ -82,20 +88,6 @@ struct __align__(8) Barriers {
 struct PairMaps {
     CUtensorMap q, k, v, o;
 };
-
-#ifdef VBP_PROF
-// development build only: per-CTA cycle counters, [cta][slot]
-__device__ long long g_pair_prof[160 * 32];
-#define PROF_DECL(name) long long name = 0
-#define PROF_T0(v) const long long v = clock64()
-#define PROF_ADD(acc, t0) acc += clock64() - (t0)
-#define PROF_OUT(slot, val) g_pair_prof[blockIdx.x * 32 + (slot)] = (val)
-#else
-#define PROF_DECL(name)
-#define PROF_T0(v)
-#define PROF_ADD(acc, t0)
-#define PROF_OUT(slot, val)
-#endif
 
 // How the two tiles of an item are laid over (head, row tile): two heads of a group (an even number of query
 // heads per KV head), else two adjacent row tiles of one head.
@@ -169,14 +161,6 @@ __device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_add
 }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-
-#ifdef VBP_BACKOFF
-#define WAIT_OFFPATH mbar_wait_relaxed
-#define WAIT_OFFPATH_WARP mbar_wait_relaxed_warp
-#else
-#define WAIT_OFFPATH mbar_wait
-#define WAIT_OFFPATH_WARP mbar_wait_warp
-#endif
 
 // 4-D tiled TMA load whose completion bytes go to a barrier that may live in the peer CTA (`bar_cluster_addr` is a
 // shared::cluster address); the destination is this CTA's own shared memory.  No multicast.
@@ -325,7 +309,7 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                 auto load_q = [&](const BlockCursor& c) {
                     if (!ok || !c.valid || c.item_no <= q_loaded) return;
                     const int b = c.item_no % kQBufs, use = c.item_no / kQBufs;
-                    if (use > 0) ok = WAIT_OFFPATH(&bar->q_free[b], (use - 1) & 1, abort_flag, 0x110 + b);
+                    if (use > 0) ok = mbar_wait(&bar->q_free[b], (use - 1) & 1, abort_flag, 0x110 + b);
                     if (!ok) return;
                     q_loaded = c.item_no;
                     mbar_arrive_expect_tx(&bar->q_full[b], kTileBytes);
@@ -336,7 +320,7 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                 auto load_half = [&](const BlockCursor& c, bool is_v) {
                     if (!ok) return;
                     const int slot = kv_item % kStages;
-                    if (kv_item >= kStages) ok = WAIT_OFFPATH(&bar->kv_empty[slot], ((kv_item / kStages) - 1) & 1, abort_flag, 0x100);
+                    if (kv_item >= kStages) ok = mbar_wait(&bar->kv_empty[slot], ((kv_item / kStages) - 1) & 1, abort_flag, 0x100);
                     if (!ok) return;
                     ++kv_item;
                     // the leader's barrier collects the bytes of both CTAs' halves
@@ -377,21 +361,18 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                 const uint32_t tmem_o = tmem_base + 256;
                 int kv_item = 0;
                 bool ok = true;
-                PROF_DECL(w_qrot); PROF_DECL(w_sfree); PROF_DECL(w_kfull); PROF_DECL(w_pready); PROF_DECL(w_ofree); PROF_DECL(w_vfull); PROF_DECL(n_blocks); PROF_DECL(t_iqk); PROF_DECL(t_ipv);
-                PROF_T0(t_start);
                 // S[g & 1] = Q K(block)^T for the block the cursor stands on
                 auto issue_qk = [&](const BlockCursor& c) {
                     if (!ok) return;
                     const int qbuf = c.item_no % kQBufs;
-                    { PROF_T0(t0); if (c.j == 0) ok = mbar_wait(&bar->q_rot[qbuf], (c.item_no / kQBufs) & 1, abort_flag, 0x210); PROF_ADD(w_qrot, t0); }
+                    if (c.j == 0) ok = mbar_wait(&bar->q_rot[qbuf], (c.item_no / kQBufs) & 1, abort_flag, 0x210);
                     // S[g & 1] was last used by block g - 2: both softmax warpgroups must have read it
-                    { PROF_T0(t0); if (ok && c.g >= 2) ok = mbar_wait(&bar->s_free[c.g & 1], ((c.g >> 1) - 1) & 1, abort_flag, 0x220); PROF_ADD(w_sfree, t0); }
+                    if (ok && c.g >= 2) ok = mbar_wait(&bar->s_free[c.g & 1], ((c.g >> 1) - 1) & 1, abort_flag, 0x220);
                     const int slot = kv_item % kStages;
-                    { PROF_T0(t0); if (ok) ok = mbar_wait(&bar->kv_full[slot], (kv_item / kStages) & 1, abort_flag, 0x200); PROF_ADD(w_kfull, t0); }
+                    if (ok) ok = mbar_wait(&bar->kv_full[slot], (kv_item / kStages) & 1, abort_flag, 0x200);
                     if (!ok) return;
                     ++kv_item;
                     tc_fence_after();
-                    PROF_T0(t_i0);
                     const uint32_t d = tmem_base + static_cast<uint32_t>((c.g & 1) * 128);
                     const uint64_t a0 = desc_q0 + static_cast<uint64_t>(qbuf * (kTileBytes >> 4));
                     const uint64_t b0 = desc_k0 + static_cast<uint64_t>(slot * (kSlotBytes >> 4));
@@ -405,7 +386,6 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                     umma2_commit(&bar->s_full[c.g & 1]);
                     umma2_commit(&bar->kv_empty[slot]);
                     if (c.j + 1 == c.w.n) umma2_commit(&bar->q_free[qbuf]);          // last QK of the item
-                    PROF_ADD(t_iqk, t_i0);
                 };
                 BlockCursor qk, pv;
                 qk.init(p, n_rounds, n_items, cluster_id, n_clusters, n_cols, n_rows, 0);
@@ -416,18 +396,14 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                     if (!ok) break;
                     // O += P[g & 1] V(block)
                     const int b = pv.g & 1;
-                    { PROF_T0(t0); ok = mbar_wait(&bar->p_ready[b], (pv.g >> 1) & 1, abort_flag, 0x400); PROF_ADD(w_pready, t0); }
+                    ok = mbar_wait(&bar->p_ready[b], (pv.g >> 1) & 1, abort_flag, 0x400);
                     // the first product of an item overwrites O: the previous item's O must have been drained
-                    { PROF_T0(t0); if (ok && pv.j == 0 && pv.item_no > 0) ok = mbar_wait(&bar->o_free, (pv.item_no - 1) & 1, abort_flag, 0x410); PROF_ADD(w_ofree, t0); }
+                    if (ok && pv.j == 0 && pv.item_no > 0) ok = mbar_wait(&bar->o_free, (pv.item_no - 1) & 1, abort_flag, 0x410);
                     const int slot = kv_item % kStages;
-                    { PROF_T0(t0); if (ok) ok = mbar_wait(&bar->kv_full[slot], (kv_item / kStages) & 1, abort_flag, 0x300); PROF_ADD(w_vfull, t0); }
+                    if (ok) ok = mbar_wait(&bar->kv_full[slot], (kv_item / kStages) & 1, abort_flag, 0x300);
                     if (!ok) break;
-#ifdef VBP_PROF
-                    ++n_blocks;
-#endif
                     ++kv_item;
                     tc_fence_after();
-                    PROF_T0(t_i1);
                     const uint32_t a_tmem = tmem_base + static_cast<uint32_t>(384 + b * 64);
                     const uint64_t v0 = desc_v0 + static_cast<uint64_t>(slot * (kSlotBytes >> 4));
                     const uint32_t acc0 = pv.j > 0 ? 1u : 0u;
@@ -438,13 +414,10 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                     }
                     umma2_commit(&bar->pv_done[b]);
                     umma2_commit(&bar->kv_empty[slot]);
-                    PROF_ADD(t_ipv, t_i1);
                     pv.next(p);
                 }
                 // everything issued so far has to retire (in both CTAs) before TMEM is released
                 umma2_commit(&bar->mma_done);
-                PROF_OUT(0, clock64() - t_start); PROF_OUT(1, w_qrot); PROF_OUT(2, w_sfree); PROF_OUT(3, w_kfull); PROF_OUT(4, w_pready);
-                PROF_OUT(5, w_ofree); PROF_OUT(6, w_vfull); PROF_OUT(7, n_blocks); PROF_OUT(18, t_iqk); PROF_OUT(19, t_ipv);
             }
             __syncwarp();
         } else {
@@ -464,7 +437,7 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
             for (; it.valid && ok; it.next_item(p)) {
                 const Item& w = it.w;
                 const int b = it.item_no % kQBufs, ph = (it.item_no / kQBufs) & 1;
-                ok = WAIT_OFFPATH_WARP(&bar->q_full[b], ph, abort_flag, 0x700 + b);
+                ok = mbar_wait_warp(&bar->q_full[b], ph, abort_flag, 0x700 + b);
                 if (!ok) break;
                 if (rope) {
                     unsigned char* qtile = q_smem + b * kTileBytes + (c >> 3) * kBoxBytes;
@@ -543,9 +516,6 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
         const uint32_t s_free_leader = map_to_cta(smem_u32(&bar->s_free[0]), 0);
         const uint32_t p_ready_leader = map_to_cta(smem_u32(&bar->p_ready[0]), 0);
         bool ok = true;
-        PROF_DECL(w_sfull); PROF_DECL(w_pvdone); PROF_DECL(t_ld); PROF_DECL(t_math); PROF_DECL(w_stat); PROF_DECL(n_resc);
-        PROF_DECL(t_max); PROF_DECL(t_exp); PROF_DECL(t_st);
-        PROF_T0(t_start);
         BlockCursor it;
         it.init(p, n_rounds, n_items, cluster_id, n_clusters, n_cols, n_rows, cta);
         while (it.valid && ok) {
@@ -556,21 +526,18 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                 const int g = it.g + j, b = g & 1;
                 const uint32_t s_addr = tmem_base + lane_base + static_cast<uint32_t>(b * 128);
                 const uint32_t p_addr = tmem_base + lane_base + static_cast<uint32_t>(384 + b * 64);
-                { PROF_T0(t0); ok = mbar_wait_warp(&bar->s_full[b], (g >> 1) & 1, abort_flag, 0x800 + b); PROF_ADD(w_sfull, t0); }
+                ok = mbar_wait_warp(&bar->s_full[b], (g >> 1) & 1, abort_flag, 0x800 + b);
                 if (!ok) break;
-                PROF_T0(t_blk);
                 tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
                 tmem_ld_wait();
-                PROF_ADD(t_ld, t_blk);
                 // the scores are in registers: the product of block g + 2 may overwrite S[b]
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(s_free_leader + 8 * b);
 
-#ifndef VBP_NOSOFTMAX
                 const int k0 = j * kBlockN;
                 const bool need_mask = (k0 + kBlockN > p.Skv) || (p.causal && (k0 + kBlockN - 1 > p.start_pos + tile_r0));
                 if (need_mask) {
@@ -591,16 +558,12 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                         mx8[(i >> 1) & 7] = fmaxf(mx8[(i >> 1) & 7], fmaxf(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
                 const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
                 const float m_cand = mx * scale_log2;
-                PROF_ADD(t_max, t_blk);
                 // a block this row sees nothing of (it belongs to the longer tile of the item) has m_cand = -inf: no growth
                 const bool grow = m_cand > m_ref + kRescaleThreshold;      // true on the first block of an item
                 if (__any_sync(0xFFFFFFFFu, grow)) {
                     const float m_new = grow ? m_cand : m_ref;
                     const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
                     if (j > 0) {
-#ifdef VBP_PROF
-                        ++n_resc;
-#endif
                         // every product of this item issued so far (the last one read P of block g - 1) must have landed in O
                         ok = mbar_wait_warp(&bar->pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag, 0x900);
                         if (!ok) break;
@@ -621,14 +584,11 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                 }
                 // P[b] was last read by the product of block g - 2
                 if (g >= 2) {
-                    PROF_T0(t0);
                     ok = mbar_wait_warp(&bar->pv_done[b], ((g >> 1) - 1) & 1, abort_flag, 0x910);
-                    PROF_ADD(w_pvdone, t0);
                     if (!ok) break;
                     tc_fence_after();
                 }
                 // p = 2^(s*scale*log2e - m_ref); packed to 16 bit two per column
-                PROF_T0(t_e0);
                 float2 rs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
                 const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_ref, -m_ref);
 #pragma unroll
@@ -648,30 +608,19 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
                     tmem_st32(p_addr + half * 32, pk);
                 }
                 l_sum += ((rs[0].x + rs[0].y) + (rs[1].x + rs[1].y)) + ((rs[2].x + rs[2].y) + (rs[3].x + rs[3].y));
-                PROF_ADD(t_exp, t_e0);
-#else
-                if (g >= 2) { ok = mbar_wait_warp(&bar->pv_done[b], ((g >> 1) - 1) & 1, abort_flag, 0x910); if (!ok) break; }
-                m_ref = 0.f; l_sum = 1.f; (void)s; (void)p_addr; (void)o_addr; (void)row; (void)scale_log2;
-#endif
-                PROF_T0(t_s0);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(p_ready_leader + 8 * b);
-                PROF_ADD(t_st, t_s0);
-                PROF_ADD(t_math, t_blk);
             }
             if (!ok) break;
             // hand (m, l) of the finished item to the epilogue warpgroup and go straight on to the next item
             // (the epilogue warpgroup read the previous item's pair a whole item ago)
-            { PROF_T0(t0); if (item_no >= 1) ok = mbar_wait_warp(&bar->stat_free, (item_no - 1) & 1, abort_flag, 0x920); PROF_ADD(w_stat, t0); }
+            if (item_no >= 1) ok = mbar_wait_warp(&bar->stat_free, (item_no - 1) & 1, abort_flag, 0x920);
             if (!ok) break;
             stats[r] = make_float2(m_ref, l_sum);
             mbar_arrive(&bar->stat_full);
             it.next_item(p);
-        }
-        if (tid == 0) {
-            PROF_OUT(8, clock64() - t_start); PROF_OUT(9, w_sfull); PROF_OUT(10, w_pvdone); PROF_OUT(11, t_ld); PROF_OUT(12, t_math); PROF_OUT(13, w_stat); PROF_OUT(14, n_resc); PROF_OUT(15, t_max); PROF_OUT(16, t_exp); PROF_OUT(17, t_st);
         }
     } else {
         // =========================== epilogue of finished items: O / l -> staging tile -> TMA store; LSE ===========================
@@ -690,7 +639,7 @@ prefill_pair_kernel(const __grid_constant__ PairMaps maps, PrefillParams p) {
             const int g_last = it.g + w.n - 1;
             const int row = w.r0 + r;
             const bool present = w.r0 < p.T;
-            ok = WAIT_OFFPATH_WARP(&bar->stat_full, item_no & 1, abort_flag, 0xA00);
+            ok = mbar_wait_warp(&bar->stat_full, item_no & 1, abort_flag, 0xA00);
             if (!ok) break;
             const float2 st = stats[r];
             mbar_arrive(&bar->stat_free);
@@ -861,12 +810,6 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
 }
 
 }  // namespace
-
-#ifdef VBP_PROF
-extern "C" int vb200_debug_read_pair_prof(long long* host, int n) {
-    return cudaMemcpyFromSymbol(host, g_pair_prof, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
-}
-#endif
 
 // head_dim 128, bf16 / fp16.  The caller (launch_prefill_sm100) keeps the single-CTA kernel for head_dim 64.
 int launch_prefill_pair_sm100(cudaStream_t s, const PrefillParams& p) {
