@@ -156,7 +156,10 @@ int sm_count() {
     return cache[dev];
 }
 
-DecodePlan plan_decode(const vb200_decode_args* a) {
+// `waves`: CTAs per SM the split count aims at (4 = two waves of two resident CTAs; the one-launch sharded step asks
+// for 1: one CTA per SM, so that the last CTA of a group finds few enough partial records to merge them from shared
+// memory in one round).
+DecodePlan plan_decode(const vb200_decode_args* a, int waves = 4) {
     DecodePlan pl{};
     const int tile = decode_tile_keys();
     int max_total = (a->max_len > 0 ? a->max_len : a->cache_cap);
@@ -169,7 +172,7 @@ DecodePlan plan_decode(const vb200_decode_args* a) {
         // more than 512 keys per CTA so ragged batches balance (one common length needs no such cap:
         // longer chunks spend less of a CTA's life in its prologue and merge)
         long long units = static_cast<long long>(a->B) * a->Hkv;
-        const long long ctas = 2LL * 2 * sm_count();
+        const long long ctas = static_cast<long long>(waves) * sm_count();
         int want = static_cast<int>((ctas + units - 1) / units);
         chunk = (max_total + want - 1) / want;
         if (chunk > 512 && a->seq_lens) chunk = 512;
@@ -410,7 +413,7 @@ int decode_impl(const vb200_decode_args* a, const vb200_exchange_args* x) {
     if (int rc = validate_decode(a)) return rc;
     if (!x && !a->o.ptr && !a->partial_out) return set_detail(VB200_ERR_INVALID_ARG, "o or partial_out must be given");
     if (a->D % 8 != 0 || a->D > 128) return set_detail(VB200_ERR_UNSUPPORTED, "head_dim must be a multiple of 8 and <= 128");
-    DecodePlan pl = plan_decode(a);
+    DecodePlan pl = plan_decode(a, x ? 1 : 4);
     if (!a->workspace || a->workspace_bytes < pl.total) return set_detail(VB200_ERR_WORKSPACE, "decode workspace too small (see vb200_decode_workspace_bytes)");
     if (reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0) return set_detail(VB200_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
     DeviceGuard g;
@@ -447,6 +450,7 @@ int decode_impl(const vb200_decode_args* a, const vb200_exchange_args* x) {
         if (int rc = fill_exchange(p.xchg, x, "vb200_decode_exchange_fwd")) return rc;
         if (x->rows != static_cast<int64_t>(a->B) * a->Hq || x->D != a->D || x->dtype != a->dtype)
             return set_detail(VB200_ERR_INVALID_ARG, "vb200_decode_exchange_fwd: the exchange must carry B * Hq rows of head_dim D in the decode dtype");
+        if (pl.num_splits > 1024) return set_detail(VB200_ERR_UNSUPPORTED, "vb200_decode_exchange_fwd: at most 1024 splits");
         if (static_cast<int64_t>(a->B) * a->Hkv > 64)
             return set_detail(VB200_ERR_UNSUPPORTED, "vb200_decode_exchange_fwd: at most 64 (batch, kv_head) groups; use vb200_decode_fwd + vb200_exchange_combine");
         if (p.seq_lens && p.advance_lens && p.append)

@@ -36,9 +36,13 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 // (the online-softmax recurrence of src/ops/flash_attention.cpp:309-345 across shards).  `sync` synchronises the
 // kNT participating threads (tid in [0, kNT)); s_step / s_ok are shared-memory scratch words.  On expiry the
 // output is left untouched and the status word names the rank that never arrived.
+// `scratch` (shared memory, 16-byte aligned, `scratch_floats` long; may be null): when all ranks' rows of this CTA fit,
+// they are fetched there in one round of asynchronous copies and merged from shared memory instead of in two dependent
+// rounds of L2 loads per row (needs r0 * (D + 2) * 4 and rows * (D + 2) * 4 to be multiples of 16 bytes).
 template <typename T, int kNT, typename Sync>
 __device__ __forceinline__ void exchange_rows(const ExchangeParams& p, int c, long long r0, long long r1, const float* src,
-                                              int tid, uint32_t* s_step, int* s_ok, Sync sync) {
+                                              int tid, uint32_t* s_step, int* s_ok, Sync sync,
+                                              float* scratch = nullptr, int scratch_floats = 0) {
     const int W = p.world, D = p.D, rec = p.D + 2;
     char* self = static_cast<char*>(p.peers[p.rank]);
     uint32_t* counter = reinterpret_cast<uint32_t*>(self) + c;
@@ -57,7 +61,9 @@ __device__ __forceinline__ void exchange_rows(const ExchangeParams& p, int c, lo
                       (static_cast<size_t>(parity) * W + p.rank) * slot_floats / 2 + r0 * rec / 2;
         for (long long i = tid; i < n2; i += kNT) dst[i] = src2[i];
     }
-    __threadfence_system();
+    // all threads' peer stores, then the CTA barrier, then the release store of the flag by a few threads: the release
+    // is cumulative over what the barrier ordered before it, so no thread needs a system-wide fence of its own
+    // (measured at ~5 us per call when all 128 threads issued one)
     sync();
     if (tid < W) {
         uint32_t* flag = reinterpret_cast<uint32_t*>(static_cast<char*>(p.peers[tid]) + kXFlagBase) +
@@ -84,25 +90,65 @@ __device__ __forceinline__ void exchange_rows(const ExchangeParams& p, int c, lo
     if (tid == 0) *counter = step;
     if (!*s_ok) return;
 
-    // ---- merge ----
+    // ---- merge: one warp per row (rows of the CTA dealt round-robin), a lane owns dim pairs lane, lane + 32, ... ----
+    // Two dependent rounds of L2 loads per row (the maxima, then everything else), all ranks' loads of a round in flight
+    // together: the merge is latency-bound, so the rounds are what counts.
     const float* slots = reinterpret_cast<const float*>(self + kXSlotBase) + static_cast<size_t>(parity) * W * slot_floats;
-    for (long long row = r0; row < r1; ++row) {
+    const int warp = tid >> 5, lane = tid & 31;
+    const int nrows = static_cast<int>(r1 - r0);
+    const int row_floats = nrows * rec;
+    if (scratch != nullptr && static_cast<long long>(W) * row_floats <= scratch_floats && (row_floats % 4) == 0 &&
+        ((r0 * rec) % 4) == 0 && (slot_floats % 4) == 0) {
+        const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(scratch));
+        const int per_rank = row_floats / 4;                            // 16-byte pieces per rank
+        for (int i = tid; i < W * per_rank; i += kNT) {
+            const int r = i / per_rank, j = i % per_rank;
+            const float4* g = reinterpret_cast<const float4*>(slots + r * slot_floats + r0 * rec) + j;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + i * 16), "l"(g) : "memory");
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        sync();
+        for (int rr = warp; rr < nrows; rr += kNT / 32) {
+            const float* base = scratch + rr * rec;                     // rank r's copy of the row: base + r * row_floats
+            float M = -INFINITY;
+            for (int r = 0; r < W; ++r) M = fmaxf(M, base[r * row_floats + D]);
+            float L = 0.f;
+            for (int d2 = lane; d2 < D / 2; d2 += 32) {
+                float2 acc = make_float2(0.f, 0.f);
+                float l = 0.f;
+                for (int r = 0; r < W; ++r) {
+                    const float2 ml = *reinterpret_cast<const float2*>(base + r * row_floats + D);
+                    const float2 o = reinterpret_cast<const float2*>(base + r * row_floats)[d2];
+                    const float w = (ml.x == -INFINITY) ? 0.f : expf(ml.x - M) * ml.y;
+                    l += w;
+                    acc.x += w * o.x; acc.y += w * o.y;
+                }
+                L = l;
+                reinterpret_cast<uint32_t*>(static_cast<T*>(p.out) + (r0 + rr) * D)[d2] = Elem<T>::pack2(acc.x / l, acc.y / l);
+            }
+            if (p.lse && lane == 0) p.lse[r0 + rr] = M + logf(L);
+        }
+        return;
+    }
+    for (long long row = r0 + warp; row < r1; row += kNT / 32) {
         const float* base = slots + row * rec;
         float M = -INFINITY;
         for (int r = 0; r < W; ++r) M = fmaxf(M, __ldcg(base + r * slot_floats + D));
         float L = 0.f;
-        for (int d = tid; d < D; d += kNT) {
-            float acc = 0.f, l = 0.f;
+        for (int d2 = lane; d2 < D / 2; d2 += 32) {
+            float2 acc = make_float2(0.f, 0.f);
+            float l = 0.f;
             for (int r = 0; r < W; ++r) {
-                const float mr = __ldcg(base + r * slot_floats + D);
-                const float w = (mr == -INFINITY) ? 0.f : expf(mr - M) * __ldcg(base + r * slot_floats + D + 1);
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + r * slot_floats + D));
+                const float2 o = __ldcg(reinterpret_cast<const float2*>(base + r * slot_floats) + d2);
+                const float w = (ml.x == -INFINITY) ? 0.f : expf(ml.x - M) * ml.y;
                 l += w;
-                acc += w * __ldcg(base + r * slot_floats + d);
+                acc.x += w * o.x; acc.y += w * o.y;
             }
             L = l;
-            static_cast<T*>(p.out)[row * D + d] = Elem<T>::from_f(acc / l);
+            reinterpret_cast<uint32_t*>(static_cast<T*>(p.out) + row * D)[d2] = Elem<T>::pack2(acc.x / l, acc.y / l);
         }
-        if (p.lse && tid == 0) p.lse[row] = M + logf(L);         // thread 0 ran d = 0, so L holds the row's l*
+        if (p.lse && lane == 0) p.lse[row] = M + logf(L);        // lane 0 ran d2 = 0, so L holds the row's l*
     }
 }
 #endif  // __CUDACC__

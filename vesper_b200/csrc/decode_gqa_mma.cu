@@ -371,9 +371,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa_mma_kernel(con
     __shared__ int s_ok;
     const int unit = b * p.Hkv + kvh;
     const int nvalid = min((total + p.chunk - 1) / p.chunk, p.num_splits);
-    __threadfence();                                          // this CTA's rows before its ticket
+    // every thread's rows, then (cumulatively, through the CTA barrier) one thread's fence, before the ticket
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
     if (tid == 0) {
+        __threadfence();
         int* ticket = reinterpret_cast<int*>(static_cast<char*>(p.xchg.peers[p.xchg.rank]) + kXTicketBase) + unit;
         const int t = atomicAdd(ticket, 1);
         s_last = (t == nvalid - 1) ? 1 : 0;
@@ -382,40 +383,100 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa_mma_kernel(con
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
     if (!s_last) return;
     __threadfence();
+    constexpr int kRec2 = (D + 2) / 2, kBlk2 = NREP * kRec2, kNT = CW * 32;
+    constexpr int kRingBytes = kStages * kStageBytes;
+    constexpr int kRecBytes = NREP * (D + 2) * 4, kMiscBytes = 128;
+    // splits staged per round: their records (kBlk2 float2 each) and one weight per (head, split) must fit behind rec
+    constexpr int kStageCap = ((kRingBytes - kRecBytes - kMiscBytes) / (kBlk2 * 8 + NREP * 4)) & ~3;
+    static_assert(kStageCap >= 8 && (NREP * kStageCap * 4) % 16 == 0 && kRecBytes % 16 == 0, "staging layout");
+    float* sm_run = rec + NREP * (D + 2);                     // [0,8) running max, [8,16) running sum, [16,24) rescale factor per head
+    float* sm_w = sm_run + kMiscBytes / 4;                    // [NREP][kStageCap] merge weights of the staged splits
+    float2* stage2 = reinterpret_cast<float2*>(sm_w + NREP * kStageCap);
     {
-        // warp w merges heads w, w + CW, ...; lane l owns dims 4l .. 4l+3.  Rows come from L2 (written by other CTAs).
-        const float* grp = p.workspace + p.ws_header + (static_cast<long long>(unit) * p.num_splits) * NREP * (D + 2);
-        for (int h = warp; h < NREP; h += CW) {
-            const float* rows = grp + h * (D + 2);
-            const long long sstride = static_cast<long long>(NREP) * (D + 2);
-            float M = -INFINITY;
-            for (int sidx = lane; sidx < nvalid; sidx += 32) M = fmaxf(M, __ldcg(rows + sidx * sstride + D));
+        // Merge of the group's splits by all 128 threads.  A split's records of the NREP heads are one contiguous
+        // block of NREP * (D + 2) floats, viewed as float2 columns: column h * 65 + i (i < 64) holds dims 2i, 2i + 1
+        // of head h, column h * 65 + 64 its (m, l).  The rows come from L2, written by other CTAs, at a time when the
+        // other groups still stream their keys: a dependent round of loads costs ~2500 cycles, so the records of as many
+        // splits as fit (all of them, for the split counts this path plans) are brought into the now idle K/V ring
+        // by 16-byte asynchronous copies -- no registers held, every copy in flight at once -- and merged from there;
+        // further rounds fold in with the usual rescale.
+        constexpr int kCols = (kBlk2 + kNT - 1) / kNT;
+        const float2* grp2 = reinterpret_cast<const float2*>(p.workspace + p.ws_header + (static_cast<long long>(unit) * p.num_splits) * NREP * (D + 2));
+        float2 acc[kCols];
+        int col[kCols], head[kCols];
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            float L = 0.f;
-#pragma unroll 8
-            for (int sidx = 0; sidx < nvalid; ++sidx) {
-                const float* row = rows + sidx * sstride;
-                const float ms = __ldcg(row + D);
-                const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - M) * __ldcg(row + D + 1);
-                // a record is D + 2 = 130 floats long: its rows are 8-byte, not 16-byte, aligned
-                const float2 oa = __ldcg(reinterpret_cast<const float2*>(row) + 2 * lane);
-                const float2 ob = __ldcg(reinterpret_cast<const float2*>(row) + 2 * lane + 1);
-                L += wgt;
-                acc.x += wgt * oa.x; acc.y += wgt * oa.y; acc.z += wgt * ob.x; acc.w += wgt * ob.y;
-            }
-            const float inv = (nvalid > 0 && L > 0.f) ? 1.0f / L : 0.f;
-            float* out = rec + h * (D + 2);
-            *reinterpret_cast<float2*>(out + 4 * lane) = make_float2(acc.x * inv, acc.y * inv);
-            *reinterpret_cast<float2*>(out + 4 * lane + 2) = make_float2(acc.z * inv, acc.w * inv);
-            if (lane == 0) { out[D] = M; out[D + 1] = L; }
+        for (int k = 0; k < kCols; ++k) {
+            acc[k] = make_float2(0.f, 0.f);
+            const int c = tid + k * kNT;
+            const bool use = c < kBlk2 && (c % kRec2) != D / 2;
+            col[k] = use ? c : -1;
+            head[k] = use ? c / kRec2 : 0;
         }
+        if (tid < NREP) { sm_run[tid] = -INFINITY; sm_run[8 + tid] = 0.f; }
+        const uint32_t stage_addr = smem_u32(stage2);
+        for (int s0 = 0; s0 < nvalid; s0 += kStageCap) {
+            const int n = min(kStageCap, nvalid - s0);
+            const float4* src4 = reinterpret_cast<const float4*>(grp2 + static_cast<long long>(s0) * kBlk2);
+            for (int i = tid; i < n * (kBlk2 / 2); i += kNT)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage_addr + i * 16), "l"(src4 + i) : "memory");
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kNT) : "memory");
+            for (int h = warp; h < NREP; h += CW) {
+                float Mc = -INFINITY;
+                for (int u = lane; u < n; u += 32) Mc = fmaxf(Mc, stage2[u * kBlk2 + h * kRec2 + D / 2].x);
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) Mc = fmaxf(Mc, __shfl_xor_sync(0xFFFFFFFFu, Mc, o));
+                const float Mold = sm_run[h], Mnew = fmaxf(Mold, Mc);
+                float Lc = 0.f;
+                for (int u = lane; u < n; u += 32) {
+                    const float2 ml = stage2[u * kBlk2 + h * kRec2 + D / 2];
+                    const float wgt = (ml.x == -INFINITY) ? 0.f : expf(ml.x - Mnew) * ml.y;
+                    sm_w[h * kStageCap + u] = wgt;
+                    Lc += wgt;
+                }
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) Lc += __shfl_xor_sync(0xFFFFFFFFu, Lc, o);
+                __syncwarp();
+                if (lane == 0) {
+                    const float keep = (Mold == -INFINITY) ? 0.f : expf(Mold - Mnew);
+                    sm_run[16 + h] = keep;
+                    sm_run[8 + h] = sm_run[8 + h] * keep + Lc;
+                    sm_run[h] = Mnew;
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kNT) : "memory");
+#pragma unroll
+            for (int k = 0; k < kCols; ++k) {
+                const float keep = sm_run[16 + head[k]];
+                acc[k].x *= keep; acc[k].y *= keep;
+            }
+            for (int u = 0; u < n; ++u) {
+#pragma unroll
+                for (int k = 0; k < kCols; ++k)
+                    if (col[k] >= 0) {
+                        const float wgt = sm_w[head[k] * kStageCap + u];
+                        const float2 v = stage2[u * kBlk2 + col[k]];
+                        acc[k].x += wgt * v.x;
+                        acc[k].y += wgt * v.y;
+                    }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kNT) : "memory");      // the round is consumed before the next one lands
+        }
+#pragma unroll
+        for (int k = 0; k < kCols; ++k)
+            if (col[k] >= 0) {
+                const float L = sm_run[8 + head[k]];
+                const float inv = L > 0.f ? 1.0f / L : 0.f;
+                reinterpret_cast<float2*>(rec)[col[k]] = make_float2(acc[k].x * inv, acc[k].y * inv);
+            }
+        if (tid < NREP) { rec[tid * (D + 2) + D] = sm_run[tid]; rec[tid * (D + 2) + D + 1] = sm_run[8 + tid]; }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
     const long long r0 = static_cast<long long>(b) * p.Hq + static_cast<long long>(kvh) * NREP;
+    // (the staging area is free again: the peers' rows of this group land there for the final merge)
     exchange_rows<T, CW * 32>(p.xchg, unit, r0, r0 + NREP, rec, tid, &s_step, &s_ok,
-                              [] { asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory"); });
+                              [] { asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory"); },
+                              reinterpret_cast<float*>(stage2), kStageCap * kBlk2 * 2);
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -492,3 +553,4 @@ template int launch_decode_gqa_mma_split<__nv_bfloat16, 4>(cudaStream_t, const D
 template int launch_decode_gqa_mma_split<__half, 4>(cudaStream_t, const DecodeParams&);
 
 }  // namespace vb200
+
