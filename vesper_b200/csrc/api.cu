@@ -173,7 +173,9 @@ DecodePlan plan_decode(const vb200_decode_args* a, int waves = 4) {
         // longer chunks spend less of a CTA's life in its prologue and merge)
         long long units = static_cast<long long>(a->B) * a->Hkv;
         const long long ctas = static_cast<long long>(waves) * sm_count();
-        int want = static_cast<int>((ctas + units - 1) / units);
+        // (one wave: rounded down, so that no SM gets a second CTA -- it would finish last, at twice the time)
+        int want = waves == 1 ? static_cast<int>(ctas / units) : static_cast<int>((ctas + units - 1) / units);
+        if (want < 1) want = 1;
         chunk = (max_total + want - 1) / want;
         if (chunk > 512 && a->seq_lens) chunk = 512;
         // short contexts: at most 16 splits, so that they can run as one cluster that merges its own partials
