@@ -400,7 +400,7 @@ def bench_prefill(cx, K, W, quick=False):
         "value": cx.world * flops / (ms_per_step * 1e-3) / 1e12, "ms_per_step": ms_per_step, "gpu_launches": launches,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tf"], "unit": "TFLOP/s", "frac": achieved / pk["tf"],
                      "peak_source": pk["source"] + " (burst cuBLAS bf16)", "frac_of_sustained": achieved / pk["tf_sustained"],
-                     "frac_of_nominal_2250": achieved / 2250.0, "kernel": "prefill_sm100_kernel", "kernel_ms": kern_avg_ms,
+                     "frac_of_nominal_2250": achieved / 2250.0, "kernel": L.vb200_last_prefill_kernel().decode(), "kernel_ms": kern_avg_ms,
                      "traffic": cx.traffic.get("prefill_sm100_bytes_per_launch")},
         "e2e": {"value": cx.world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "value_per_gpu": flops / (e2e_ms * 1e-3) / 1e12,
                 "host_placement": placement,

@@ -314,6 +314,10 @@ int vb200_abi_version(void);
  * the last reset (used by the benchmark's launch count). */
 uint64_t vb200_launch_count(void);
 void vb200_reset_launch_count(void);
+/* Name of the attention kernel the calling thread's last vb200_prefill_fwd launched ("prefill_sm100_kernel",
+ * "prefill_pair_kernel", "prefill_f32_kernel"; "" before the first call): which of the kernels a shape, a dtype or the
+ * VB200_PREFILL_KERNEL switch selected, for reports and tests. */
+const char* vb200_last_prefill_kernel(void);
 /* Optional timing of the dominant kernel of each call (the attention kernel of
  * vb200_prefill_fwd, the split-KV kernel of vb200_decode_fwd), for roofline
  * reports: while enabled, the launch is bracketed by two CUDA events on the

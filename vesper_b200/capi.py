@@ -55,7 +55,7 @@ EXPORTS = [
     "vb200_attention_bwd_workspace_bytes", "vb200_attention_bwd",
     "vb200_lse_combine", "vb200_kv_append", "vb200_apply_rope", "vb200_repeat_kv", "vb200_rope_inv_freq",
     "vb200_strerror", "vb200_last_error_detail", "vb200_abi_version", "vb200_launch_count",
-    "vb200_reset_launch_count", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
+    "vb200_reset_launch_count", "vb200_last_prefill_kernel", "vb200_check_kernel_status", "vb200_profile_enable", "vb200_profile_read",
 ]
 BLOCK_EXPORTS = [
     "vb200_linear", "vb200_linear_bias", "vb200_linear_f32", "vb200_linear_ex", "vb200_row_inv_rms", "vb200_embedding_scaled", "vb200_linear_add_rmsnorm", "vb200_embedding_rmsnorm", "vb200_interleave_rows", "vb200_rms_norm", "vb200_silu_mul", "vb200_embedding", "vb200_greedy_step",
@@ -138,6 +138,7 @@ def load():
     L.vb200_strerror.restype = C.c_char_p
     L.vb200_last_error_detail.restype = C.c_char_p
     L.vb200_launch_count.restype = C.c_uint64
+    L.vb200_last_prefill_kernel.restype = C.c_char_p
     L.vb200_reset_launch_count.restype = None
     L.vb200_check_kernel_status.argtypes = [C.c_int, C.c_void_p]
     L.vb200_profile_enable.argtypes = [C.c_int]

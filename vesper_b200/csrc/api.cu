@@ -28,9 +28,11 @@ int* kernel_status_word() {
 namespace {
 thread_local std::string t_detail;
 thread_local uint64_t t_launches = 0;
+thread_local const char* t_prefill_kernel = "";
 }  // namespace
 
 void note_launch(int n) { t_launches += static_cast<uint64_t>(n); }
+void note_prefill_kernel(const char* name) { t_prefill_kernel = name; }
 
 namespace {
 struct ProfileState {
@@ -240,6 +242,7 @@ const char* vb200_strerror(int status) {
 
 const char* vb200_last_error_detail(void) { return t_detail.c_str(); }
 uint64_t vb200_launch_count(void) { return t_launches; }
+const char* vb200_last_prefill_kernel(void) { return t_prefill_kernel; }
 void vb200_reset_launch_count(void) { t_launches = 0; }
 
 void vb200_rope_inv_freq(float theta, int32_t D, float* inv_freq_host) {

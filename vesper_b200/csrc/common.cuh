@@ -16,6 +16,7 @@ namespace vb200 {
 // host-side bookkeeping (api.cu owns the definitions)
 // ---------------------------------------------------------------------------
 void note_launch(int n = 1);
+void note_prefill_kernel(const char* name);     // static string: the attention kernel a prefill call launched
 int cuda_fail(cudaError_t e, const char* what);   // records detail, returns VB200_ERR_CUDA
 int set_detail(int status, const char* msg);      // records detail, returns status
 // Optional timing of the dominant kernel of a call (vb200_profile_enable): the

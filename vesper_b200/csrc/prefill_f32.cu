@@ -214,6 +214,7 @@ int launch_prefill_f32(cudaStream_t s, const PrefillParams& p) {
     dim3 grid((p.T + kBM - 1) / kBM, p.Hq, p.B);
     prefill_f32_kernel<<<grid, kThreads, smem, s>>>(p);
     note_launch();
+    note_prefill_kernel("prefill_f32_kernel");
     VB200_CUDA_TRY(cudaPeekAtLastError());
     return VB200_OK;
 }

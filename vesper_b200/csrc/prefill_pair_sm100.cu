@@ -805,6 +805,7 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
     VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, cached_maps, p));
     profile_mark_end(s);
     note_launch();
+    note_prefill_kernel("prefill_pair_kernel");
     VB200_CUDA_TRY(cudaPeekAtLastError());
     return VB200_OK;
 }

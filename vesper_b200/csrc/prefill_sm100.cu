@@ -628,6 +628,7 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
     prefill_sm100_kernel<T, D, kExactRope><<<grid, kThreads, Cfg<D>::kSmemBytes, s>>>(maps, p);
     profile_mark_end(s);
     note_launch();
+    note_prefill_kernel("prefill_sm100_kernel");
     VB200_CUDA_TRY(cudaPeekAtLastError());
     return VB200_OK;
 }
