@@ -522,9 +522,27 @@ int launch_decode_gqa_mma_split(cudaStream_t s, const DecodeParams& p) {
     constexpr int CW = 4, kStages = 3, MINB = 2;
     constexpr size_t smem = static_cast<size_t>(kStages) * 4 * kBoxBytes + 128 * 4 + 128 * 2 + sizeof(MmaSmem<CW, kStages>) + 1024;
     static_assert(CW * NREP * 128 * 4 + 2 * CW * NREP * 4 <= kStages * 4 * kBoxBytes, "merge buffers must fit in the ring");
-    KvMaps maps;
-    if (int rc = make_kv_map(&maps.k, p.dtype, p.k_cache, p.cache_cap, p.Hkv, p.B)) return rc;
-    if (int rc = make_kv_map(&maps.v, p.dtype, p.v_cache, p.cache_cap, p.Hkv, p.B)) return rc;
+    // the maps of this thread's last call, reused while the cache views are unchanged (a decode loop calls with the same
+    // caches step after step)
+    struct Key {
+        int dtype, cap, Hkv, B;
+        View4 k, v;
+        bool operator==(const Key& x) const {
+            auto same = [](const View4& a, const View4& b) { return a.ptr == b.ptr && a.sb == b.sb && a.sh == b.sh && a.ss == b.ss; };
+            return dtype == x.dtype && cap == x.cap && Hkv == x.Hkv && B == x.B && same(k, x.k) && same(v, x.v);
+        }
+    };
+    static thread_local Key cached_key{};
+    static thread_local KvMaps maps;
+    static thread_local bool cached_valid = false;
+    const Key key{p.dtype, p.cache_cap, p.Hkv, p.B, p.k_cache, p.v_cache};
+    if (!cached_valid || !(cached_key == key)) {
+        cached_valid = false;
+        if (int rc = make_kv_map(&maps.k, p.dtype, p.k_cache, p.cache_cap, p.Hkv, p.B)) return rc;
+        if (int rc = make_kv_map(&maps.v, p.dtype, p.v_cache, p.cache_cap, p.Hkv, p.B)) return rc;
+        cached_key = key;
+        cached_valid = true;
+    }
     auto kernel = decode_gqa_mma_kernel<T, NREP, CW, kStages, MINB>;
     static thread_local bool configured[64] = {};      // per device ordinal: the attribute belongs to the device's context
     int dev = 0;

@@ -605,12 +605,32 @@ int make_map(CUtensorMap* m, int dtype, const View4& v, int rows, int H, int B, 
     return VB200_OK;
 }
 
+// The three maps of the last call of this thread, reused while the views they describe are unchanged (a serving loop
+// calls with the same buffers step after step; encoding costs a few microseconds of host time per map).
+struct MapKey {
+    int dtype, D, B, Hq, Hkv, T, Skv;
+    View4 q, k, v;
+    bool operator==(const MapKey& x) const {
+        auto same = [](const View4& a, const View4& b) { return a.ptr == b.ptr && a.sb == b.sb && a.sh == b.sh && a.ss == b.ss; };
+        return dtype == x.dtype && D == x.D && B == x.B && Hq == x.Hq && Hkv == x.Hkv && T == x.T && Skv == x.Skv && same(q, x.q) &&
+               same(k, x.k) && same(v, x.v);
+    }
+};
+
 template <typename T, int D, bool kExactRope>
 int launch_t(cudaStream_t s, const PrefillParams& p) {
-    TmaMaps maps;
-    if (int rc = make_map(&maps.q, p.dtype, p.q, p.T, p.Hq, p.B, D)) return rc;
-    if (int rc = make_map(&maps.k, p.dtype, p.k, p.Skv, p.Hkv, p.B, D)) return rc;
-    if (int rc = make_map(&maps.v, p.dtype, p.v, p.Skv, p.Hkv, p.B, D)) return rc;
+    static thread_local MapKey cached_key{};
+    static thread_local TmaMaps maps;
+    static thread_local bool cached_valid = false;
+    const MapKey key{p.dtype, D, p.B, p.Hq, p.Hkv, p.T, p.Skv, p.q, p.k, p.v};
+    if (!cached_valid || !(cached_key == key)) {
+        cached_valid = false;
+        if (int rc = make_map(&maps.q, p.dtype, p.q, p.T, p.Hq, p.B, D)) return rc;
+        if (int rc = make_map(&maps.k, p.dtype, p.k, p.Skv, p.Hkv, p.B, D)) return rc;
+        if (int rc = make_map(&maps.v, p.dtype, p.v, p.Skv, p.Hkv, p.B, D)) return rc;
+        cached_key = key;
+        cached_valid = true;
+    }
     static thread_local bool configured[64] = {};      // per device ordinal: the attribute belongs to the device's context
     int dev = 0;
     VB200_CUDA_TRY(cudaGetDevice(&dev));
@@ -636,10 +656,9 @@ int launch_t(cudaStream_t s, const PrefillParams& p) {
 }  // namespace
 
 
-// Which of the two tensor-core kernels runs a head_dim-128 call: the two-SM kernel (prefill_pair_sm100.cu) works on
-// four query tiles per item, so it is chosen when the call fills them -- four query heads per KV head, or enough
-// rows for the two / four row tiles the other pairings need; short calls stay on the single-CTA kernel below.
-// VB200_PREFILL_KERNEL=single|pair in the environment overrides the choice (read once; for A/B measurements).
+// Which of the two tensor-core kernels runs a head_dim-128 call: the single-CTA kernel of this file, unless
+// VB200_PREFILL_KERNEL=pair in the environment (read once per process) asks for the two-SM kernel
+// (prefill_pair_sm100.cu), which is correct but measured slower at every shape tried.
 static bool use_pair_kernel(const PrefillParams& p) {
     static const int forced = []() {
         const char* e = getenv("VB200_PREFILL_KERNEL");
