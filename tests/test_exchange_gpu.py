@@ -132,17 +132,19 @@ def test_absent_peer_times_out_with_a_status_not_a_hang(cuda, oracle):
     assert np.abs(from_torch(out) - o).max() <= 2.0 ** -8 * max(1.0, np.abs(o).max())
 
 
-@pytest.mark.parametrize("n_rep", [8, 4])
-def test_decode_and_exchange_in_one_launch_with_an_emulated_peer(cuda, oracle, n_rep):
+@pytest.mark.parametrize("n_rep,L,num_splits", [(8, 4096, 0), (4, 4096, 0), (8, 8192, 64), (4, 8192, 64)])
+def test_decode_and_exchange_in_one_launch_with_an_emulated_peer(cuda, oracle, n_rep, L, num_splits):
     """vb200_decode_exchange_fwd: rank 0 of a 2-way sequence-sharded decode runs its shard, merges its splits and
     exchanges in ONE launch; rank 1 is emulated by seeding what it would have pushed (its record comes from a
     vb200_decode_fwd(partial_out) over the second shard).  Result against the oracle's attention over the whole
     context, query rotated at the absolute position; push side: the stand-in peer buffer received this rank's record
-    (compared with the two-call form's record)."""
+    (compared with the two-call form's record).  With 64 splits of 64 keys the group's records do not fit one staging
+    round of the in-kernel split merge (20 records for 8-head groups, 44 for 4-head groups): the later rounds fold in
+    with a rescale."""
     import torch
     from helpers import bf16_round, maxabs, to_torch
     from vesper_b200 import capi
-    B, Hkv, D, L = 1, 2, 128, 4096
+    B, Hkv, D = 1, 2, 128
     Hq = Hkv * n_rep
     rows = B * Hq
     rng = np.random.default_rng(70 + n_rep)
@@ -169,7 +171,7 @@ def test_decode_and_exchange_in_one_launch_with_an_emulated_peer(cuda, oracle, n
         torch.cuda.synchronize()
         _seed_peer(bufs[0], 2, rows, D, 1, step, rec1.cpu().numpy())
         capi.decode_exchange(tq, k0, v0, [b.data_ptr() for b in bufs], 0, out, lse, scale=scale, theta=10000.0,
-                             uniform_len=half, max_len=half, pos_offset=0, q_positions=qpos)
+                             uniform_len=half, max_len=half, pos_offset=0, q_positions=qpos, num_splits=num_splits)
         torch.cuda.synchronize()
         capi.check_kernel_status(0)
         q_rot = oracle.apply_rope(q, L, 10000.0)
