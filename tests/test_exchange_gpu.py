@@ -206,3 +206,40 @@ def test_decode_exchange_refuses_shapes_it_does_not_take(cuda):
     assert e.value.status == -2
     torch.cuda.synchronize()
     capi.check_kernel_status(0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n_rep", [8, 4])
+def test_one_launch_step_on_a_ragged_batch_single_rank(cuda, oracle, n_rep):
+    """vb200_decode_exchange_fwd with per-sequence lengths (world 1, so the exchange is the rank with itself): groups
+    of different sequences have different numbers of live splits -- a one-key sequence has a single one, splits past a
+    sequence's end take no ticket -- and every group's last CTA must still find its count.  Against the oracle's ragged
+    decode; three consecutive calls (the ticket words return to zero)."""
+    import torch
+    from helpers import bf16_round, maxabs, to_torch
+    from vesper_b200 import capi
+    B, Hkv, D, cap = 4, 2, 128, 3072
+    Hq = Hkv * n_rep
+    rows = B * Hq
+    lens = np.array([3000, 700, 1, 2049], dtype=np.int32)
+    rng = np.random.default_rng(91 + n_rep)
+    k = bf16_round(rng.standard_normal((B, Hkv, cap, D), dtype=np.float32))
+    v = bf16_round(rng.standard_normal((B, Hkv, cap, D), dtype=np.float32))
+    for b in range(B):
+        k[b, :, lens[b]:] = 0
+        v[b, :, lens[b]:] = 0
+    tk, tv = to_torch(k, torch.bfloat16, cuda), to_torch(v, torch.bfloat16, cuda)
+    tl = torch.from_numpy(lens).to(cuda)
+    buf = torch.zeros(capi.exchange_buffer_bytes(1, rows, D), dtype=torch.uint8, device=cuda)
+    out = torch.empty(rows, D, dtype=torch.bfloat16, device=cuda)
+    lse = torch.empty(rows, dtype=torch.float32, device=cuda)
+    scale = float(1.0 / np.sqrt(D))
+    for step in range(3):
+        q = bf16_round(rng.standard_normal((B, Hq, 1, D), dtype=np.float32))
+        capi.decode_exchange(to_torch(q, torch.bfloat16, cuda), tk, tv, [buf.data_ptr()], 0, out, lse, scale=scale,
+                             seq_lens=tl, max_len=int(lens.max()))
+        torch.cuda.synchronize()
+        capi.check_kernel_status(0)
+        want_o, want_lse = oracle.decode_ragged(q[:, :, 0], k, v, lens)
+        assert maxabs(from_torch(out).reshape(B, Hq, D), want_o) <= 1e-2, step
+        assert maxabs(from_torch(lse).reshape(B, Hq), want_lse) <= 1e-3, step
