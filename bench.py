@@ -149,7 +149,9 @@ def cpu_prefill_sample(target_seconds=12.0, threads=None, S=None, total_slices=N
     dt = time.time() - t0
     slices = sum(done)
     flops = slices * 4.0 * D * S * (S + 1) / 2.0
-    return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=threads, kind=kind,
+    # the reference's attention code is single-threaded: one core's rate is its own figure, `value` the all-threads one
+    one_core = (4.0 * D * S * (S + 1) / 2.0) / max(t_one, 1e-9) / 1e12
+    return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=threads, kind=kind, value_one_core=one_core,
                 sample=f"{slices} slice passes = {threads} distinct seeded (batch, head) slices of {what} (one per host thread; the workload has "
                        f"{total_slices}) x {per_thread} repeats each (S={S}, D={D}, fp32, RoPE + causal flash), {dt:.1f} s; "
                        f"single-thread slice {t_one * 1e3:.0f} ms"), dt
