@@ -530,6 +530,12 @@ def bench_sharded(cx, nsteps=50):
     def step_fused():
         cuda_step(step4, q4, ks, vs, scale=scale, theta=10000.0, partial_buf=part, out=out4, workspace=ws4, exchange=exchange, qpos=qpos)
 
+    def step_local_only():
+        # this rank's shard alone (split kernel + combine into a partial record, nothing exchanged): what is left of a
+        # step's time is the exchange's share
+        capi.decode(q4, None, ks, vs, scale=scale, theta=10000.0, uniform_len=end - begin, max_len=end - begin, pos_offset=begin,
+                    q_positions=qpos, partial_out=part, workspace=ws4)
+
     one_launch_ok = exchange is not None and exchange.supports_one_launch(Bq, Hq, Hkv)
 
     def step_one_launch():
@@ -548,6 +554,25 @@ def bench_sharded(cx, nsteps=50):
         return cx.max_over_ranks(s0.elapsed_time(s1)) / n
 
     ms_gather = timed(step_gather, nsteps)
+    ms_local = None
+    if world > 1:
+        try:
+            cx.sync_all()
+            graph_local = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_local):
+                for _ in range(nsteps):
+                    step_local_only()
+            for _ in range(2):
+                graph_local.replay()
+            cx.sync_all()
+            s0, s1 = cx.event(), cx.event()
+            s0.record()
+            graph_local.replay()
+            s1.record()
+            cx.sync_all()
+            ms_local = cx.max_over_ranks(s0.elapsed_time(s1)) / nsteps
+        except Exception as e:
+            exchange_error = f"graph (local only): {type(e).__name__}: {e}"[:200]
     ms_fused = ms_graph = ms_one = ms_one_graph = None
     graph_one = None
     if one_launch_ok:
@@ -655,6 +680,8 @@ def bench_sharded(cx, nsteps=50):
         "ms_per_step": ms, "scaling": "strong", "path": path,
         "ms_per_step_all_gather_path": ms_gather, "ms_per_step_fused_exchange": ms_fused, "ms_per_step_fused_exchange_graph": ms_graph,
         "ms_per_step_one_launch": ms_one, "ms_per_step_one_launch_graph": ms_one_graph, "one_launch_max_diff_vs_all_gather_path": one_launch_max_diff,
+        "ms_per_step_local_shard_only_graph": ms_local,
+        "exchange_share_of_step": (1.0 - ms_local / ms) if (ms_local and ms > 0) else None,
         "exchange_error": exchange_error,
         "paths_bit_identical": paths_bit_identical, "max_abs_err": max_abs_err,
         "max_abs_err_what": f"query heads {err_heads} over the whole context against the CPU oracle (gate 1e-2, bf16)",

@@ -174,6 +174,13 @@ DecodePlan plan_decode(const vb200_decode_args* a, int waves = 4) {
         // more than 512 keys per CTA so ragged batches balance (one common length needs no such cap:
         // longer chunks spend less of a CTA's life in its prologue and merge)
         long long units = static_cast<long long>(a->B) * a->Hkv;
+        if (!a->seq_lens && waves == 4) {
+            // One common length: nothing to balance, so fewer and longer chunks win (measured on 8 groups of 8 heads, split
+            // kernel + combine from a graph: 131072 keys 95.4 us with four CTAs per SM, 90.5 with two, 88.8 with one; 16384
+            // keys 23.5 / 16.6 / 17.3 us): one CTA per SM once a CTA of the two-per-SM plan would stream 1024 keys or more.
+            const long long two = std::max<long long>(1, 2LL * sm_count() / units);
+            waves = (max_total / two >= 1024) ? 1 : 2;
+        }
         const long long ctas = static_cast<long long>(waves) * sm_count();
         // (one wave: rounded down, so that no SM gets a second CTA -- it would finish last, at twice the time)
         int want = waves == 1 ? static_cast<int>(ctas / units) : static_cast<int>((ctas + units - 1) / units);
