@@ -51,10 +51,10 @@ def test_decode_workspace_plan_is_consistent(lib):
     d = capi.DecodeArgs()
     d.struct_size = C.sizeof(capi.DecodeArgs)
     d.B, d.Hq, d.Hkv, d.D, d.cache_cap, d.max_len = 32, 32, 8, 128, 8448, 8193
-    d.seq_lens = 0x1000          # per-sequence lengths (only its presence matters for the plan): splits of at most 512 keys
+    d.seq_lens = 0x1000          # per-sequence lengths (only its presence matters for the plan): splits of at most 2048 keys
     n = lib.vb200_decode_workspace_bytes(C.byref(d))
-    # [B,Hkv,splits,n_rep,D+2] fp32 with 512-key splits -> 17 splits
-    assert n >= 32 * 8 * 17 * 4 * 130 * 4 and n % 256 == 0
+    # [B,Hkv,splits,n_rep,D+2] fp32 with 2048-key splits of 8193 keys -> 5 splits
+    assert n >= 32 * 8 * 5 * 4 * 130 * 4 and n % 256 == 0
     d.seq_lens = None            # one common length: longer chunks, fewer splits
     assert lib.vb200_decode_workspace_bytes(C.byref(d)) < n
     d.seq_lens = 0x1000
