@@ -59,7 +59,7 @@ def load_traffic():
     """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels,
     copied from the ncu captures summarised in profiles/prefill_sm100_c2.md and
     profiles/decode_gqa_mma_c3.md (captured on exactly these workloads, so no scaling applies)."""
-    return {"prefill_sm100_bytes_per_launch": 138.3e6, "decode_splitkv_bytes_per_launch": 709.2e6}
+    return {"prefill_sm100_bytes_per_launch": 138.3e6, "decode_splitkv_bytes_per_launch": 705.5e6}
 
 
 class ClockSampler:
