@@ -20,6 +20,9 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 exchange_combine_kernel(ExchangeParams p) {
     const int c = blockIdx.x;
+    // Launched with programmatic stream serialization: the blocks may become resident while the kernel that writes the
+    // partial records drains; nothing of its output is touched before this wait returns.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long r0 = static_cast<long long>(c) * p.rows_per_cta;
     const long long r1 = min(p.rows, r0 + p.rows_per_cta);
     __shared__ uint32_t s_step;
@@ -42,9 +45,19 @@ int launch_exchange_combine(cudaStream_t s, ExchangeParams p) {
         ctas = (p.rows + p.rows_per_cta - 1) / p.rows_per_cta;
     }
     if (p.timeout_cycles <= 0) p.timeout_cycles = kWaitCycles;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     switch (p.dtype) {
-        case VB200_BF16: exchange_combine_kernel<__nv_bfloat16><<<static_cast<unsigned>(ctas), kThreads, 0, s>>>(p); break;
-        case VB200_F16: exchange_combine_kernel<__half><<<static_cast<unsigned>(ctas), kThreads, 0, s>>>(p); break;
+        case VB200_BF16: VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, exchange_combine_kernel<__nv_bfloat16>, p)); break;
+        case VB200_F16: VB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, exchange_combine_kernel<__half>, p)); break;
         default: return set_detail(VB200_ERR_UNSUPPORTED, "exchange_combine: dtype must be bf16 or fp16");
     }
     note_launch();
