@@ -211,12 +211,15 @@ int vb200_lse_combine(int device, void* stream, const float* partials, int32_t R
 
 /* ---- fused exchange + merge for sequence-sharded decode (no reference counterpart) ----------
  * Replaces "all-gather the partial_out records of all ranks, then vb200_lse_combine" by one kernel
- * over NVLink peer memory: every rank stores its records into every rank's exchange buffer (plain
- * peer stores), publishes a flag, waits for all ranks' flags in its own buffer and merges.
+ * over NVLink peer memory: every rank stores its records into every rank's exchange buffer as 8-byte words
+ * {fp32 value, call number} (plain peer stores; a word is valid as soon as its number matches, so there is no
+ * separate flag and no system-wide fence), waits until every rank's words have landed in its own buffer and merges.
  * peer_buffers[r] is rank r's exchange buffer as THIS process addresses it (peer-mapped device
  * memory: CUDA IPC, VMM or a symmetric-memory allocator; entry [rank] is the local buffer); each is
  * vb200_exchange_buffer_bytes(...) long and zero-filled once before the first call.  All ranks
- * must make the same sequence of calls with the same rows / D.  step: 0 = number the calls with
+ * must make the same sequence of calls with the same rows / D, and a set of buffers serves ONE entry point
+ * (vb200_exchange_combine or vb200_decode_exchange_fwd: they number their calls per exchanging block and cut the
+ * rows into blocks differently; mixing them on one buffer ends in the bounded wait's error).  step: 0 = number the calls with
  * a counter kept in the buffer (works under CUDA-graph replay), else a caller-chosen number that
  * grows by one per call.  A rank that never arrives ends the wait after timeout_cycles GPU clock
  * cycles (0 = about one second): the output is left unwritten and vb200_check_kernel_status
@@ -244,7 +247,7 @@ int vb200_exchange_combine(const vb200_exchange_args* a);
  * over this rank's shard of the KV sequence, with the merge of its splits and the exchange above run as the tail of
  * the split kernel -- the CTA that delivers the last split of a (batch, kv_head) merges that group's splits in
  * registers / shared memory, stores the merged records into every rank's exchange buffer, waits (bounded) for the
- * peers' flags and writes the final rows.  No combine kernel, no exchange kernel, no partial records in HBM: two
+ * peers' words and writes the final rows.  No combine kernel, no exchange kernel, no partial records in HBM: two
  * launch gaps and two round trips less than vb200_decode_fwd(partial_out) + vb200_exchange_combine, which is what a
  * step of a few microseconds per GPU is made of.
  * `a`: as for vb200_decode_fwd (o, lse, partial_out are ignored; the workspace is needed); `x`: as for

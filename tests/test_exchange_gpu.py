@@ -1,6 +1,6 @@
 """vb200_exchange_combine (the fused peer-memory exchange + LSE merge of sequence-sharded decode) on ONE
-GPU: the other ranks are emulated by writing what they would have pushed (records + flags) into this
-rank's buffer before the launch, so no launch ever waits for another one.  The real multi-GPU run is
+GPU: the other ranks are emulated by writing what they would have pushed (8-byte words {value, call number})
+into this rank's buffer before the launch, so no launch ever waits for another one.  The real multi-GPU run is
 tests/test_exchange_multi_gpu.py."""
 import numpy as np
 import pytest
@@ -9,16 +9,7 @@ from helpers import from_torch
 
 pytestmark = pytest.mark.gpu
 
-FLAG_BASE, SLOT_BASE, MAX_WORLD, MAX_CTAS, ROWS_PER_CTA = 4096, 4096 + 2 * 16 * 64 * 4, 16, 64, 4
-
-
-def _ctas(rows):
-    """CTAs the launcher uses: 4 rows each, at most 64 (then more rows per CTA)."""
-    n = (rows + ROWS_PER_CTA - 1) // ROWS_PER_CTA
-    if n > MAX_CTAS:
-        per = (rows + MAX_CTAS - 1) // MAX_CTAS
-        n = (rows + per - 1) // per
-    return n
+SLOT_BASE = 4096 + 2 * 16 * 64 * 4
 
 
 def _partials(rng, world, rows, D):
@@ -37,21 +28,33 @@ def _want(oracle, p):
     return o, lse
 
 
-def _seed_peer(buf, world, rows, D, src, step, record):
+ONE_LAUNCH_TAG = 0x80000000      # the numbers vb200_decode_exchange_fwd's words carry have bit 31 set
+
+
+def _seed_peer(buf, world, rows, D, src, step, record, tag=0):
     """What rank `src` would have pushed into this buffer for call number `step`."""
     import torch
     parity = step & 1
     n = rows * (D + 2)
-    off = SLOT_BASE + (parity * world + src) * n * 4
-    buf[off:off + n * 4].view(torch.float32).copy_(torch.from_numpy(record.reshape(-1)).to(buf.device))
-    ctas = _ctas(rows)
-    f0 = FLAG_BASE + ((parity * MAX_WORLD + src) * MAX_CTAS) * 4
-    buf[f0:f0 + ctas * 4].view(torch.int32).fill_(step)
+    off = SLOT_BASE + (parity * world + src) * n * 8
+    words = np.empty((n, 2), np.uint32)
+    words[:, 0] = record.reshape(-1).astype(np.float32).view(np.uint32)
+    words[:, 1] = step | tag
+    buf[off:off + n * 8].view(torch.int32).copy_(torch.from_numpy(words.reshape(-1).view(np.int32)).to(buf.device))
+
+
+def _pushed(buf, world, rows, D, src, step):
+    """(values, call numbers) of the words rank `src` pushed into this buffer for call number `step`."""
+    import torch
+    n = rows * (D + 2)
+    off = SLOT_BASE + ((step & 1) * world + src) * n * 8
+    w = buf[off:off + n * 8].view(torch.int32).cpu().numpy().view(np.uint32).reshape(n, 2)
+    return w[:, 0].copy().view(np.float32), w[:, 1]
 
 
 def test_buffer_size_and_argument_checks(lib):
     from vesper_b200 import capi
-    assert capi.exchange_buffer_bytes(8, 64, 128) == SLOT_BASE + 2 * 8 * 64 * 130 * 4
+    assert capi.exchange_buffer_bytes(8, 64, 128) == SLOT_BASE + 2 * 8 * 64 * 130 * 8
     assert capi.exchange_buffer_bytes(17, 64, 128) == 0 and capi.exchange_buffer_bytes(0, 64, 128) == 0
     a = capi.ExchangeArgs()
     assert lib.vb200_exchange_combine(None) == -1
@@ -97,18 +100,14 @@ def test_emulated_peers_receive_side_and_push_side(cuda, oracle, world, rows, D)
         o, l = _want(oracle, p)
         assert np.abs(from_torch(out) - o).max() <= 2.0 ** -8 * max(1.0, np.abs(o).max()), step
         assert np.abs(from_torch(lse) - l).max() <= 1e-4, step
-        # push side: every stand-in peer buffer now holds our records in slot[parity][rank] and our flags
-        n = rows * (D + 2)
+        # push side: every stand-in peer buffer now holds our records in slot[parity][rank], every word with the call number
         for dst in range(world):
-            off = SLOT_BASE + ((step & 1) * world + rank) * n * 4
-            got = bufs[dst][off:off + n * 4].view(torch.float32).cpu().numpy()
-            assert np.array_equal(got, p[rank].reshape(-1))
-            f0 = FLAG_BASE + (((step & 1) * MAX_WORLD + rank) * MAX_CTAS) * 4
-            assert bool((bufs[dst][f0:f0 + _ctas(rows) * 4].view(torch.int32) == step).all())
+            got, numbers = _pushed(bufs[dst], world, rows, D, rank, step)
+            assert np.array_equal(got, p[rank].reshape(-1)) and bool((numbers == step).all())
 
 
 def test_absent_peer_times_out_with_a_status_not_a_hang(cuda, oracle):
-    """A flag that nothing sets: the bounded wait (here 2e6 cycles, about a millisecond) gives up, the
+    """Words that nothing writes: the bounded wait (here 2e6 cycles, about a millisecond) gives up, the
     output stays untouched, the status word reports it, and the next call works."""
     import torch
     from vesper_b200 import capi
@@ -169,7 +168,7 @@ def test_decode_and_exchange_in_one_launch_with_an_emulated_peer(cuda, oracle, n
         capi.decode(tq, None, k0, v0, scale=scale, theta=10000.0, uniform_len=half, max_len=half, pos_offset=0,
                     q_positions=qpos, partial_out=rec0)
         torch.cuda.synchronize()
-        _seed_peer(bufs[0], 2, rows, D, 1, step, rec1.cpu().numpy())
+        _seed_peer(bufs[0], 2, rows, D, 1, step, rec1.cpu().numpy(), tag=ONE_LAUNCH_TAG)
         capi.decode_exchange(tq, k0, v0, [b.data_ptr() for b in bufs], 0, out, lse, scale=scale, theta=10000.0,
                              uniform_len=half, max_len=half, pos_offset=0, q_positions=qpos, num_splits=num_splits)
         torch.cuda.synchronize()
@@ -180,17 +179,15 @@ def test_decode_and_exchange_in_one_launch_with_an_emulated_peer(cuda, oracle, n
         assert maxabs(from_torch(lse), want_lse[0]) <= 1e-3, step
         # push side: our merged record in the stand-in peer's slot[parity][0]; same numbers as the two-call form up to
         # the summation order of the split merge
-        n = rows * (D + 2)
-        off = SLOT_BASE + ((step & 1) * 2 + 0) * n * 4
-        got = bufs[1][off:off + n * 4].view(torch.float32).cpu().numpy().reshape(rows, D + 2)
+        got, numbers = _pushed(bufs[1], 2, rows, D, 0, step)
+        got = got.reshape(rows, D + 2)
+        assert bool((numbers == (step | ONE_LAUNCH_TAG)).all())
         ref = rec0.cpu().numpy()
         # (for 4-head groups the two-call form at this length runs the CUDA-core split kernel, the one-launch form the
         # warp-MMA one, whose P is rounded to 16 bits: a few 1e-4 apart on records of size ~0.1)
         # (m is a reference maximum, raised lazily, not necessarily the true one: only m + ln l is determined)
         assert np.abs(got[:, :D] - ref[:, :D]).max() <= 1e-3
         assert np.abs((got[:, D] + np.log(got[:, D + 1])) - (ref[:, D] + np.log(ref[:, D + 1]))).max() <= 1e-3
-        f0 = FLAG_BASE + (((step & 1) * MAX_WORLD + 0) * MAX_CTAS) * 4
-        assert bool((bufs[1][f0:f0 + B * Hkv * 4].view(torch.int32) == step).all())
 
 
 def test_decode_exchange_refuses_shapes_it_does_not_take(cuda):

@@ -1,7 +1,7 @@
 // Sequence-sharded decode: exchange of the per-rank partial results (O/l, m, l) and their
 // log-sum-exp merge in ONE kernel over NVLink peer memory -- each rank stores its partial rows
-// straight into every peer's receive slots (plain peer stores, no TMA, no multicast), raises a
-// per-CTA flag there, waits (bounded) for the flags of all ranks in its own buffer and merges.
+// straight into every peer's receive slots (plain 8-byte peer stores {value, call number}, no TMA, no multicast),
+// waits (bounded) until every rank's words of this call have landed in its own buffer and merges.
 // It stands in for "all-gather, then vb200_lse_combine": one launch, no collective library call, no
 // host wait between the two.  The merge algebra is the online-softmax recurrence of
 // src/ops/flash_attention.cpp:309-345 applied across shards.
@@ -33,7 +33,7 @@ exchange_combine_kernel(ExchangeParams p) {
 }  // namespace
 
 size_t exchange_buffer_bytes(int world, long long rows, int D) {
-    return kXSlotBase + static_cast<size_t>(2) * world * rows * (D + 2) * sizeof(float);
+    return kXSlotBase + static_cast<size_t>(2) * world * rows * (D + 2) * 8;      // 8-byte words {value, call number}
 }
 
 int launch_exchange_combine(cudaStream_t s, ExchangeParams p) {

@@ -476,7 +476,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa_mma_kernel(con
     // (the staging area is free again: the peers' rows of this group land there for the final merge)
     exchange_rows<T, CW * 32>(p.xchg, unit, r0, r0 + NREP, rec, tid, &s_step, &s_ok,
                               [] { asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory"); },
-                              reinterpret_cast<float*>(stage2), kStageCap * kBlk2 * 2);
+                              reinterpret_cast<float*>(stage2), kStageCap * kBlk2 * 2, 0x80000000u);
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

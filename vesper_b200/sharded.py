@@ -104,7 +104,7 @@ class ShardedDecodeStep:
 class PeerExchange:
     """Exchange buffers of all ranks mapped into every process (torch symmetric memory supplies the
     allocation and the address exchange: plumbing only) for ``vb200_exchange_combine``, which pushes
-    this rank's partial records into every peer's buffer over NVLink, waits for the peers' flags and
+    this rank's partial records into every peer's buffer over NVLink, waits for the peers' records and
     merges -- one kernel instead of all-gather + combine.  Collective: every rank constructs it with
     the same (rows, D) at the same point."""
 
@@ -114,14 +114,19 @@ class PeerExchange:
         from . import capi
         self.world, self.rank, self.rows, self.D = world, rank, rows, D
         nbytes = capi.exchange_buffer_bytes(world, rows, D)
-        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
-        self.buf.zero_()
-        handle = symm_mem.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
-        self.ptrs = [int(p) for p in handle.buffer_ptrs]
-        if len(self.ptrs) != world or self.ptrs[rank] != self.buf.data_ptr():
-            raise ShardExchangeError("symmetric memory rendezvous returned an unexpected set of buffers")
-        self._handle = handle
-        torch.cuda.synchronize(device)          # every rank's flags are zero before anybody publishes one
+        # one set of buffers per entry point: vb200_exchange_combine (`ptrs`) and vb200_decode_exchange_fwd (`ptrs_one`)
+        # number their calls per exchanging block and cut the rows into blocks differently
+        self._bufs, self._handles, sets = [], [], []
+        for _ in range(2):
+            buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+            buf.zero_()
+            handle = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+            if len(ptrs) != world or ptrs[rank] != buf.data_ptr():
+                raise ShardExchangeError("symmetric memory rendezvous returned an unexpected set of buffers")
+            self._bufs.append(buf); self._handles.append(handle); sets.append(ptrs)
+        self.buf, self.ptrs, self.ptrs_one = self._bufs[0], sets[0], sets[1]
+        torch.cuda.synchronize(device)          # every rank's buffer is zero before anybody stores into it
         dist.barrier()
 
     def combine(self, partial, out, lse=None, *, timeout_cycles=0, stream=None):
@@ -148,7 +153,7 @@ def cuda_step(step: ShardedDecodeStep, q, k_shard, v_shard, *, scale, theta, par
     if qpos is None:
         qpos = torch.full((B,), step.context_len, dtype=torch.int32, device=q.device)
     if exchange is not None and one_launch:
-        capi.decode_exchange(q, k_shard, v_shard, exchange.ptrs, exchange.rank, out, lse, scale=scale, theta=theta,
+        capi.decode_exchange(q, k_shard, v_shard, exchange.ptrs_one, exchange.rank, out, lse, scale=scale, theta=theta,
                              uniform_len=end - begin, max_len=end - begin, pos_offset=begin, q_positions=qpos,
                              workspace=workspace, stream=stream)
         return out
