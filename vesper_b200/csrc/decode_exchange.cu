@@ -27,7 +27,9 @@ exchange_combine_kernel(ExchangeParams p) {
     const long long r1 = min(p.rows, r0 + p.rows_per_cta);
     __shared__ uint32_t s_step;
     __shared__ int s_ok;
-    exchange_rows<T, kThreads>(p, c, r0, r1, p.partial + r0 * (p.D + 2), threadIdx.x, &s_step, &s_ok, [] { __syncthreads(); });
+    extern __shared__ __align__(16) unsigned char stage_raw[];       // all ranks' words of this CTA's rows, when they fit
+    exchange_rows<T, kThreads>(p, c, r0, r1, p.partial + r0 * (p.D + 2), threadIdx.x, &s_step, &s_ok, [] { __syncthreads(); },
+                               p.stage_floats > 0 ? reinterpret_cast<float*>(stage_raw) : nullptr, p.stage_floats);
 }
 
 }  // namespace
@@ -45,10 +47,26 @@ int launch_exchange_combine(cudaStream_t s, ExchangeParams p) {
         ctas = (p.rows + p.rows_per_cta - 1) / p.rows_per_cta;
     }
     if (p.timeout_cycles <= 0) p.timeout_cycles = kWaitCycles;
+    // room to stage every rank's words of a CTA's rows (8 bytes per value) in shared memory, when that fits
+    size_t stage = static_cast<size_t>(p.world) * p.rows_per_cta * (p.D + 2) * 8;
+    if (stage > 96 * 1024) stage = 0;
+    p.stage_floats = static_cast<int>(stage / 4);
+    if (stage > 48 * 1024) {
+        static thread_local bool configured[64][2] = {};
+        int dev = 0;
+        VB200_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64) return set_detail(VB200_ERR_NO_DEVICE, "device ordinal out of range");
+        const int which = p.dtype == VB200_BF16 ? 0 : 1;
+        if (!configured[dev][which]) {
+            if (which == 0) VB200_CUDA_TRY(cudaFuncSetAttribute(exchange_combine_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+            else VB200_CUDA_TRY(cudaFuncSetAttribute(exchange_combine_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+            configured[dev][which] = true;
+        }
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(ctas));
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = stage;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -61,6 +61,7 @@ struct ExchangeParams {
     const float* partial;                    // local [rows, D+2]
     long long rows;
     long long rows_per_cta;                  // filled in by the launcher
+    int stage_floats;                        // dynamic shared memory of the stand-alone kernel, in floats (0: none)
     int D, dtype;
     void* out;                               // [rows, D]
     float* lse;                              // [rows] or null
