@@ -90,6 +90,16 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa_mma_kernel(con
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+    // (nothing below depends on the previous kernel until the wait: the barriers and the tensor maps are set up while it drains)
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], CW); }
+        sm->abort_flag = 0;
+        mbar_fence_init();
+    } else if (tid == CW * 32) {
+        tma_prefetch_desc(&maps.k);
+        tma_prefetch_desc(&maps.v);
+    }
+    __syncthreads();
     asm volatile("griddepcontrol.wait;" ::: "memory");       // q / k_new / v_new / lengths may come from the previous kernel
     const StepLen sl = step_length(p, b);
     const int len = sl.len, total = sl.total;
@@ -104,12 +114,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa_mma_kernel(con
     const bool owns_new = sl.append && (len / p.chunk == split);
     const int ntiles = (k_end > k_begin) ? (k_end - k_begin + kTileM - 1) / kTileM : 0;
 
-    if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], CW); }
-        sm->abort_flag = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
     const WaitCtx ctx{&sm->abort_flag, p.status};
     const T* kc = static_cast<const T*>(p.k_cache.ptr) + b * p.k_cache.sb + kvh * p.k_cache.sh;
     const T* vc = static_cast<const T*>(p.v_cache.ptr) + b * p.v_cache.sb + kvh * p.v_cache.sh;
@@ -117,8 +121,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, MINB) decode_gqa_mma_kernel(con
     if (warp == CW) {
         // ---------------- producer: one lane issues four TMA boxes per tile ----------------
         if (lane == 0) {
-            tma_prefetch_desc(&maps.k);
-            tma_prefetch_desc(&maps.v);
             for (int t = 0; t < ntiles; ++t) {
                 const int s = t % kStages;
                 if (t >= kStages && !mbar_wait(&sm->empty[s], ((t / kStages) - 1) & 1, ctx, 0x18)) break;
