@@ -46,6 +46,20 @@ def test_struct_layout_and_host_helpers(lib):
     assert np.array_equal(np.array(list(f), np.float32), want)
 
 
+def test_decode_plan_for_one_common_length(lib):
+    """Without per-sequence lengths the split plan aims at one or two CTAs per SM (not four): the long-context decode
+    of 8 groups of 8 heads over 131072 keys gets 148 // 8 = 18 splits, a 16384-key shard 2 * 148 / 8 = 37."""
+    from vesper_b200 import capi
+    d = capi.DecodeArgs()
+    d.struct_size = C.sizeof(capi.DecodeArgs)
+    d.B, d.Hq, d.Hkv, d.D = 1, 64, 8, 128
+    for max_len, splits in ((131072, 18), (16384, 37)):
+        d.cache_cap, d.max_len, d.uniform_len = max_len, max_len, max_len
+        n = lib.vb200_decode_workspace_bytes(C.byref(d))
+        want = (64 + 1 * 8 * splits * 8 * 130) * 4
+        assert n == (want + 255) // 256 * 256, (max_len, n, want)
+
+
 def test_decode_workspace_plan_is_consistent(lib):
     from vesper_b200 import capi
     d = capi.DecodeArgs()

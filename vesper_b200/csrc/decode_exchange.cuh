@@ -5,6 +5,7 @@
 //   [0, 256)                     counter[kXMaxCtas]     call number each exchanging CTA used last
 //   [1024, 1280)                 ticket[kXMaxCtas]      CTAs of a (batch, kv_head) that have delivered their split (fused tail)
 //   [kXSlotBase, ...)            slot[parity][src][rows*(D+2)] of 8-byte words {fp32 value, call number}
+//   (the bytes between 1280 and kXSlotBase are not used)
 // Every value travels with the call number in ONE 8-byte store (single-copy atomic, also across NVLink): the receiver
 // takes a word when its number matches, so there is no separate flag, no release fence on the sender and no acquire
 // round trip on the receiver.  Two parities: a rank can be at most one call ahead of a peer (it needs the peer's words
