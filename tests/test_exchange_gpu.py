@@ -79,7 +79,8 @@ def test_single_rank_equals_lse_combine(cuda, oracle):
     assert np.abs(from_torch(out) - o).max() <= 2.0 ** -8 * np.abs(o).max() and np.abs(from_torch(lse) - l).max() <= 1e-5
 
 
-@pytest.mark.parametrize("world,rows,D", [(2, 64, 128), (4, 7, 64), (8, 64, 128), (3, 300, 128)])
+# (8, 1024, 128): 16 rows per block, whose words of 8 ranks do not fit the shared-memory staging area -- the blocks poll and merge from global memory
+@pytest.mark.parametrize("world,rows,D", [(2, 64, 128), (4, 7, 64), (8, 64, 128), (3, 300, 128), (8, 1024, 128)])
 def test_emulated_peers_receive_side_and_push_side(cuda, oracle, world, rows, D):
     import torch
     from vesper_b200 import capi
